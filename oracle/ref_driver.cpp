@@ -1,0 +1,229 @@
+// TEST INFRASTRUCTURE (parity checker + timed CPU baseline), not product code.
+//
+// Thin C entry points over the reference's own ggml CPU backend, compiled from the reference
+// sources by oracle/Makefile into oracle/_ref/libedge0_ref.so.  The graph built here is the one
+// edge0-infer builds for the quantised MoE FFN:
+//   Builder::route  edge0-infer/src/models/edge0_35b/forward.cpp:262-271
+//   Builder::ffn    edge0-infer/src/models/edge0_35b/forward.cpp:300-311 (routed experts only)
+// plus three optional pieces the benchmark configurations ask for:
+//   * a per-expert bias added to the router logits before the softmax (prefill config),
+//   * the NVFP4 per-expert fp32 scale applied as reshape -> repeat -> get_rows -> mul, the pattern
+//     recognised at third_party/ggml/src/ggml-cuda/ggml-cuda.cu:3655-3673,
+//   * a latent wrapper  x -> D x -> experts in latent width -> U (.)  (edge0-strata
+//     src/latent/latent_moe.cpp:38-92 with one label group).
+#include <chrono>
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "ggml.h"
+#include "ggml-alloc.h"
+#include "ggml-backend.h"
+#include "ggml-cpu.h"
+
+extern "C" {
+
+struct ref_moe_args {
+    // shapes
+    int32_t H;        // hidden width fed to the router (and to D when latent != 0)
+    int32_t L;        // width the experts see (== H unless latent)
+    int32_t E;        // experts
+    int32_t K;        // experts per token
+    int32_t I;        // expert intermediate width
+    int32_t T;        // tokens
+    int32_t wtype;    // ggml_type of the expert tensors (11 = Q3_K, 40 = NVFP4, 0 = F32)
+    int32_t n_threads;
+    int32_t repeats;  // timed graph computes after one warm-up (0: compute once, no timing)
+    int32_t latent;   // 0/1
+    // inputs
+    const float * x;            // [T][H]
+    const float * router_w;     // [E][H]
+    const float * router_bias;  // [E] or null
+    const void  * gate;         // [E][I][L] quantised rows
+    const void  * up;           // [E][I][L]
+    const void  * down;         // [E][L][I]
+    const float * s_gate;       // [E] or null
+    const float * s_up;
+    const float * s_down;
+    const void  * lat_d;        // [L][H] quantised (latent only)
+    const void  * lat_u;        // [H][L] quantised (latent only)
+    const float * s_lat_d;      // [1] or null
+    const float * s_lat_u;      // [1] or null
+    // outputs (any may be null)
+    float   * logits;   // [T][E]
+    float   * probs;    // [T][E]
+    int32_t * ids;      // [T][K]
+    float   * weights;  // [T][K]
+    float   * hidden;   // [T][K][I]   silu(gate)*up
+    float   * down_out; // [T][K][L]   before the route weight
+    float   * moe_out;  // [T][L]      weighted sum in slot order
+    float   * out;      // [T][H or L] final (== moe_out unless latent)
+    double  * ms_best;
+    double  * ms_median;
+};
+
+int ref_type_row_size(int type, int64_t n, int64_t * out) {
+    *out = (int64_t) ggml_row_size((ggml_type) type, n);
+    return 0;
+}
+
+// ggml_quantize_chunk without an importance matrix = quantize_row_*_ref
+// (third_party/ggml/src/ggml-quants.c:1229 Q3_K, :384 NVFP4).
+int ref_quantize(int type, const float * src, void * dst, int64_t nrows, int64_t n_per_row) {
+    ggml_quantize_chunk((ggml_type) type, src, dst, 0, nrows, n_per_row, nullptr);
+    return 0;
+}
+
+int ref_dequantize(int type, const void * src, float * dst, int64_t n) {
+    const auto * tr = ggml_get_type_traits((ggml_type) type);
+    if (!tr || !tr->to_float) return 1;
+    tr->to_float(src, dst, n);
+    return 0;
+}
+
+// Activation quantiser of the CPU backend for a weight type (vec_dot_type's from_float):
+// Q8_K for Q3_K, Q8_0 for NVFP4.  Returns the byte size written.
+int64_t ref_quantize_activation(int wtype, const float * src, void * dst, int64_t n) {
+    const auto * tc = ggml_get_type_traits_cpu((ggml_type) wtype);
+    const ggml_type vt = tc->vec_dot_type;
+    ggml_get_type_traits_cpu(vt)->from_float(src, dst, n);
+    return (int64_t) ggml_row_size(vt, n);
+}
+
+int ref_vec_dot(int wtype, int64_t n, const void * wrow, const void * act, float * out) {
+    const auto * tc = ggml_get_type_traits_cpu((ggml_type) wtype);
+    tc->vec_dot((int) n, out, 0, wrow, 0, act, 0, 1);
+    return 0;
+}
+
+static ggml_tensor * scaled(ggml_context * c, ggml_tensor * mm, ggml_tensor * scale, ggml_tensor * ids, int E, int T) {
+    if (!scale) return mm;
+    ggml_tensor * s = ggml_reshape_2d(c, scale, 1, E);
+    s = ggml_repeat_4d(c, s, 1, E, T, 1);
+    s = ggml_get_rows(c, s, ids);  // [1, K, T]
+    return ggml_mul(c, mm, s);
+}
+
+int ref_moe_layer(const ref_moe_args * a) {
+    const int H = a->H, L = a->latent ? a->L : a->H, E = a->E, K = a->K, I = a->I, T = a->T;
+    const ggml_type wt = (ggml_type) a->wtype;
+
+    ggml_init_params ip = { ggml_tensor_overhead() * 256 + ggml_graph_overhead_custom(512, false), nullptr, true };
+    ggml_context * c = ggml_init(ip);
+    if (!c) return 1;
+
+    ggml_tensor * x   = ggml_new_tensor_2d(c, GGML_TYPE_F32, H, T);
+    ggml_tensor * rw  = ggml_new_tensor_2d(c, GGML_TYPE_F32, H, E);
+    ggml_tensor * rb  = a->router_bias ? ggml_new_tensor_1d(c, GGML_TYPE_F32, E) : nullptr;
+    ggml_tensor * wg  = ggml_new_tensor_3d(c, wt, L, I, E);
+    ggml_tensor * wu  = ggml_new_tensor_3d(c, wt, L, I, E);
+    ggml_tensor * wd  = ggml_new_tensor_3d(c, wt, I, L, E);
+    ggml_tensor * sg  = a->s_gate ? ggml_new_tensor_1d(c, GGML_TYPE_F32, E) : nullptr;
+    ggml_tensor * su  = a->s_up   ? ggml_new_tensor_1d(c, GGML_TYPE_F32, E) : nullptr;
+    ggml_tensor * sd  = a->s_down ? ggml_new_tensor_1d(c, GGML_TYPE_F32, E) : nullptr;
+    ggml_tensor * ld  = a->latent ? ggml_new_tensor_2d(c, wt, H, L) : nullptr;
+    ggml_tensor * lu  = a->latent ? ggml_new_tensor_2d(c, wt, L, H) : nullptr;
+    ggml_tensor * sld = (a->latent && a->s_lat_d) ? ggml_new_tensor_1d(c, GGML_TYPE_F32, 1) : nullptr;
+    ggml_tensor * slu = (a->latent && a->s_lat_u) ? ggml_new_tensor_1d(c, GGML_TYPE_F32, 1) : nullptr;
+
+    // ---- route (forward.cpp:262-271)
+    ggml_tensor * logits = ggml_mul_mat(c, rw, x);                       // [E, T]
+    if (rb) logits = ggml_add(c, logits, rb);
+    ggml_tensor * probs  = ggml_soft_max(c, logits);
+    ggml_tensor * ids    = ggml_argsort_top_k(c, probs, K);              // view [K, T] of [E, T]
+    ggml_tensor * wts    = ggml_reshape_2d(c, ggml_get_rows(c, ggml_reshape_3d(c, probs, 1, E, T), ids), K, T);
+    wts = ggml_div(c, wts, ggml_clamp(c, ggml_sum_rows(c, wts), 6.103515625e-5f, INFINITY));
+
+    // ---- optional latent down-projection
+    ggml_tensor * xe = x;
+    if (a->latent) {
+        xe = ggml_mul_mat(c, ld, x);                                     // [L, T]
+        if (sld) xe = ggml_mul(c, xe, sld);
+    }
+
+    // ---- ffn (forward.cpp:300-311)
+    ggml_tensor * input = ggml_reshape_3d(c, xe, L, 1, T);
+    ggml_tensor * gate  = scaled(c, ggml_mul_mat_id(c, wg, input, ids), sg, ids, E, T);  // [I, K, T]
+    ggml_tensor * up    = scaled(c, ggml_mul_mat_id(c, wu, input, ids), su, ids, E, T);
+    ggml_tensor * hid   = ggml_mul(c, ggml_silu(c, gate), up);
+    ggml_tensor * down  = scaled(c, ggml_mul_mat_id(c, wd, hid, ids), sd, ids, E, T);    // [L, K, T]
+    ggml_tensor * dw    = ggml_mul(c, down, ggml_reshape_3d(c, wts, 1, K, T));
+    ggml_tensor * sum   = ggml_view_2d(c, dw, L, T, dw->nb[2], 0);
+    for (int i = 1; i < K; ++i) sum = ggml_add(c, sum, ggml_view_2d(c, dw, L, T, dw->nb[2], i * dw->nb[1]));
+    ggml_tensor * moe = (K == 1) ? ggml_cont(c, sum) : sum;
+
+    ggml_tensor * out = moe;
+    if (a->latent) {
+        out = ggml_mul_mat(c, lu, moe);                                  // [H, T]
+        if (slu) out = ggml_mul(c, out, slu);
+    }
+    ggml_tensor * ids_c = ggml_cont(c, ids);
+
+    ggml_cgraph * g = ggml_new_graph_custom(c, 512, false);
+    ggml_build_forward_expand(g, out);
+    ggml_build_forward_expand(g, ids_c);
+    // observation points must not be overwritten by the allocator: mark them as outputs
+    ggml_tensor * keep[] = { logits, probs, wts, hid, down, moe, out, ids_c };
+    for (ggml_tensor * t : keep) ggml_set_output(t);
+
+    ggml_backend_t be = ggml_backend_cpu_init();
+    if (!be) { ggml_free(c); return 2; }
+    ggml_backend_cpu_set_n_threads(be, a->n_threads > 0 ? a->n_threads : 1);
+
+    // leaf tensors and graph results both live in one backend buffer
+    ggml_backend_buffer_t buf = ggml_backend_alloc_ctx_tensors(c, be);
+    if (!buf) { ggml_backend_free(be); ggml_free(c); return 3; }
+
+    auto set = [](ggml_tensor * t, const void * p) { if (t && p) ggml_backend_tensor_set(t, p, 0, ggml_nbytes(t)); };
+    set(x, a->x); set(rw, a->router_w); set(rb, a->router_bias);
+    set(wg, a->gate); set(wu, a->up); set(wd, a->down);
+    set(sg, a->s_gate); set(su, a->s_up); set(sd, a->s_down);
+    set(ld, a->lat_d); set(lu, a->lat_u); set(sld, a->s_lat_d); set(slu, a->s_lat_u);
+
+    ggml_status st = ggml_backend_graph_compute(be, g);
+    int rc = st == GGML_STATUS_SUCCESS ? 0 : 4;
+
+    if (rc == 0) {
+        auto get = [](ggml_tensor * t, void * p) { if (t && p) ggml_backend_tensor_get(t, p, 0, ggml_nbytes(t)); };
+        get(logits, a->logits); get(probs, a->probs); get(ids_c, a->ids); get(wts, a->weights);
+        get(hid, a->hidden); get(down, a->down_out); get(out, a->out);
+        if (a->moe_out) {
+            // moe may be a strided view when K > 1? no: ggml_add results are contiguous
+            ggml_backend_tensor_get(moe, a->moe_out, 0, ggml_nbytes(moe));
+        }
+    }
+
+    if (rc == 0 && a->repeats > 0) {
+        std::vector<double> ms;
+        for (int r = 0; r < a->repeats; ++r) {
+            auto t0 = std::chrono::steady_clock::now();
+            st = ggml_backend_graph_compute(be, g);
+            auto t1 = std::chrono::steady_clock::now();
+            if (st != GGML_STATUS_SUCCESS) { rc = 4; break; }
+            ms.push_back(std::chrono::duration<double, std::milli>(t1 - t0).count());
+        }
+        if (rc == 0) {
+            std::vector<double> s = ms;
+            for (size_t i = 1; i < s.size(); ++i) for (size_t j = i; j > 0 && s[j] < s[j-1]; --j) std::swap(s[j], s[j-1]);
+            if (a->ms_best)   *a->ms_best   = s.front();
+            if (a->ms_median) *a->ms_median = s[s.size() / 2];
+        }
+    }
+
+    ggml_backend_buffer_free(buf);
+    ggml_backend_free(be);
+    ggml_free(c);
+    return rc;
+}
+
+const char * ref_isa(void) {
+    static char buf[256];
+    snprintf(buf, sizeof buf, "avx=%d avx2=%d fma=%d f16c=%d avx512=%d avx_vnni=%d bmi2=%d",
+             ggml_cpu_has_avx(), ggml_cpu_has_avx2(), ggml_cpu_has_fma(), ggml_cpu_has_f16c(),
+             ggml_cpu_has_avx512(), ggml_cpu_has_avx_vnni(), ggml_cpu_has_bmi2());
+    return buf;
+}
+
+}  // extern "C"
