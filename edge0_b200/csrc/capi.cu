@@ -1,0 +1,776 @@
+// C ABI of the B200 MoE-FFN path (declared in include/edge0_b200_moe.h): context, device scratch,
+// argument validation and kernel dispatch.  No torch types, no host fallback: without a CUDA device
+// every compute entry point fails with B200MOE_ERR_NO_DEVICE / B200MOE_ERR_CUDA.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <thread>
+#include <type_traits>
+#include <vector>
+
+#include "../../include/edge0_b200_moe.h"
+#include "expert_gemv.cuh"
+#include "router.cuh"
+
+using namespace b200moe;
+
+namespace {
+
+struct Scratch {
+    uint8_t * base = nullptr;
+    size_t bytes = 0;
+};
+
+struct Plan {  // carved out of the scratch arena for one (layer shape, max_tokens)
+    int max_tokens = 0, n_embd = 0, n_in = 0, n_expert = 0, k = 0, n_ff = 0, wtype = 0;
+    float * logits = nullptr;
+    float * probs = nullptr;
+    int32_t * ids = nullptr;
+    float * wts = nullptr;
+    Groups groups{};
+    ActQuant xq{};    // [T][n_embd or n_in] (reused: latent-down input, then expert input)
+    ActQuant xlq{};   // [T][n_in] expert input when latent
+    ActQuant hq{};    // [T*k][n_ff]
+    ActQuant moq{};   // [T][n_in] latent-up input
+    float * xl = nullptr;   // [T][n_in] latent activations
+    float * hid = nullptr;  // [T*k][n_ff]
+    float * y = nullptr;    // [T*k][n_in]
+    float * moe = nullptr;  // [T][n_in]
+    float * xf = nullptr;   // [T][n_embd] fp32 copy of bf16 input (only for host entry / conversions)
+    void * xin = nullptr;   // [T][n_embd] staging for the host entry point (input dtype bytes, <= 4 B/elt)
+    float * outb = nullptr; // [T][n_embd] staging for the host entry point
+    int * one_group_ids = nullptr;  // [T] zeros: dense matvec expressed as one expert
+    size_t total = 0;
+};
+
+}  // namespace
+
+struct b200moe_ctx {
+    int device = 0;
+    int sm_count = 0;
+    Scratch scratch;
+    Plan plan;
+    int * d_err = nullptr;
+    int * h_err = nullptr;  // pinned
+    std::string last_error;
+    b200moe_counters counters{};
+    int64_t launches = 0;
+    bool timing = false;
+    struct Timed { cudaEvent_t beg, end; int kind; };
+    std::vector<Timed> timed;
+};
+
+namespace {
+
+int fail(b200moe_ctx * ctx, int code, const char * fmt, ...) {
+    if (ctx) {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        ctx->last_error = buf;
+    }
+    return code;
+}
+
+#define CUDA_TRY(ctx, expr)                                                                          \
+    do {                                                                                             \
+        cudaError_t _e = (expr);                                                                     \
+        if (_e != cudaSuccess) return fail(ctx, B200MOE_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(_e)); \
+    } while (0)
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct Carver {
+    uint8_t * base;
+    size_t off = 0;
+    template <typename T>
+    T * take(size_t n) {
+        off = align_up(off, 256);
+        T * p = base ? reinterpret_cast<T *>(base + off) : nullptr;
+        off += n * sizeof(T);
+        return p;
+    }
+    ActQuant act(size_t rows, size_t k) {
+        ActQuant a;
+        a.q = take<int8_t>(rows * k);
+        a.d = take<float>(rows * (k / 32));
+        a.bsum = take<int16_t>(rows * (k / 16));
+        return a;
+    }
+};
+
+void carve(Plan & p, uint8_t * base) {
+    Carver c{base};
+    const size_t T = p.max_tokens, E = p.n_expert, k = p.k, R = T * k;
+    const size_t kin = p.n_in, H = p.n_embd, I = p.n_ff;
+    p.logits = c.take<float>(T * E);
+    p.probs = c.take<float>(T * E);
+    p.ids = c.take<int32_t>(R);
+    p.wts = c.take<float>(R);
+    p.groups.counts = c.take<int>(std::max<size_t>(E, 1) + 8);
+    p.groups.offsets = c.take<int>(E + 1);
+    p.groups.pos = c.take<int>(std::max(R, T));
+    p.groups.perm = c.take<int>(std::max(R, T));
+    p.groups.active = c.take<int>(E);
+    p.groups.meta = c.take<int>(4);
+    p.xq = c.act(T, std::max(H, kin));
+    p.xlq = c.act(T, kin);
+    p.hq = c.act(R, I);
+    p.moq = c.act(T, kin);
+    p.xl = c.take<float>(T * kin);
+    p.hid = c.take<float>(R * I);
+    p.y = c.take<float>(R * kin);
+    p.moe = c.take<float>(T * kin);
+    p.xf = c.take<float>(T * H);
+    p.xin = c.take<float>(T * H);
+    p.outb = c.take<float>(T * H);
+    p.one_group_ids = c.take<int>(T);
+    p.total = align_up(c.off, 256);
+}
+
+bool gemv_supported(int wtype, int64_t k) {
+    if (wtype == TYPE_NVFP4) return k == 256 || k == 512 || k == 768 || k == 1024 || k == 2048 || k == 4096;
+    if (wtype == TYPE_Q3_K) return k == 256 || k == 512 || k == 768 || k == 2048;
+    return false;
+}
+
+int validate_layer(b200moe_ctx * ctx, const b200moe_layer * l) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    if (!l) return fail(ctx, B200MOE_ERR_INVALID_ARG, "layer is null");
+    if (l->n_embd <= 0 || l->n_expert <= 0 || l->n_expert_used <= 0 || l->n_ff <= 0 || l->n_latent < 0)
+        return fail(ctx, B200MOE_ERR_INVALID_ARG, "non-positive layer dimension");
+    if (l->n_expert_used > l->n_expert) return fail(ctx, B200MOE_ERR_INVALID_ARG, "n_expert_used > n_expert");
+    if (l->n_expert_used > 32) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "n_expert_used > 32");
+    if (l->n_expert > 1024 || l->n_expert % 8) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "n_expert must be a multiple of 8, at most 1024");
+    if (l->n_embd % 32) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "n_embd must be a multiple of 32");
+    if (l->wtype != TYPE_NVFP4 && l->wtype != TYPE_Q3_K) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "expert type %d has no kernel", l->wtype);
+    const int n_in = l->n_latent ? l->n_latent : l->n_embd;
+    if (!gemv_supported(l->wtype, n_in) || !gemv_supported(l->wtype, l->n_ff))
+        return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no kernel for widths n_in=%d n_ff=%d of type %d", n_in, l->n_ff, l->wtype);
+    if (l->n_latent && !gemv_supported(l->wtype, l->n_embd)) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no kernel for n_embd=%d", l->n_embd);
+    if (l->n_ff % 8 || n_in % 8) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "row counts must be multiples of 8");
+    if (!l->router_w || !l->gate || !l->up || !l->down) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null weight pointer");
+    if (l->n_latent && (!l->lat_down || !l->lat_up)) return fail(ctx, B200MOE_ERR_INVALID_ARG, "latent layer without projections");
+    const uintptr_t al = (uintptr_t) l->gate | (uintptr_t) l->up | (uintptr_t) l->down | (uintptr_t) l->lat_down | (uintptr_t) l->lat_up;
+    if (al & 15) return fail(ctx, B200MOE_ERR_INVALID_ARG, "quantised tensors must be 16-byte aligned");
+    return B200MOE_OK;
+}
+
+int ensure_plan(b200moe_ctx * ctx, int n_embd, int n_in, int n_expert, int k, int n_ff, int wtype, int tokens) {
+    Plan & p = ctx->plan;
+    if (p.max_tokens >= tokens && p.n_embd == n_embd && p.n_in == n_in && p.n_expert == n_expert && p.k == k && p.n_ff == n_ff &&
+        p.wtype == wtype && ctx->scratch.base)
+        return B200MOE_OK;
+    Plan np;
+    np.max_tokens = std::max(tokens, 1);
+    np.n_embd = n_embd; np.n_in = n_in; np.n_expert = n_expert; np.k = k; np.n_ff = n_ff; np.wtype = wtype;
+    carve(np, nullptr);
+    if (np.total > ctx->scratch.bytes) {
+        CUDA_TRY(ctx, cudaDeviceSynchronize());
+        if (ctx->scratch.base) cudaFree(ctx->scratch.base);
+        ctx->scratch.base = nullptr;
+        ctx->scratch.bytes = 0;
+        void * ptr = nullptr;
+        if (cudaMalloc(&ptr, np.total) != cudaSuccess) {
+            cudaGetLastError();
+            ctx->plan = Plan{};
+            return fail(ctx, B200MOE_ERR_ALLOC, "cannot allocate %zu bytes of device scratch", np.total);
+        }
+        ctx->scratch.base = static_cast<uint8_t *>(ptr);
+        ctx->scratch.bytes = np.total;
+    }
+    carve(np, ctx->scratch.base);
+    CUDA_TRY(ctx, cudaMemset(np.one_group_ids, 0, sizeof(int) * np.max_tokens));
+    ctx->plan = np;
+    return B200MOE_OK;
+}
+
+int check_launch(b200moe_ctx * ctx, const char * what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(ctx, B200MOE_ERR_CUDA, "%s launch: %s", what, cudaGetErrorString(e));
+    ctx->launches++;
+    return B200MOE_OK;
+}
+
+// ---- kernel dispatch -----------------------------------------------------------------------------------
+template <int WT, int K, bool DUAL, int NT>
+int launch_gemv_t(b200moe_ctx * ctx, const GemvParams & p, cudaStream_t st) {
+    constexpr int GEMV_STAGES = gemv_stages<WT, K, DUAL>();
+    constexpr size_t smem = gemv_smem_bytes<WT, K, DUAL, GEMV_STAGES>();
+    static_assert(smem <= 227 * 1024, "ring does not fit shared memory");
+    auto kern = expert_gemv_kernel<WT, K, DUAL, NT, GEMV_STAGES>;
+    static bool configured = false;  // per instantiation
+    if (!configured) {
+        CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+        configured = true;
+    }
+    b200moe_ctx::Timed tm{};
+    if (ctx->timing) {
+        CUDA_TRY(ctx, cudaEventCreate(&tm.beg));
+        CUDA_TRY(ctx, cudaEventCreate(&tm.end));
+        tm.kind = DUAL ? 0 : 1;
+        CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
+    }
+    kern<<<ctx->sm_count, GemvCfg<WT, K>::NWARPS * 32, smem, st>>>(p);
+    if (ctx->timing) {
+        CUDA_TRY(ctx, cudaEventRecord(tm.end, st));
+        ctx->timed.push_back(tm);
+    }
+    return check_launch(ctx, "expert_gemv");
+}
+
+template <int WT, int K, bool DUAL>
+int launch_gemv_k(b200moe_ctx * ctx, const GemvParams & p, int nt, cudaStream_t st) {
+    // token rows held in registers per pass: 4, or 2 where a lane owns three or more units (register budget)
+    constexpr int NTB = GemvCfg<WT, K>::UPL >= 3 ? 2 : 4;
+    if (nt <= 1) return launch_gemv_t<WT, K, DUAL, 1>(ctx, p, st);
+    return launch_gemv_t<WT, K, DUAL, NTB>(ctx, p, st);
+}
+
+template <bool DUAL>
+int launch_gemv(b200moe_ctx * ctx, int wtype, int k, const GemvParams & p, int nt, cudaStream_t st) {
+#define CASE(WT, KK) \
+    if (wtype == WT && k == KK) return launch_gemv_k<WT, KK, DUAL>(ctx, p, nt, st);
+    CASE(TYPE_NVFP4, 256) CASE(TYPE_NVFP4, 512) CASE(TYPE_NVFP4, 768) CASE(TYPE_NVFP4, 1024) CASE(TYPE_NVFP4, 2048) CASE(TYPE_NVFP4, 4096)
+    CASE(TYPE_Q3_K, 256) CASE(TYPE_Q3_K, 512) CASE(TYPE_Q3_K, 768) CASE(TYPE_Q3_K, 2048)
+#undef CASE
+    return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no expert kernel for type %d width %d", wtype, k);
+}
+
+template <typename XT>
+int launch_quantize(b200moe_ctx * ctx, const XT * src, int64_t stride, ActQuant dst, int rows, int k, int wtype, cudaStream_t st) {
+    const int kind = wtype == TYPE_Q3_K ? 1 : 0;
+    const int64_t warps = (int64_t) rows * (kind ? k / 256 : k / 32);
+    if (warps == 0) return B200MOE_OK;
+    const int blocks = (int) ((warps * 32 + 255) / 256);
+    quantize_act_kernel<XT><<<blocks, 256, 0, st>>>(src, stride, dst, rows, k, kind);
+    return check_launch(ctx, "quantize_act");
+}
+
+template <typename XT>
+int launch_logits(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, cudaStream_t st) {
+    Plan & p = ctx->plan;
+    constexpr int TT = 4;
+    const int64_t warps = (int64_t) l->n_expert * ((T + TT - 1) / TT);
+    const int blocks = (int) ((warps * 32 + 255) / 256);
+    router_logits_kernel<TT, XT><<<blocks, 256, 0, st>>>(l->router_w, l->router_bias, x, p.logits, l->n_embd, l->n_expert, T,
+                                                          p.groups.counts, l->n_expert);
+    return check_launch(ctx, "router_logits");
+}
+
+int launch_select(b200moe_ctx * ctx, const b200moe_layer * l, int T, int32_t * ids, float * wts, float * probs, bool count, cudaStream_t st) {
+    Plan & p = ctx->plan;
+    const int blocks = (T * 32 + 255) / 256;
+    const int E = l->n_expert, K = l->n_expert_used;
+    int * counts = count ? p.groups.counts : nullptr;
+#define SEL(EPL) route_select_kernel<EPL><<<blocks, 256, 0, st>>>(p.logits, E, K, T, ids, wts, probs, counts, p.groups.pos)
+    if (E <= 32) SEL(1);
+    else if (E <= 64) SEL(2);
+    else if (E <= 128) SEL(4);
+    else if (E <= 256) SEL(8);
+    else if (E <= 512) SEL(16);
+    else SEL(32);
+#undef SEL
+    return check_launch(ctx, "route_select");
+}
+
+int launch_group(b200moe_ctx * ctx, const int32_t * ids, int E, int rows, cudaStream_t st) {
+    Plan & p = ctx->plan;
+    const size_t sh = (size_t) (2 * E + 1) * sizeof(int);
+    group_scan_kernel<<<1, 1024, sh, st>>>(p.groups, ids, E, rows, ctx->d_err);
+    return check_launch(ctx, "group_scan");
+}
+
+GemvParams gemv_params(b200moe_ctx * ctx, const void * w0, const void * w1, const float * s0, const float * s1, ActQuant act, float * out,
+                       int n_out, int n_ids, int ne11, int n_as) {
+    Plan & p = ctx->plan;
+    GemvParams g{};
+    g.w0 = static_cast<const uint8_t *>(w0);
+    g.w1 = static_cast<const uint8_t *>(w1);
+    g.scale0 = s0;
+    g.scale1 = s1;
+    g.act = act;
+    g.offsets = p.groups.offsets;
+    g.perm = p.groups.perm;
+    g.active = p.groups.active;
+    g.meta = p.groups.meta;
+    g.out = out;
+    g.n_out = n_out;
+    g.n_ids = n_ids;
+    g.ne11 = ne11;
+    g.n_as = n_as;
+    g.err = ctx->d_err;
+    return g;
+}
+
+int tokens_per_pass(int rows, int n_as) { return rows <= n_as ? (rows <= 32 ? 1 : 4) : 4; }
+
+__global__ void scale_rows_kernel(float * v, const float * s, size_t n) {
+    const size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) v[i] = __fmul_rn(v[i], s[0]);
+}
+
+__global__ void bf16_to_f32_kernel(const __nv_bfloat16 * src, float * dst, size_t n) {
+    const size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = __bfloat162float(src[i]);
+}
+
+// Dense quantised matvec y[T][n_out] = W[n_out][k] . x[T][k], as one "expert" that every row is routed to.
+int dense_matvec(b200moe_ctx * ctx, int wtype, const void * w, const float * scale, const float * x, ActQuant xq, int k, int n_out, int T,
+                 float * y, cudaStream_t st) {
+    Plan & p = ctx->plan;
+    int rc = launch_quantize<float>(ctx, x, k, xq, T, k, wtype, st);
+    if (rc) return rc;
+    CUDA_TRY(ctx, cudaMemsetAsync(p.groups.counts, 0, sizeof(int) * 8, st));
+    count_ids_kernel<<<(T + 255) / 256, 256, 0, st>>>(p.one_group_ids, 1, 1, T, 1, p.groups.perm /*scratch: compact ids*/, p.groups.counts,
+                                                      p.groups.pos, ctx->d_err);
+    if ((rc = check_launch(ctx, "count_ids"))) return rc;
+    // perm is about to be overwritten by the scan; the compact ids are all zero, so read them from one_group_ids
+    if ((rc = launch_group(ctx, p.one_group_ids, 1, T, st))) return rc;
+    GemvParams g = gemv_params(ctx, w, nullptr, nullptr, nullptr, xq, y, n_out, 1, 1, 1);
+    if ((rc = launch_gemv<false>(ctx, wtype, k, g, 4, st))) return rc;
+    if (scale) {
+        const size_t n = (size_t) T * n_out;
+        scale_rows_kernel<<<(unsigned) ((n + 255) / 256), 256, 0, st>>>(y, scale, n);
+        if ((rc = check_launch(ctx, "scale_rows"))) return rc;
+    }
+    return B200MOE_OK;
+}
+
+int read_device_error(b200moe_ctx * ctx, cudaStream_t st) {
+    CUDA_TRY(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(ctx, cudaStreamSynchronize(st));
+    if (*ctx->h_err != 0) {
+        const int code = *ctx->h_err;
+        cudaMemsetAsync(ctx->d_err, 0, sizeof(int), st);
+        return fail(ctx, B200MOE_ERR_DEVICE_CHECK, "device check failed with code %d (1 barrier wait ran out, 2 expert id out of range, 3 shape)", code);
+    }
+    return B200MOE_OK;
+}
+
+template <typename XT>
+int route_impl(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, int32_t * ids, float * wts, const b200moe_observe * ob,
+               bool count, cudaStream_t st) {
+    Plan & p = ctx->plan;
+    int rc = launch_logits<XT>(ctx, l, x, T, st);
+    if (rc) return rc;
+    float * probs = (ob && ob->ffn_moe_probs) ? ob->ffn_moe_probs : nullptr;
+    if ((rc = launch_select(ctx, l, T, ids, wts, probs, count, st))) return rc;
+    if (ob && ob->ffn_moe_logits)
+        CUDA_TRY(ctx, cudaMemcpyAsync(ob->ffn_moe_logits, p.logits, sizeof(float) * (size_t) T * l->n_expert, cudaMemcpyDeviceToDevice, st));
+    return B200MOE_OK;
+}
+
+// experts on activations xe [T][n_in] (fp32), routing already grouped in the plan
+int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const int32_t * ids, const float * wts, int T, float * out,
+                 const b200moe_observe * ob, cudaStream_t st) {
+    Plan & p = ctx->plan;
+    const int n_in = l->n_latent ? l->n_latent : l->n_embd;
+    const int k = l->n_expert_used, rows = T * k;
+    const int nt = tokens_per_pass(rows, l->n_expert);
+    int rc;
+    GemvParams gu = gemv_params(ctx, l->gate, l->up, l->gate_scale, l->up_scale, xq, p.hid, l->n_ff, k, 1, l->n_expert);
+    if ((rc = launch_gemv<true>(ctx, l->wtype, n_in, gu, nt, st))) return rc;
+    if ((rc = launch_quantize<float>(ctx, p.hid, l->n_ff, p.hq, rows, l->n_ff, l->wtype, st))) return rc;
+    GemvParams dn = gemv_params(ctx, l->down, nullptr, l->down_scale, nullptr, p.hq, p.y, n_in, k, k, l->n_expert);
+    if ((rc = launch_gemv<false>(ctx, l->wtype, l->n_ff, dn, nt, st))) return rc;
+    dim3 grid((n_in / 4 + 255) / 256, T);
+    combine_kernel<<<grid, 256, 0, st>>>(p.y, wts, out, n_in, k, T);
+    if ((rc = check_launch(ctx, "combine"))) return rc;
+    if (ob && ob->ffn_moe_hidden)
+        CUDA_TRY(ctx, cudaMemcpyAsync(ob->ffn_moe_hidden, p.hid, sizeof(float) * (size_t) rows * l->n_ff, cudaMemcpyDeviceToDevice, st));
+    if (ob && ob->ffn_moe_down)
+        CUDA_TRY(ctx, cudaMemcpyAsync(ob->ffn_moe_down, p.y, sizeof(float) * (size_t) rows * n_in, cudaMemcpyDeviceToDevice, st));
+    (void) ids;
+    return B200MOE_OK;
+}
+
+void account(b200moe_ctx * ctx, const b200moe_layer * l, int T) {
+    ctx->counters.tokens += T;
+    ctx->counters.kernel_launches = ctx->launches;
+}
+
+template <typename XT>
+int layer_impl(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, float * out, const b200moe_observe * ob, cudaStream_t st) {
+    Plan & p = ctx->plan;
+    const int k = l->n_expert_used;
+    int rc = route_impl<XT>(ctx, l, x, T, p.ids, p.wts, ob, true, st);
+    if (rc) return rc;
+    if (!l->n_latent && (rc = launch_group(ctx, p.ids, l->n_expert, T * k, st))) return rc;
+    if (ob && ob->ffn_moe_topk) CUDA_TRY(ctx, cudaMemcpyAsync(ob->ffn_moe_topk, p.ids, sizeof(int32_t) * (size_t) T * k, cudaMemcpyDeviceToDevice, st));
+    if (ob && ob->ffn_moe_weights_norm)
+        CUDA_TRY(ctx, cudaMemcpyAsync(ob->ffn_moe_weights_norm, p.wts, sizeof(float) * (size_t) T * k, cudaMemcpyDeviceToDevice, st));
+
+    if (!l->n_latent) {
+        if ((rc = launch_quantize<XT>(ctx, x, l->n_embd, p.xq, T, l->n_embd, l->wtype, st))) return rc;
+        rc = experts_impl(ctx, l, p.xq, p.ids, p.wts, T, out, ob, st);
+        account(ctx, l, T);
+        return rc;
+    }
+    // latent: routing was grouped into the plan's Groups, but the dense projections reuse the same Groups
+    // buffers, so run the down-projection first and regroup afterwards.
+    const float * xf32;
+    if (std::is_same<XT, float>::value) {
+        xf32 = reinterpret_cast<const float *>(x);
+    } else {
+        const size_t n = (size_t) T * l->n_embd;
+        bf16_to_f32_kernel<<<(unsigned) ((n + 255) / 256), 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16 *>(x), p.xf, n);
+        if ((rc = check_launch(ctx, "bf16_to_f32"))) return rc;
+        xf32 = p.xf;
+    }
+    if ((rc = dense_matvec(ctx, l->wtype, l->lat_down, l->lat_down_scale, xf32, p.xq, l->n_embd, l->n_latent, T, p.xl, st))) return rc;
+    // regroup the expert routing
+    CUDA_TRY(ctx, cudaMemsetAsync(p.groups.counts, 0, sizeof(int) * l->n_expert, st));
+    count_ids_kernel<<<(T * k + 255) / 256, 256, 0, st>>>(p.ids, k, k, T, l->n_expert, p.groups.perm, p.groups.counts, p.groups.pos, ctx->d_err);
+    if ((rc = check_launch(ctx, "count_ids"))) return rc;
+    if ((rc = launch_group(ctx, p.ids, l->n_expert, T * k, st))) return rc;
+    if ((rc = launch_quantize<float>(ctx, p.xl, l->n_latent, p.xlq, T, l->n_latent, l->wtype, st))) return rc;
+    if ((rc = experts_impl(ctx, l, p.xlq, p.ids, p.wts, T, p.moe, ob, st))) return rc;
+    rc = dense_matvec(ctx, l->wtype, l->lat_up, l->lat_up_scale, p.moe, p.moq, l->n_latent, l->n_embd, T, out, st);
+    account(ctx, l, T);
+    return rc;
+}
+
+}  // namespace
+
+// ============================================================================================ C ABI
+
+extern "C" {
+
+const char * b200moe_status_string(int s) {
+    switch (s) {
+        case B200MOE_OK: return "ok";
+        case B200MOE_ERR_INVALID_ARG: return "invalid argument";
+        case B200MOE_ERR_UNSUPPORTED: return "unsupported type or shape";
+        case B200MOE_ERR_ALLOC: return "device allocation failed";
+        case B200MOE_ERR_CUDA: return "CUDA error";
+        case B200MOE_ERR_DEVICE_CHECK: return "device-side check failed";
+        case B200MOE_ERR_NO_DEVICE: return "no CUDA device";
+        default: return "unknown status";
+    }
+}
+
+int b200moe_create(int device, b200moe_ctx ** out) {
+    if (!out) return B200MOE_ERR_INVALID_ARG;
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) { cudaGetLastError(); return B200MOE_ERR_NO_DEVICE; }
+    if (device < 0 || device >= n) return B200MOE_ERR_INVALID_ARG;
+    if (cudaSetDevice(device) != cudaSuccess) { cudaGetLastError(); return B200MOE_ERR_CUDA; }
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { cudaGetLastError(); return B200MOE_ERR_CUDA; }
+    if (prop.major != 10) return B200MOE_ERR_UNSUPPORTED;  // kernels are built for sm_100a only
+    auto * ctx = new b200moe_ctx();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    if (cudaMalloc(&ctx->d_err, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_err, 0, sizeof(int)) != cudaSuccess ||
+        cudaMallocHost(&ctx->h_err, sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        delete ctx;
+        return B200MOE_ERR_ALLOC;
+    }
+    *ctx->h_err = 0;
+    *out = ctx;
+    return B200MOE_OK;
+}
+
+void b200moe_destroy(b200moe_ctx * ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaDeviceSynchronize();
+    if (ctx->scratch.base) cudaFree(ctx->scratch.base);
+    if (ctx->d_err) cudaFree(ctx->d_err);
+    if (ctx->h_err) cudaFreeHost(ctx->h_err);
+    delete ctx;
+}
+
+const char * b200moe_last_error(const b200moe_ctx * ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
+
+int b200moe_device_memory(int device, size_t * free_bytes, size_t * total_bytes) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) { cudaGetLastError(); return B200MOE_ERR_NO_DEVICE; }
+    if (device < 0 || device >= n || !free_bytes || !total_bytes) return B200MOE_ERR_INVALID_ARG;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(device);
+    cudaError_t e = cudaMemGetInfo(free_bytes, total_bytes);
+    cudaSetDevice(prev);
+    return e == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
+int b200moe_get_counters(const b200moe_ctx * ctx, b200moe_counters * out) {
+    if (!ctx || !out) return B200MOE_ERR_INVALID_ARG;
+    *out = ctx->counters;
+    out->kernel_launches = ctx->launches;
+    return B200MOE_OK;
+}
+
+int b200moe_enable_kernel_timing(b200moe_ctx * ctx, int enable) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    ctx->timing = enable != 0;
+    return B200MOE_OK;
+}
+
+int b200moe_kernel_times(b200moe_ctx * ctx, int64_t launches[2], double total_ms[2]) {
+    if (!ctx || !launches || !total_ms) return B200MOE_ERR_INVALID_ARG;
+    launches[0] = launches[1] = 0;
+    total_ms[0] = total_ms[1] = 0.0;
+    for (auto & t : ctx->timed) {
+        float ms = 0.0f;
+        CUDA_TRY(ctx, cudaEventSynchronize(t.end));
+        CUDA_TRY(ctx, cudaEventElapsedTime(&ms, t.beg, t.end));
+        launches[t.kind] += 1;
+        total_ms[t.kind] += ms;
+        cudaEventDestroy(t.beg);
+        cudaEventDestroy(t.end);
+    }
+    ctx->timed.clear();
+    return B200MOE_OK;
+}
+
+int b200moe_synchronize(b200moe_ctx * ctx, void * stream) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    return read_device_error(ctx, static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_reserve(b200moe_ctx * ctx, const b200moe_layer * l, int32_t max_tokens) {
+    int rc = validate_layer(ctx, l);
+    if (rc) return rc;
+    if (max_tokens <= 0) return fail(ctx, B200MOE_ERR_INVALID_ARG, "max_tokens must be positive");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return ensure_plan(ctx, l->n_embd, l->n_latent ? l->n_latent : l->n_embd, l->n_expert, l->n_expert_used, l->n_ff, l->wtype, max_tokens);
+}
+
+int64_t b200moe_row_size(int type, int64_t n) {
+    if (n < 0) return -1;
+    if (type == TYPE_NVFP4 && n % 64) return -1;
+    if (type == TYPE_Q3_K && n % 256) return -1;
+    return weight_row_bytes(type, n);
+}
+
+// ---- host-side format helpers (ggml-quants.c:337-348, 384-417 for the quantiser; :589-612, :1305-1353 dequantisers)
+static const int8_t k_fp4_values[16] = { 0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12 };
+
+static uint8_t fp32_to_ue4m3(float x) {
+    if (!(x > 0.0f)) return 0;
+    if (x > 448.0f) x = 448.0f;
+    uint32_t bits;
+    memcpy(&bits, &x, 4);
+    const int fexp = (int) ((bits >> 23) & 0xff) - 127, fman = (bits >> 20) & 7;
+    int ue = fexp + 7;
+    if (ue <= 0) {
+        int man = (int) (x * 512.0f + 0.5f);
+        if (man > 7) man = 7;
+        return man < 1 ? 0 : (uint8_t) man;
+    }
+    if (ue >= 15) return 0x7e;
+    int um = fman + ((bits >> 19) & 1);
+    if (um > 7) { um = 0; if (++ue >= 15) return 0x7e; }
+    return (uint8_t) ((ue << 3) | um);
+}
+
+static void quantize_row_nvfp4(const float * x, uint8_t * y, int64_t k) {
+    for (int64_t b = 0; b < k / 64; ++b) {
+        uint8_t * blk = y + b * 36;
+        for (int s = 0; s < 4; ++s) {
+            const float * xb = x + b * 64 + s * 16;
+            float amax = 0.0f;
+            for (int j = 0; j < 16; ++j) amax = std::max(amax, std::fabs(xb[j]));
+            const uint8_t ue = fp32_to_ue4m3(amax / 6.0f);
+            blk[s] = ue;
+            const float d = ue4m3_half_to_f32(ue);
+            auto best = [&](float v) {
+                int bi = 0;
+                float be = std::fabs(k_fp4_values[0] * d - v);
+                for (int i = 1; i < 16; ++i) {
+                    const float err = std::fabs(k_fp4_values[i] * d - v);
+                    if (err < be) { bi = i; be = err; }
+                }
+                return (uint8_t) bi;
+            };
+            for (int j = 0; j < 8; ++j) blk[4 + s * 8 + j] = (uint8_t) (best(xb[j]) | (best(xb[8 + j]) << 4));
+        }
+    }
+}
+
+int b200moe_quantize_nvfp4_host(const float * src, void * dst, int64_t nrows, int64_t n_per_row) {
+    if (!src || !dst || nrows < 0 || n_per_row <= 0 || n_per_row % 64) return B200MOE_ERR_INVALID_ARG;
+    const int64_t rs = n_per_row / 64 * 36;
+    const unsigned hw = std::max(1u, std::thread::hardware_concurrency());
+    const int nthreads = (int) std::min<int64_t>(hw, std::max<int64_t>(1, nrows / 64));
+    std::vector<std::thread> th;
+    for (int t = 0; t < nthreads; ++t)
+        th.emplace_back([=] {
+            for (int64_t r = nrows * t / nthreads; r < nrows * (t + 1) / nthreads; ++r)
+                quantize_row_nvfp4(src + r * n_per_row, static_cast<uint8_t *>(dst) + r * rs, n_per_row);
+        });
+    for (auto & t : th) t.join();
+    return B200MOE_OK;
+}
+
+int b200moe_dequantize_host(int type, const void * src, float * dst, int64_t nrows, int64_t n_per_row) {
+    if (!src || !dst || nrows < 0 || n_per_row <= 0) return B200MOE_ERR_INVALID_ARG;
+    const uint8_t * s = static_cast<const uint8_t *>(src);
+    if (type == TYPE_NVFP4) {
+        if (n_per_row % 64) return B200MOE_ERR_INVALID_ARG;
+        for (int64_t b = 0; b < nrows * n_per_row / 64; ++b) {
+            const uint8_t * blk = s + b * 36;
+            for (int sb = 0; sb < 4; ++sb) {
+                const float d = ue4m3_half_to_f32(blk[sb]);
+                for (int j = 0; j < 8; ++j) {
+                    dst[b * 64 + sb * 16 + j] = k_fp4_values[blk[4 + sb * 8 + j] & 15] * d;
+                    dst[b * 64 + sb * 16 + j + 8] = k_fp4_values[blk[4 + sb * 8 + j] >> 4] * d;
+                }
+            }
+        }
+        return B200MOE_OK;
+    }
+    if (type == TYPE_Q3_K) {
+        if (n_per_row % 256) return B200MOE_ERR_INVALID_ARG;
+        for (int64_t b = 0; b < nrows * n_per_row / 256; ++b) {
+            const uint8_t * blk = s + b * 110;
+            uint32_t sw[3], sc[4];
+            memcpy(sw, blk + 96, 12);
+            q3k_unpack_scales(sw[0], sw[1], sw[2], sc);
+            uint16_t hb;
+            memcpy(&hb, blk + 108, 2);
+            // half -> float on the host
+            const uint32_t sign = (uint32_t) (hb & 0x8000) << 16, ex = (hb >> 10) & 31, mn = hb & 1023;
+            float d;
+            if (ex == 0) d = std::ldexp((float) mn, -24);
+            else if (ex == 31) d = INFINITY;
+            else { uint32_t u = ((ex + 112) << 23) | (mn << 13); memcpy(&d, &u, 4); }
+            if (sign) d = -d;
+            for (int idx = 0; idx < 256; ++idx) {
+                const int half = idx >> 7, shift = (idx >> 5) & 3, l = idx & 31;
+                const int lo = (blk[32 + 32 * half + l] >> (2 * shift)) & 3;
+                const int hbit = (blk[l] >> (4 * half + shift)) & 1;
+                const float dl = d * (float) q3k_scale_at(sc, idx >> 4);
+                dst[b * 256 + idx] = dl * (float) (lo - (hbit ? 0 : 4));
+            }
+        }
+        return B200MOE_OK;
+    }
+    return B200MOE_ERR_UNSUPPORTED;
+}
+
+// ---- compute
+
+int b200moe_route(b200moe_ctx * ctx, const b200moe_layer * l, const void * x, int x_type, int32_t T, int32_t * ids, float * weights,
+                  const b200moe_observe * ob, void * stream) {
+    int rc = validate_layer(ctx, l);
+    if (rc) return rc;
+    if (T == 0) return B200MOE_OK;
+    if (!x || !ids || !weights || T < 0) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer or negative token count");
+    if (x_type != TYPE_F32 && x_type != TYPE_BF16) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "activations must be F32 or BF16");
+    if (T == 0) return B200MOE_OK;
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    if ((rc = b200moe_reserve(ctx, l, T))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (x_type == TYPE_F32) return route_impl<float>(ctx, l, static_cast<const float *>(x), T, ids, weights, ob, false, st);
+    return route_impl<__nv_bfloat16>(ctx, l, static_cast<const __nv_bfloat16 *>(x), T, ids, weights, ob, false, st);
+}
+
+int b200moe_mul_mat_id(b200moe_ctx * ctx, int wtype, const void * as, int64_t ne00, int64_t ne01, int64_t n_as, const float * b, int64_t ne11,
+                       const int32_t * ids, int64_t n_ids, int64_t ids_nb1, int64_t T, float * dst, void * stream) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    if (T == 0) return B200MOE_OK;
+    if (!as || !b || !ids || !dst) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer");
+    if (ne00 <= 0 || ne01 <= 0 || n_as <= 0 || ne11 <= 0 || n_ids <= 0 || T < 0) return fail(ctx, B200MOE_ERR_INVALID_ARG, "non-positive size");
+    if (n_ids > 32) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "more than 32 ids per token");
+    if (n_ids % ne11) return fail(ctx, B200MOE_ERR_INVALID_ARG, "ids->ne[0] must be a multiple of b->ne[1]");  // ggml.c:3406
+    if (ids_nb1 % 4 || ids_nb1 < n_ids * 4) return fail(ctx, B200MOE_ERR_INVALID_ARG, "bad ids row stride");
+    if ((uintptr_t) as & 15) return fail(ctx, B200MOE_ERR_INVALID_ARG, "expert tensor must be 16-byte aligned");
+    if (!gemv_supported(wtype, ne00) || ne01 % 8 || n_as > 1024) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no kernel for type %d, K=%lld", wtype, (long long) ne00);
+    if (T == 0) return B200MOE_OK;
+    if (T * n_ids > (1 << 30)) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "too many routed rows");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // plan: treat as a layer with n_embd = n_in = ne00, rows = T * max(n_ids, ne11)
+    const int k = (int) n_ids;
+    int rc = ensure_plan(ctx, (int) ne00, (int) ne00, (int) std::max<int64_t>(n_as, 8), k, (int) ne00, wtype, (int) T);
+    if (rc) return rc;
+    Plan & p = ctx->plan;
+    const int rows = (int) (T * n_ids);
+    // activations: T*ne11 rows of ne00; plan.hq holds T*k rows of width n_ff (= ne00 here), ne11 <= k
+    if ((rc = launch_quantize<float>(ctx, b, ne00, p.hq, (int) (T * ne11), (int) ne00, wtype, st))) return rc;
+    CUDA_TRY(ctx, cudaMemsetAsync(p.groups.counts, 0, sizeof(int) * n_as, st));
+    count_ids_kernel<<<(rows + 255) / 256, 256, 0, st>>>(ids, ids_nb1 / 4, (int) n_ids, (int) T, (int) n_as, p.ids, p.groups.counts, p.groups.pos, ctx->d_err);
+    if ((rc = check_launch(ctx, "count_ids"))) return rc;
+    if ((rc = launch_group(ctx, p.ids, (int) n_as, rows, st))) return rc;
+    GemvParams g = gemv_params(ctx, as, nullptr, nullptr, nullptr, p.hq, dst, (int) ne01, (int) n_ids, (int) ne11, (int) n_as);
+    return launch_gemv<false>(ctx, wtype, (int) ne00, g, tokens_per_pass(rows, (int) n_as), st);
+}
+
+int b200moe_ffn(b200moe_ctx * ctx, const b200moe_layer * l, const void * x, int x_type, int32_t T, const int32_t * ids, const float * weights,
+                float * out, const b200moe_observe * ob, void * stream) {
+    int rc = validate_layer(ctx, l);
+    if (rc) return rc;
+    if (T == 0) return B200MOE_OK;
+    if (!x || !ids || !weights || !out || T < 0) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer or negative token count");
+    if (x_type != TYPE_F32 && x_type != TYPE_BF16) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "activations must be F32 or BF16");
+    if (T == 0) return B200MOE_OK;
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    if ((rc = b200moe_reserve(ctx, l, T))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    Plan & p = ctx->plan;
+    const int n_in = l->n_latent ? l->n_latent : l->n_embd, k = l->n_expert_used;
+    CUDA_TRY(ctx, cudaMemsetAsync(p.groups.counts, 0, sizeof(int) * l->n_expert, st));
+    count_ids_kernel<<<(T * k + 255) / 256, 256, 0, st>>>(ids, k, k, T, l->n_expert, p.ids, p.groups.counts, p.groups.pos, ctx->d_err);
+    if ((rc = check_launch(ctx, "count_ids"))) return rc;
+    if ((rc = launch_group(ctx, p.ids, l->n_expert, T * k, st))) return rc;
+    if (x_type == TYPE_F32) rc = launch_quantize<float>(ctx, static_cast<const float *>(x), n_in, p.xq, T, n_in, l->wtype, st);
+    else rc = launch_quantize<__nv_bfloat16>(ctx, static_cast<const __nv_bfloat16 *>(x), n_in, p.xq, T, n_in, l->wtype, st);
+    if (rc) return rc;
+    rc = experts_impl(ctx, l, p.xq, p.ids, weights, T, out, ob, st);
+    account(ctx, l, T);
+    return rc;
+}
+
+int b200moe_layer_forward(b200moe_ctx * ctx, const b200moe_layer * l, const void * x, int x_type, int32_t T, float * out,
+                          const b200moe_observe * ob, void * stream) {
+    int rc = validate_layer(ctx, l);
+    if (rc) return rc;
+    if (T == 0) return B200MOE_OK;
+    if (!x || !out || T < 0) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer or negative token count");
+    if (x_type != TYPE_F32 && x_type != TYPE_BF16) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "activations must be F32 or BF16");
+    if (T == 0) return B200MOE_OK;
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    if ((rc = b200moe_reserve(ctx, l, T))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (x_type == TYPE_F32) return layer_impl<float>(ctx, l, static_cast<const float *>(x), T, out, ob, st);
+    return layer_impl<__nv_bfloat16>(ctx, l, static_cast<const __nv_bfloat16 *>(x), T, out, ob, st);
+}
+
+int b200moe_layer_forward_host(b200moe_ctx * ctx, const b200moe_layer * l, const void * x_host, int x_type, int32_t T, float * out_host,
+                               int32_t * ids_host, float * weights_host, void * stream) {
+    int rc = validate_layer(ctx, l);
+    if (rc) return rc;
+    if (T == 0) return B200MOE_OK;
+    if (!x_host || !out_host || T < 0) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer or negative token count");
+    if (x_type != TYPE_F32 && x_type != TYPE_BF16) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "activations must be F32 or BF16");
+    if (T == 0) return B200MOE_OK;
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    if ((rc = b200moe_reserve(ctx, l, T))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    Plan & p = ctx->plan;
+    const size_t xbytes = (size_t) T * l->n_embd * (x_type == TYPE_F32 ? 4 : 2);
+    CUDA_TRY(ctx, cudaMemcpyAsync(p.xin, x_host, xbytes, cudaMemcpyHostToDevice, st));
+    if (x_type == TYPE_F32) rc = layer_impl<float>(ctx, l, static_cast<const float *>(p.xin), T, p.outb, nullptr, st);
+    else rc = layer_impl<__nv_bfloat16>(ctx, l, static_cast<const __nv_bfloat16 *>(p.xin), T, p.outb, nullptr, st);
+    if (rc) return rc;
+    CUDA_TRY(ctx, cudaMemcpyAsync(out_host, p.outb, sizeof(float) * (size_t) T * l->n_embd, cudaMemcpyDeviceToHost, st));
+    if (ids_host) CUDA_TRY(ctx, cudaMemcpyAsync(ids_host, p.ids, sizeof(int32_t) * (size_t) T * l->n_expert_used, cudaMemcpyDeviceToHost, st));
+    if (weights_host) CUDA_TRY(ctx, cudaMemcpyAsync(weights_host, p.wts, sizeof(float) * (size_t) T * l->n_expert_used, cudaMemcpyDeviceToHost, st));
+    return read_device_error(ctx, st);
+}
+
+}  // extern "C"

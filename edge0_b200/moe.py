@@ -1,0 +1,225 @@
+"""Host-side mirror of the reference's operator interface for the quantised MoE FFN.
+
+Names follow edge0-infer: `route` and `ffn` are Builder::route / Builder::ffn
+(edge0-infer/src/models/edge0_35b/forward.cpp:262-271, 300-311), `mul_mat_id` is ggml_mul_mat_id
+(third_party/ggml/src/ggml.c:3392-3416).  Tensors are torch CUDA tensors used purely as device memory;
+all arithmetic happens in libedge0_b200.so through the C ABI.  Shapes are written row-major, i.e. the
+reverse of ggml's ne[] order: x [T, n_embd], ids [T, k], expert tensors [n_expert, n_out, row_bytes].
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import capi
+from .capi import TYPE_BF16, TYPE_F32, TYPE_NVFP4, TYPE_Q3_K, B200MoeError, Layer, Observe
+
+TYPE_BY_NAME = {"q3_k": TYPE_Q3_K, "nvfp4": TYPE_NVFP4}
+
+
+def row_size(wtype: int, n: int) -> int:
+    r = capi.load().b200moe_row_size(wtype, n)
+    if r < 0:
+        raise ValueError(f"width {n} is not a whole number of blocks of type {wtype}")
+    return int(r)
+
+
+def quantize_nvfp4(w: np.ndarray) -> np.ndarray:
+    """float32 [..., n] -> ggml block_nvfp4 bytes [..., n/64*36] (quantize_row_nvfp4_ref, ggml-quants.c:384-417)."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    n = w.shape[-1]
+    out = np.empty(w.shape[:-1] + (row_size(TYPE_NVFP4, n),), dtype=np.uint8)
+    rc = capi.load().b200moe_quantize_nvfp4_host(w.ctypes.data, out.ctypes.data, w.size // n, n)
+    if rc:
+        raise B200MoeError(rc, "quantize_nvfp4_host")
+    return out
+
+
+def dequantize(wtype: int, q: np.ndarray, n: int) -> np.ndarray:
+    q = np.ascontiguousarray(q, dtype=np.uint8)
+    rows = q.size // row_size(wtype, n)
+    out = np.empty(q.shape[:-1] + (n,), dtype=np.float32)
+    rc = capi.load().b200moe_dequantize_host(wtype, q.ctypes.data, out.ctypes.data, rows, n)
+    if rc:
+        raise B200MoeError(rc, "dequantize_host")
+    return out
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _x_type(x: torch.Tensor) -> int:
+    if x.dtype == torch.float32:
+        return TYPE_F32
+    if x.dtype == torch.bfloat16:
+        return TYPE_BF16
+    raise TypeError("activations must be float32 or bfloat16")
+
+
+class Context:
+    """One per GPU and stream of work (reference: one ggml backend instance, one graph in flight)."""
+
+    def __init__(self, device: int = 0):
+        self.lib = capi.load()
+        h = C.c_void_p()
+        rc = self.lib.b200moe_create(device, C.byref(h))
+        if rc:
+            raise B200MoeError(rc, "b200moe_create: " + self.lib.b200moe_status_string(rc).decode())
+        self.handle = h
+        self.device = device
+
+    def close(self):
+        if self.handle:
+            self.lib.b200moe_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def check(self, rc: int):
+        if rc:
+            raise B200MoeError(rc, self.lib.b200moe_last_error(self.handle).decode())
+
+    def synchronize(self):
+        self.check(self.lib.b200moe_synchronize(self.handle, self._stream()))
+
+    def _stream(self):
+        return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def launches(self) -> int:
+        c = capi.Counters()
+        self.check(self.lib.b200moe_get_counters(self.handle, C.byref(c)))
+        return int(c.kernel_launches)
+
+    def enable_kernel_timing(self, on: bool = True):
+        self.check(self.lib.b200moe_enable_kernel_timing(self.handle, int(on)))
+
+    def kernel_times(self):
+        """[(launches, total_ms) for the fused gate/up kernel, (launches, total_ms) for the single-matrix kernel]; clears the record."""
+        n = (C.c_int64 * 2)()
+        ms = (C.c_double * 2)()
+        self.check(self.lib.b200moe_kernel_times(self.handle, n, ms))
+        return [(int(n[0]), float(ms[0])), (int(n[1]), float(ms[1]))]
+
+    def mul_mat_id(self, wtype: int, experts: torch.Tensor, b: torch.Tensor, ids: torch.Tensor, ne00: int) -> torch.Tensor:
+        """experts uint8 [n_as, ne01, row_bytes]; b float32 [T, ne11, ne00]; ids int32 [T, n_ids] (may be a
+        column slice of a wider tensor) -> float32 [T, n_ids, ne01]."""
+        n_as, ne01, _ = experts.shape
+        T, ne11, _ = b.shape
+        n_ids = ids.shape[1]
+        dst = torch.empty((T, n_ids, ne01), dtype=torch.float32, device=b.device)
+        self.check(self.lib.b200moe_mul_mat_id(self.handle, wtype, _ptr(experts), ne00, ne01, n_as, _ptr(b), ne11, _ptr(ids), n_ids,
+                                               ids.stride(0) * 4 if T > 0 else n_ids * 4, T, _ptr(dst), self._stream()))
+        return dst
+
+
+@dataclass
+class Observed:
+    logits: torch.Tensor
+    probs: torch.Tensor
+    topk: torch.Tensor
+    weights_norm: torch.Tensor
+    hidden: torch.Tensor
+    down: torch.Tensor
+
+
+class MoeLayer:
+    """Weights of one MoE FFN layer on one GPU plus the calls the reference graph makes on them."""
+
+    def __init__(self, ctx: Context, *, wtype: int, top_k: int, router_w, gate, up, down, router_bias=None, gate_scale=None,
+                 up_scale=None, down_scale=None, lat_down=None, lat_up=None, lat_down_scale=None, lat_up_scale=None):
+        dev = torch.device("cuda", ctx.device)
+
+        def put(a, dtype):
+            if a is None:
+                return None
+            if isinstance(a, torch.Tensor):
+                return a.to(device=dev, dtype=dtype).contiguous()
+            return torch.from_numpy(np.ascontiguousarray(a)).to(device=dev, dtype=dtype).contiguous()
+
+        self.ctx, self.wtype, self.top_k = ctx, wtype, top_k
+        self.router_w = put(router_w, torch.float32)
+        self.router_bias = put(router_bias, torch.float32)
+        self.gate, self.up, self.down = put(gate, torch.uint8), put(up, torch.uint8), put(down, torch.uint8)
+        self.gate_scale, self.up_scale, self.down_scale = (put(s, torch.float32) for s in (gate_scale, up_scale, down_scale))
+        self.lat_down, self.lat_up = put(lat_down, torch.uint8), put(lat_up, torch.uint8)
+        self.lat_down_scale, self.lat_up_scale = put(lat_down_scale, torch.float32), put(lat_up_scale, torch.float32)
+        self.n_expert, self.n_embd = self.router_w.shape
+        self.n_ff = self.gate.shape[1]
+        self.n_latent = 0 if self.lat_down is None else self.lat_down.shape[0]
+        self.n_in = self.n_latent or self.n_embd
+        if self.gate.shape != (self.n_expert, self.n_ff, row_size(wtype, self.n_in)):
+            raise ValueError(f"gate tensor has shape {tuple(self.gate.shape)}")
+        if self.down.shape != (self.n_expert, self.n_in, row_size(wtype, self.n_ff)):
+            raise ValueError(f"down tensor has shape {tuple(self.down.shape)}")
+        self.desc = Layer(n_embd=self.n_embd, n_latent=self.n_latent, n_expert=self.n_expert, n_expert_used=top_k, n_ff=self.n_ff,
+                          wtype=wtype)
+        for name in ("router_w", "router_bias", "gate", "up", "down", "gate_scale", "up_scale", "down_scale", "lat_down", "lat_up",
+                     "lat_down_scale", "lat_up_scale"):
+            t = getattr(self, name)
+            setattr(self.desc, name, None if t is None else t.data_ptr())
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.router_w, self.gate, self.up, self.down, self.lat_down, self.lat_up)
+                   if t is not None)
+
+    def _observe(self, T: int, dev) -> tuple[Observe, Observed]:
+        k, E = self.top_k, self.n_expert
+        o = Observed(logits=torch.empty((T, E), dtype=torch.float32, device=dev), probs=torch.empty((T, E), dtype=torch.float32, device=dev),
+                     topk=torch.empty((T, k), dtype=torch.int32, device=dev), weights_norm=torch.empty((T, k), dtype=torch.float32, device=dev),
+                     hidden=torch.empty((T, k, self.n_ff), dtype=torch.float32, device=dev),
+                     down=torch.empty((T, k, self.n_in), dtype=torch.float32, device=dev))
+        s = Observe(ffn_moe_logits=o.logits.data_ptr(), ffn_moe_probs=o.probs.data_ptr(), ffn_moe_topk=o.topk.data_ptr(),
+                    ffn_moe_weights_norm=o.weights_norm.data_ptr(), ffn_moe_hidden=o.hidden.data_ptr(), ffn_moe_down=o.down.data_ptr())
+        return s, o
+
+    def route(self, x: torch.Tensor):
+        """x [T, n_embd] -> (ids int32 [T, k], weights float32 [T, k])."""
+        T = x.shape[0]
+        ids = torch.empty((T, self.top_k), dtype=torch.int32, device=x.device)
+        w = torch.empty((T, self.top_k), dtype=torch.float32, device=x.device)
+        c = self.ctx
+        c.check(c.lib.b200moe_route(c.handle, C.byref(self.desc), _ptr(x), _x_type(x), T, _ptr(ids), _ptr(w), None, c._stream()))
+        return ids, w
+
+    def ffn(self, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        """x [T, n_in] with given routing -> float32 [T, n_in]."""
+        T = x.shape[0]
+        out = torch.empty((T, self.n_in), dtype=torch.float32, device=x.device)
+        c = self.ctx
+        c.check(c.lib.b200moe_ffn(c.handle, C.byref(self.desc), _ptr(x), _x_type(x), T, _ptr(ids.contiguous()), _ptr(weights.contiguous()),
+                                  _ptr(out), None, c._stream()))
+        return out
+
+    def forward(self, x: torch.Tensor, observe: bool = False, out: Optional[torch.Tensor] = None):
+        """The whole layer on device tensors: x [T, n_embd] -> float32 [T, n_embd] (and the observation tensors)."""
+        T = x.shape[0]
+        if out is None:
+            out = torch.empty((T, self.n_embd), dtype=torch.float32, device=x.device)
+        c = self.ctx
+        if observe:
+            s, o = self._observe(T, x.device)
+            c.check(c.lib.b200moe_layer_forward(c.handle, C.byref(self.desc), _ptr(x), _x_type(x), T, _ptr(out), C.byref(s), c._stream()))
+            return out, o
+        c.check(c.lib.b200moe_layer_forward(c.handle, C.byref(self.desc), _ptr(x), _x_type(x), T, _ptr(out), None, c._stream()))
+        return out
+
+    def forward_host(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, ids: Optional[torch.Tensor] = None,
+                     weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Same with HOST tensors (ideally pinned): copies in, computes, copies out, waits."""
+        assert not x.is_cuda
+        T = x.shape[0]
+        if out is None:
+            out = torch.empty((T, self.n_embd), dtype=torch.float32)
+        c = self.ctx
+        c.check(c.lib.b200moe_layer_forward_host(c.handle, C.byref(self.desc), _ptr(x), _x_type(x), T, _ptr(out), _ptr(ids), _ptr(weights),
+                                                 c._stream()))
+        return out

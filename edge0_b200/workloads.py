@@ -1,0 +1,150 @@
+"""Seeded synthetic MoE layers with the shapes and value distributions of the benchmark configurations.
+
+No dataset is involved: every tensor is drawn from a seeded numpy Generator and quantised on the host.
+  router   F32 [E, H]   ~ N(0, 0.02)
+  experts  gate/up [E, I, n_in], down [E, n_in, I] ~ N(0, 0.02), then Q3_K or NVFP4
+  x        [T, H] ~ N(0, 1) (F32, or rounded to bf16)
+NVFP4 uses a two-level scheme: each expert matrix is divided by its fp32 tensor scale
+s = amax / (6 * 448) before block quantisation (so the UE4M3 block scales sit in their normal range) and s
+is handed to the layer as the per-expert scale that multiplies the matmul result.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+import numpy as np
+
+from . import moe
+from .capi import TYPE_NVFP4, TYPE_Q3_K
+
+
+@dataclass
+class LayerConfig:
+    name: str
+    wtype: int
+    n_embd: int = 2048
+    n_expert: int = 128
+    top_k: int = 8
+    n_ff: int = 768
+    n_latent: int = 0
+    router_bias: bool = False
+    tensor_scales: bool = True   # NVFP4 only
+    seed: int = 0
+
+    @property
+    def n_in(self) -> int:
+        return self.n_latent or self.n_embd
+
+
+CONFIGS = {
+    # BASELINE configs[0]: Q3_K decode
+    "c1_q3k": LayerConfig("c1_q3k", TYPE_Q3_K, seed=101),
+    # configs[1]: NVFP4 batched decode
+    "c2_nvfp4": LayerConfig("c2_nvfp4", TYPE_NVFP4, seed=102),
+    # configs[2]: NVFP4 prefill with per-expert logit bias
+    "c3_nvfp4_prefill": LayerConfig("c3_nvfp4_prefill", TYPE_NVFP4, router_bias=True, seed=103),
+    # configs[4]: latent expert-parallel layer
+    "c5_latent": LayerConfig("c5_latent", TYPE_NVFP4, n_embd=4096, n_latent=1024, n_expert=512, top_k=10, n_ff=1024, seed=105),
+}
+
+
+@dataclass
+class HostLayer:
+    cfg: LayerConfig
+    router_w: np.ndarray
+    gate: np.ndarray
+    up: np.ndarray
+    down: np.ndarray
+    router_bias: Optional[np.ndarray] = None
+    gate_scale: Optional[np.ndarray] = None
+    up_scale: Optional[np.ndarray] = None
+    down_scale: Optional[np.ndarray] = None
+    lat_down: Optional[np.ndarray] = None
+    lat_up: Optional[np.ndarray] = None
+    lat_down_scale: Optional[np.ndarray] = None
+    lat_up_scale: Optional[np.ndarray] = None
+
+    def kwargs(self) -> dict:
+        """Keyword arguments shared by edge0_b200.moe.MoeLayer and the checkers' moe_layer."""
+        return dict(router_w=self.router_w, gate=self.gate, up=self.up, down=self.down, router_bias=self.router_bias)
+
+    def to_device(self, ctx) -> "moe.MoeLayer":
+        return moe.MoeLayer(ctx, wtype=self.cfg.wtype, top_k=self.cfg.top_k, router_w=self.router_w, gate=self.gate, up=self.up,
+                            down=self.down, router_bias=self.router_bias, gate_scale=self.gate_scale, up_scale=self.up_scale,
+                            down_scale=self.down_scale, lat_down=self.lat_down, lat_up=self.lat_up,
+                            lat_down_scale=self.lat_down_scale, lat_up_scale=self.lat_up_scale)
+
+    def checker_kwargs(self) -> dict:
+        return dict(wtype=self.cfg.wtype, router_w=self.router_w, gate=self.gate, up=self.up, down=self.down, top_k=self.cfg.top_k,
+                    router_bias=self.router_bias, s_gate=self.gate_scale, s_up=self.up_scale, s_down=self.down_scale,
+                    lat_d=self.lat_down, lat_u=self.lat_up, s_lat_d=self.lat_down_scale, s_lat_u=self.lat_up_scale)
+
+
+def _quantize(wtype: int, w: np.ndarray, quantize_q3k: Optional[Callable]) -> np.ndarray:
+    if wtype == TYPE_NVFP4:
+        return moe.quantize_nvfp4(w)
+    if quantize_q3k is None:
+        raise RuntimeError("Q3_K inputs need a quantiser callback (the reference quantiser)")
+    return quantize_q3k(w)
+
+
+def _matrix(rng, shape, wtype, scaled, quantize_q3k, chunk_experts=32):
+    """Draw and quantise [E, rows, n] in chunks of experts to bound host memory."""
+    E = shape[0]
+    outs, scales = [], []
+    for e0 in range(0, E, chunk_experts):
+        e1 = min(E, e0 + chunk_experts)
+        w = rng.normal(0.0, 0.02, (e1 - e0,) + tuple(shape[1:])).astype(np.float32)
+        if scaled:
+            s = (np.abs(w).reshape(e1 - e0, -1).max(axis=1) / np.float32(6 * 448)).astype(np.float32)
+            w = w / s[:, None, None]
+            scales.append(s)
+        outs.append(_quantize(wtype, w, quantize_q3k))
+    return np.concatenate(outs, axis=0), (np.concatenate(scales) if scaled else None)
+
+
+def make_layer(cfg: LayerConfig, quantize_q3k: Optional[Callable] = None, seed_offset: int = 0) -> HostLayer:
+    rng = np.random.default_rng(cfg.seed + 7919 * seed_offset)
+    E, H, I, n_in = cfg.n_expert, cfg.n_embd, cfg.n_ff, cfg.n_in
+    scaled = cfg.wtype == TYPE_NVFP4 and cfg.tensor_scales
+    router_w = rng.normal(0.0, 0.02, (E, H)).astype(np.float32)
+    gate, sg = _matrix(rng, (E, I, n_in), cfg.wtype, scaled, quantize_q3k)
+    up, su = _matrix(rng, (E, I, n_in), cfg.wtype, scaled, quantize_q3k)
+    down, sd = _matrix(rng, (E, n_in, I), cfg.wtype, scaled, quantize_q3k)
+    layer = HostLayer(cfg, router_w, gate, up, down, gate_scale=sg, up_scale=su, down_scale=sd)
+    if cfg.router_bias:
+        layer.router_bias = rng.normal(0.0, 1.0, E).astype(np.float32)
+    if cfg.n_latent:
+        d, s_d = _matrix(rng, (1, cfg.n_latent, H), cfg.wtype, scaled, quantize_q3k)
+        u, s_u = _matrix(rng, (1, H, cfg.n_latent), cfg.wtype, scaled, quantize_q3k)
+        layer.lat_down, layer.lat_up = d[0], u[0]
+        layer.lat_down_scale, layer.lat_up_scale = s_d, s_u
+    return layer
+
+
+def make_tokens(cfg: LayerConfig, n_tokens: int, bf16: bool = False, seed_offset: int = 0) -> np.ndarray:
+    """float32 [T, n_embd] ~ N(0,1); with bf16=True the values are rounded to bf16 (still stored as float32)."""
+    rng = np.random.default_rng(cfg.seed * 1000 + 17 + seed_offset)
+    x = rng.normal(0.0, 1.0, (n_tokens, cfg.n_embd)).astype(np.float32)
+    if bf16:
+        u = x.view(np.uint32)
+        u = ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)   # round to nearest even
+        x = u.view(np.float32)
+    return x
+
+
+def small_config(wtype: int, *, n_embd=512, n_expert=16, top_k=4, n_ff=256, n_latent=0, router_bias=False, seed=1, tensor_scales=True):
+    return LayerConfig(f"small_{wtype}", wtype, n_embd=n_embd, n_expert=n_expert, top_k=top_k, n_ff=n_ff, n_latent=n_latent,
+                       router_bias=router_bias, seed=seed, tensor_scales=tensor_scales)
+
+
+def algorithmic_bytes(cfg: LayerConfig, n_tokens: int, experts_touched: int, x_bytes_per_elt: int = 4) -> int:
+    """Bytes one layer pass must move: routed experts' three matrices, the router, the latent projections, x in, out out."""
+    per_matrix = cfg.n_ff * moe.row_size(cfg.wtype, cfg.n_in)
+    down = cfg.n_in * moe.row_size(cfg.wtype, cfg.n_ff)
+    b = experts_touched * (2 * per_matrix + down) + cfg.n_expert * cfg.n_embd * 4
+    if cfg.n_latent:
+        b += cfg.n_latent * moe.row_size(cfg.wtype, cfg.n_embd) + cfg.n_embd * moe.row_size(cfg.wtype, cfg.n_latent)
+    b += n_tokens * cfg.n_embd * (x_bytes_per_elt + 4)
+    return int(b)

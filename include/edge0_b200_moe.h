@@ -1,0 +1,160 @@
+/* edge0_b200_moe.h — C ABI of the B200 (sm_100a) quantised MoE-FFN path.
+ *
+ * Drop-in for the one hot path edge0-infer runs through ggml: router top-k, token->expert gather,
+ * Q3_K / NVFP4 expert gate/up/down matmuls (ggml MUL_MAT_ID), SwiGLU and the weighted combine.
+ * Plain pointers and sizes only; every function returns a b200moe_status (0 = success), validates
+ * its arguments on the host before any launch and never aborts the process.  All tensor pointers
+ * are DEVICE pointers unless the name ends in _host.  Layouts are ggml's (ne[0] fastest) and the
+ * quantised blocks are ggml's block_q3_K / block_nvfp4 bytes, unchanged.
+ *
+ * Citations name the reference interface each entry point stands in for
+ * (paths inside the Edge0 repository).
+ */
+#ifndef EDGE0_B200_MOE_H
+#define EDGE0_B200_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define B200MOE_API __attribute__((visibility("default")))
+#else
+#define B200MOE_API
+#endif
+
+typedef struct b200moe_ctx b200moe_ctx;
+
+/* values equal ggml_type (edge0-infer/third_party/ggml/include/ggml.h:398-430) */
+enum b200moe_type { B200MOE_TYPE_F32 = 0, B200MOE_TYPE_Q3_K = 11, B200MOE_TYPE_BF16 = 30, B200MOE_TYPE_NVFP4 = 40 };
+
+/* mirrors ggml_status (SUCCESS / FAILED / ALLOC_FAILED) plus argument errors that ggml asserts on */
+enum b200moe_status {
+    B200MOE_OK = 0,
+    B200MOE_ERR_INVALID_ARG = 1,  /* null pointer, negative size, shape the op contract forbids */
+    B200MOE_ERR_UNSUPPORTED = 2,  /* well-formed, but no kernel for this type / width */
+    B200MOE_ERR_ALLOC = 3,        /* device scratch could not be allocated */
+    B200MOE_ERR_CUDA = 4,         /* a CUDA call or launch failed; b200moe_last_error has the text */
+    B200MOE_ERR_DEVICE_CHECK = 5, /* a kernel's own bounded wait or index check gave up */
+    B200MOE_ERR_NO_DEVICE = 6
+};
+
+/* One MoE FFN layer's weights: what Builder::route / Builder::ffn look up by name
+ * (edge0-infer/src/models/edge0_35b/forward.cpp:262-271, 300-311).
+ *   router_w    F32 [n_embd, n_expert]            blk.N.ffn_gate_inp.weight
+ *   router_bias F32 [n_expert] or NULL            added to the logits before the softmax
+ *   gate/up     wtype [n_in, n_ff, n_expert]      blk.N.ffn_{gate,up}_exps.weight   (n_in = n_latent ? n_latent : n_embd)
+ *   down        wtype [n_ff, n_in, n_expert]      blk.N.ffn_down_exps.weight
+ *   *_scale     F32 [n_expert] or NULL            NVFP4 per-expert tensor scale, applied to the matmul result
+ *                                                 (pattern at third_party/ggml/src/ggml-cuda/ggml-cuda.cu:3655-3673)
+ *   lat_down    wtype [n_embd, n_latent]          shared projection into the latent width (n_latent > 0 only;
+ *   lat_up      wtype [n_latent, n_embd]          semantics of edge0-strata/src/latent/latent_moe.cpp:38-92, one group)
+ */
+typedef struct b200moe_layer {
+    int32_t n_embd;
+    int32_t n_latent;      /* 0: experts work at n_embd */
+    int32_t n_expert;
+    int32_t n_expert_used; /* top-k */
+    int32_t n_ff;
+    int32_t wtype;         /* b200moe_type of gate/up/down (and lat_*) */
+    const float * router_w;
+    const float * router_bias;
+    const void  * gate;
+    const void  * up;
+    const void  * down;
+    const float * gate_scale;
+    const float * up_scale;
+    const float * down_scale;
+    const void  * lat_down;
+    const void  * lat_up;
+    const float * lat_down_scale; /* F32 [1] or NULL */
+    const float * lat_up_scale;   /* F32 [1] or NULL */
+} b200moe_layer;
+
+/* Optional observation outputs, named after the reference's ForwardRequest::observe labels
+ * (forward.cpp:752-761).  Any pointer may be NULL. */
+typedef struct b200moe_observe {
+    float   * ffn_moe_logits;       /* F32 [n_expert, T] */
+    float   * ffn_moe_probs;        /* F32 [n_expert, T] */
+    int32_t * ffn_moe_topk;         /* I32 [k, T]        */
+    float   * ffn_moe_weights_norm; /* F32 [k, T]        */
+    float   * ffn_moe_hidden;       /* F32 [n_ff, k, T]  silu(gate)*up         */
+    float   * ffn_moe_down;         /* F32 [n_in, k, T]  down, before weights  */
+} b200moe_observe;
+
+/* per-call counters (reference: WeightActivity / DecodeTiming, include/edge0/weight_activity.h, timing.h) */
+typedef struct b200moe_counters {
+    int64_t tokens;
+    int64_t experts_touched;  /* distinct experts with at least one routed row */
+    int64_t weight_bytes;     /* expert + router bytes the kernels streamed   */
+    int64_t kernel_launches;
+} b200moe_counters;
+
+/* ---- lifetime (reference: ggml_backend_dev_init / ggml_backend_free through
+ *      BackendFacility::create, edge0-infer/src/platform/backend.cpp:95-129) */
+B200MOE_API int  b200moe_create(int device, b200moe_ctx ** out);
+B200MOE_API void b200moe_destroy(b200moe_ctx * ctx);
+/* Size the context's device scratch for up to max_tokens tokens of this layer shape (reference:
+ * ggml_gallocr workspace sizing in exec::build_plan, edge0-infer/src/exec/execution.cpp:303-311).
+ * Called implicitly by the compute entry points when the scratch is too small. */
+B200MOE_API int  b200moe_reserve(b200moe_ctx * ctx, const b200moe_layer * layer, int32_t max_tokens);
+B200MOE_API const char * b200moe_last_error(const b200moe_ctx * ctx);
+B200MOE_API const char * b200moe_status_string(int status);
+B200MOE_API int  b200moe_device_memory(int device, size_t * free_bytes, size_t * total_bytes); /* ggml_backend_dev_memory */
+B200MOE_API int  b200moe_get_counters(const b200moe_ctx * ctx, b200moe_counters * out);
+B200MOE_API int  b200moe_synchronize(b200moe_ctx * ctx, void * stream); /* ggml_backend_synchronize */
+
+/* Per-kernel device timing (reference: DecodeTiming with an injectable clock, include/edge0/timing.h:4-9).
+ * When enabled, every expert-matmul launch is bracketed by CUDA events on its stream; b200moe_kernel_times
+ * waits for them and returns, for kind 0 (fused gate+up+SwiGLU) and kind 1 (single indexed matmul / down),
+ * the number of launches and their summed duration since the last call, then clears the record. */
+B200MOE_API int  b200moe_enable_kernel_timing(b200moe_ctx * ctx, int enable);
+B200MOE_API int  b200moe_kernel_times(b200moe_ctx * ctx, int64_t launches[2], double total_ms[2]);
+
+/* ---- data formats (reference: ggml_row_size, ggml.h:761; quantize_row_nvfp4_ref, ggml-quants.c:384-417;
+ *      dequantize_row_q3_K / _nvfp4, ggml-quants.c:1305-1353, 589-612).  Host memory. */
+B200MOE_API int64_t b200moe_row_size(int type, int64_t n);
+B200MOE_API int  b200moe_quantize_nvfp4_host(const float * src, void * dst, int64_t nrows, int64_t n_per_row);
+B200MOE_API int  b200moe_dequantize_host(int type, const void * src, float * dst, int64_t nrows, int64_t n_per_row);
+
+/* ---- compute.  `stream` is a cudaStream_t (NULL = default stream); calls are asynchronous on it. */
+
+/* Builder::route (forward.cpp:262-271) = mul_mat(F32) -> soft_max -> argsort_top_k -> get_rows ->
+ * sum_rows -> clamp(2^-14) -> div.  x: x_type (F32 or BF16) [n_embd, T].
+ * ids I32 [k, T] (expert indices, descending probability); weights F32 [k, T]. */
+B200MOE_API int b200moe_route(b200moe_ctx * ctx, const b200moe_layer * layer, const void * x, int x_type,
+                              int32_t n_tokens, int32_t * ids, float * weights,
+                              const b200moe_observe * observe, void * stream);
+
+/* ggml_mul_mat_id (ggml.c:3392-3416; CPU kernel ggml-cpu/ggml-cpu.c:1550-1740).
+ *   as   wtype [ne00, ne01, n_as]   b  F32 [ne00, ne11, T]   ids I32 [n_ids, T], row stride ids_nb1 bytes
+ *   dst  F32 [ne01, n_ids, T];  row (id, t) uses b[:, id % ne11, t] quantised to the type's vec_dot_type.
+ * ids may index expert slots rather than experts (edge0-infer/src/weights/expert_slots.h:13-18). */
+B200MOE_API int b200moe_mul_mat_id(b200moe_ctx * ctx, int wtype, const void * as, int64_t ne00, int64_t ne01, int64_t n_as,
+                                   const float * b, int64_t ne11, const int32_t * ids, int64_t n_ids, int64_t ids_nb1,
+                                   int64_t n_tokens, float * dst, void * stream);
+
+/* Builder::ffn with given routing (forward.cpp:300-311): gate/up mul_mat_id -> silu*up -> down mul_mat_id ->
+ * * weights -> sum over slots in slot order.  x: [n_in, T] in x_type; out F32 [n_in, T]. */
+B200MOE_API int b200moe_ffn(b200moe_ctx * ctx, const b200moe_layer * layer, const void * x, int x_type, int32_t n_tokens,
+                            const int32_t * ids, const float * weights, float * out,
+                            const b200moe_observe * observe, void * stream);
+
+/* route + (latent down) + ffn + (latent up): the whole layer on device buffers.  out F32 [n_embd, T]. */
+B200MOE_API int b200moe_layer_forward(b200moe_ctx * ctx, const b200moe_layer * layer, const void * x, int x_type,
+                                      int32_t n_tokens, float * out, const b200moe_observe * observe, void * stream);
+
+/* Same through HOST buffers: copies x in, runs the layer, copies out (and ids/weights when non-NULL) back and
+ * waits.  This is what a caller holding host tensors pays (exec::Plan::set_inputs / read_output =
+ * ggml_backend_tensor_set / _get, edge0-infer/src/exec/execution.cpp:343,421). */
+B200MOE_API int b200moe_layer_forward_host(b200moe_ctx * ctx, const b200moe_layer * layer, const void * x_host, int x_type,
+                                           int32_t n_tokens, float * out_host, int32_t * ids_host, float * weights_host,
+                                           void * stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EDGE0_B200_MOE_H */
