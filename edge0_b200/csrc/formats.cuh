@@ -32,7 +32,11 @@ B200_HD int64_t weight_row_bytes(int type, int64_t k) {
 // ---- portable stand-ins for the integer intrinsics -------------------------------------------------
 B200_HD uint32_t byte_perm(uint32_t x, uint32_t y, uint32_t s) {
 #if defined(__CUDA_ARCH__)
-    return __byte_perm(x, y, s);
+    // PTX prmt directly: the __byte_perm intrinsic drops bit 3 of each selector nibble, and the NVFP4 decode
+    // relies on that bit's "replicate the sign of the selected byte" meaning.
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(x), "r"(y), "r"(s));
+    return r;
 #else
     const uint64_t v = ((uint64_t) y << 32) | x;
     uint32_t r = 0;

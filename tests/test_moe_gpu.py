@@ -1,7 +1,12 @@
 """Parity of the CUDA path (through the C ABI) with the CPU checker on identical seeded inputs.
 
-Bar: routing ids bit-exact; every floating-point output within max-abs <= 1e-2 * RMS(reference output)
-(the bound stated for this path); in practice the int8-grid arithmetic agrees to ~1e-5.
+Bar: routing ids, router logits, probabilities and route weights bit-exact; every FFN output within
+max-abs <= 1e-2 * RMS(reference output), the bound stated for this path.  What is actually observed:
+* hidden = silu(gate)*up agrees to ~1e-6 (integer dots are exact, only the fp32 summation order differs);
+* the reference re-quantises hidden to int8 before the down matmul; a 1e-7 difference in hidden occasionally
+  moves one value across a rounding boundary, which shifts that one routed row of `down` by a few 1e-3 of the
+  RMS.  So `down`/`out` are checked against the 1e-2 bar, and the share of routed rows that moved at all is
+  bounded separately.
 """
 import os
 
@@ -44,10 +49,14 @@ def run_and_compare(gpu_ctx, checker, layer, x_np, bf16, tol=TIGHT):
     assert np.array_equal(ob.logits.cpu().numpy(), r.logits), "router logits follow the reference summation order bit for bit"
     assert np.array_equal(ob.probs.cpu().numpy(), r.probs)
     assert np.array_equal(ob.weights_norm.cpu().numpy(), r.weights)
-    errs = dict(hidden=rel_err(ob.hidden.cpu().numpy(), r.hidden), down=rel_err(ob.down.cpu().numpy(), r.down_out),
-                out=rel_err(out.cpu().numpy(), r.out))
-    for k, v in errs.items():
-        assert v <= tol, (k, v, errs)
+    down = ob.down.cpu().numpy()
+    errs = dict(hidden=rel_err(ob.hidden.cpu().numpy(), r.hidden), down=rel_err(down, r.down_out), out=rel_err(out.cpu().numpy(), r.out))
+    assert errs["hidden"] <= tol, errs
+    assert errs["down"] <= TOL and errs["out"] <= TOL, errs
+    rms = np.sqrt(np.mean(r.down_out.astype(np.float64) ** 2))
+    moved = (np.abs(down - r.down_out).max(axis=2) > TIGHT * rms).mean()   # routed rows touched by a requantisation flip
+    assert moved <= 0.05, (moved, errs)
+    errs["rows_moved"] = float(moved)
     return errs
 
 
@@ -73,8 +82,8 @@ def test_golden_fixtures(name, gpu_ctx):
     assert np.array_equal(ob.probs.cpu().numpy(), z["probs"])
     assert np.array_equal(ob.weights_norm.cpu().numpy(), z["weights"])
     assert rel_err(ob.hidden.cpu().numpy(), z["hidden"]) <= TIGHT
-    assert rel_err(ob.down.cpu().numpy(), z["down_out"]) <= TIGHT
-    assert rel_err(out.cpu().numpy(), z["out"]) <= TIGHT
+    assert rel_err(ob.down.cpu().numpy(), z["down_out"]) <= TOL
+    assert rel_err(out.cpu().numpy(), z["out"]) <= TOL
 
 
 @pytest.mark.parametrize("T", [1, 2, 5, 33])
@@ -165,7 +174,7 @@ def test_host_entry_point_and_determinism(gpu_ctx, checker):
     assert torch.equal(o1, o2), "two runs must give identical bytes"
     r = checker.moe_layer(x=x_np, **layer.checker_kwargs())
     assert np.array_equal(ids.numpy(), r.ids)
-    assert rel_err(o1.numpy(), r.out) <= TIGHT
+    assert rel_err(o1.numpy(), r.out) <= TOL
 
 
 def test_argument_errors_do_not_launch(gpu_ctx):
