@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(ROOT, "lib", "libedge0_b200.so")
 
 TYPE_F32, TYPE_Q3_K, TYPE_BF16, TYPE_NVFP4 = 0, 11, 30, 40
 OK = 0
+NOALLOC_MAX_LOGITS = 32768  # B200MOE_NOALLOC_MAX_LOGITS
 STATUS = {0: "OK", 1: "INVALID_ARG", 2: "UNSUPPORTED", 3: "ALLOC", 4: "CUDA", 5: "DEVICE_CHECK", 6: "NO_DEVICE"}
 
 
@@ -54,6 +55,8 @@ SIGNATURES = {
                               C.POINTER(Observe), C.c_void_p]),
     "b200moe_layer_forward": (C.c_int, [C.c_void_p, C.POINTER(Layer), C.c_void_p, C.c_int, C.c_int32, C.c_void_p,
                                         C.POINTER(Observe), C.c_void_p]),
+    "b200moe_route_noalloc": (C.c_int, [C.c_int, C.POINTER(Layer), C.c_void_p, C.c_int, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
+                                        C.c_char_p, C.c_size_t]),
     "b200moe_layer_forward_host": (C.c_int, [C.c_void_p, C.POINTER(Layer), C.c_void_p, C.c_int, C.c_int32, C.c_void_p,
                                              C.c_void_p, C.c_void_p, C.c_void_p]),
 }

@@ -773,4 +773,61 @@ int b200moe_layer_forward_host(b200moe_ctx * ctx, const b200moe_layer * l, const
     return read_device_error(ctx, st);
 }
 
+// ---- routing with no allocation at all -----------------------------------------------------------------
+// Scratch for the router logits lives in the library image.  In HOST code the name below is only a stand-in for
+// the symbol, not a device address, so the address is looked up once per device with cudaGetSymbolAddress.
+static __device__ __align__(256) float g_noalloc_logits[B200MOE_NOALLOC_MAX_LOGITS];
+static float * g_noalloc_logits_ptr[64] = {};
+
+static int noalloc_fail(char * buf, size_t len, int code, const char * msg) {
+    if (buf && len) snprintf(buf, len, "%s", msg);
+    return code;
+}
+
+int b200moe_route_noalloc(int device, const b200moe_layer * l, const void * x, int x_type, int32_t T, int32_t * ids, float * weights,
+                          void * stream, char * errbuf, size_t errbuf_len) {
+    if (errbuf && errbuf_len) errbuf[0] = 0;
+    if (!l) return noalloc_fail(errbuf, errbuf_len, B200MOE_ERR_INVALID_ARG, "layer is null");
+    if (T == 0) return B200MOE_OK;
+    if (T < 0 || !x || !ids || !weights || !l->router_w) return noalloc_fail(errbuf, errbuf_len, B200MOE_ERR_INVALID_ARG, "null pointer or negative token count");
+    if (device < 0 || device >= 64) return noalloc_fail(errbuf, errbuf_len, B200MOE_ERR_INVALID_ARG, "device ordinal out of range");
+    if (x_type != TYPE_F32 && x_type != TYPE_BF16) return noalloc_fail(errbuf, errbuf_len, B200MOE_ERR_UNSUPPORTED, "activations must be F32 or BF16");
+    const int E = l->n_expert, K = l->n_expert_used, H = l->n_embd;
+    if (E <= 0 || K <= 0 || H <= 0 || K > E) return noalloc_fail(errbuf, errbuf_len, B200MOE_ERR_INVALID_ARG, "bad layer dimensions");
+    if (K > 32 || E > 1024 || E % 8 || H % 32) return noalloc_fail(errbuf, errbuf_len, B200MOE_ERR_UNSUPPORTED, "need k <= 32, n_expert % 8 == 0 and <= 1024, n_embd % 32 == 0");
+    if ((int64_t) T * E > B200MOE_NOALLOC_MAX_LOGITS) {
+        char msg[160];
+        snprintf(msg, sizeof msg, "n_tokens * n_expert = %lld exceeds the built-in scratch of %d floats", (long long) T * E, B200MOE_NOALLOC_MAX_LOGITS);
+        return noalloc_fail(errbuf, errbuf_len, B200MOE_ERR_UNSUPPORTED, msg);
+    }
+    if (cudaSetDevice(device) != cudaSuccess) { cudaGetLastError(); return noalloc_fail(errbuf, errbuf_len, B200MOE_ERR_CUDA, "cudaSetDevice failed"); }
+    if (!g_noalloc_logits_ptr[device]) {  // set-up, once per device, with that device current
+        float * ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void **) &ptr, g_noalloc_logits);
+        if (e != cudaSuccess || !ptr) { cudaGetLastError(); return noalloc_fail(errbuf, errbuf_len, B200MOE_ERR_CUDA, cudaGetErrorString(e)); }
+        g_noalloc_logits_ptr[device] = ptr;
+    }
+    float * logits = g_noalloc_logits_ptr[device];
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    constexpr int TT = 4;
+    const int64_t warps = (int64_t) E * ((T + TT - 1) / TT);
+    const int lblocks = (int) ((warps * 32 + 255) / 256);
+    if (x_type == TYPE_F32)
+        router_logits_kernel<TT, float><<<lblocks, 256, 0, st>>>(l->router_w, l->router_bias, static_cast<const float *>(x), logits, H, E, T, nullptr, 0);
+    else
+        router_logits_kernel<TT, __nv_bfloat16><<<lblocks, 256, 0, st>>>(l->router_w, l->router_bias, static_cast<const __nv_bfloat16 *>(x), logits, H, E, T, nullptr, 0);
+    const int sblocks = (T * 32 + 255) / 256;
+#define SEL(EPL) route_select_kernel<EPL><<<sblocks, 256, 0, st>>>(logits, E, K, T, ids, weights, nullptr, nullptr, nullptr)
+    if (E <= 32) SEL(1);
+    else if (E <= 64) SEL(2);
+    else if (E <= 128) SEL(4);
+    else if (E <= 256) SEL(8);
+    else if (E <= 512) SEL(16);
+    else SEL(32);
+#undef SEL
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return noalloc_fail(errbuf, errbuf_len, B200MOE_ERR_CUDA, cudaGetErrorString(e));
+    return B200MOE_OK;
+}
+
 }  // extern "C"

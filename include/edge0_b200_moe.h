@@ -154,6 +154,28 @@ B200MOE_API int b200moe_layer_forward_host(b200moe_ctx * ctx, const b200moe_laye
                                            int32_t n_tokens, float * out_host, int32_t * ids_host, float * weights_host,
                                            void * stream);
 
+/* Routing without any allocation.  (No counterpart in the reference: its backends always own a workspace.)
+ *
+ * For callers that must not trigger cudaMalloc: code running inside a latency-critical serving loop, inside a
+ * memory pool that has handed the whole device to someone else, or on a thread that is not allowed to take the
+ * allocator's lock.  It computes exactly what b200moe_route computes (same kernels, same bits), but keeps the
+ * intermediate router logits in a fixed array that is part of the library image instead of context scratch, and it
+ * needs no b200moe_ctx.
+ *
+ * Limit: n_tokens * n_expert <= B200MOE_NOALLOC_MAX_LOGITS (32768 floats = 128 KiB, e.g. 256 tokens x 128 experts).
+ * Every GPU that loads the library holds that array until the process exits.  Larger requests are rejected with
+ * B200MOE_ERR_UNSUPPORTED; nothing is launched.
+ *
+ * The first call on each device looks up the array's device address (one cudaGetSymbolAddress, which may load the
+ * module): make that first call outside of any stream capture.  All calls on a device share the one array: it is
+ * fully overwritten by each call (nothing has to start at zero), and two calls whose kernels overlap on the GPU
+ * (different streams, no ordering between them) race on it - serialise them.
+ * `device` is the CUDA device ordinal of the pointers; it is made current.  errbuf (may be NULL) receives a
+ * message when the status is not B200MOE_OK. */
+#define B200MOE_NOALLOC_MAX_LOGITS 32768
+B200MOE_API int b200moe_route_noalloc(int device, const b200moe_layer * layer, const void * x, int x_type, int32_t n_tokens,
+                                      int32_t * ids, float * weights, void * stream, char * errbuf, size_t errbuf_len);
+
 #ifdef __cplusplus
 }
 #endif
