@@ -121,6 +121,7 @@ void carve(Plan & p, uint8_t * base) {
     p.groups.perm = c.take<int>(std::max(R, T));
     p.groups.active = c.take<int>(E);
     p.groups.meta = c.take<int>(4);
+    p.groups.cost = c.take<int>(3 * (E + 1));
     p.xq = c.act(T, std::max(H, kin));
     p.xlq = c.act(T, kin);
     p.hq = c.act(R, I);
@@ -302,6 +303,7 @@ GemvParams gemv_params(b200moe_ctx * ctx, const void * w0, const void * w1, cons
     g.perm = p.groups.perm;
     g.active = p.groups.active;
     g.meta = p.groups.meta;
+    g.cost = p.groups.cost;
     g.out = out;
     g.n_out = n_out;
     g.n_ids = n_ids;

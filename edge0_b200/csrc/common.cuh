@@ -162,6 +162,8 @@ __device__ __forceinline__ int group_reduce_owner_value(int lane_in_group) {
     return idx;
 }
 
-__device__ __forceinline__ int dp4a_s(int a, int b, int c) { return __dp4a(a, b, c); }
+// Exact int -> float for |i| < 2^22 without the conversion unit (which issues at a fraction of the ALU rate):
+// 0x4B400000 is 1.5*2^23, whose ulp is 1, so adding i to the bit pattern adds i to the value.
+__device__ __forceinline__ float small_int_to_float(int i) { return __int_as_float(0x4B400000 + i) - 12582912.0f; }
 
 }  // namespace b200moe

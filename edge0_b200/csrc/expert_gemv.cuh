@@ -28,6 +28,7 @@ struct GemvParams {
     const int * perm;     // [rows]
     const int * active;   // [n_as]
     const int * meta;     // meta[0] = number of active experts
+    const int * cost;     // [3][n_as+1] work prefixes (see Groups::cost)
     float * out;          // [rows][n_out]
     int n_out;
     int n_ids;
@@ -139,8 +140,8 @@ __device__ __forceinline__ void row_partial(const uint8_t * __restrict__ row, in
                 nb = dot4((int) b1.neg_a, (int) q[6], nb);
                 nb = dot4((int) b1.neg_b, (int) q[7], nb);
                 const float dy = acts[t].d[i];
-                acc[t] = fmaf(s0 * dy, (float) (pa - na), acc[t]);
-                acc[t] = fmaf(s1 * dy, (float) (pb - nb), acc[t]);
+                acc[t] = fmaf(s0 * dy, small_int_to_float(pa - na), acc[t]);
+                acc[t] = fmaf(s1 * dy, small_int_to_float(pb - nb), acc[t]);
             }
         } else {
             const int sb = u >> 3, p = u & 7;
@@ -157,7 +158,7 @@ __device__ __forceinline__ void row_partial(const uint8_t * __restrict__ row, in
                 int isum = q3k_unit_dot(qs0, qs1, hm, sc, p, acts[t].q[i]);
                 const int bs = acts[t].bs[i];
                 isum -= 4 * (c0 * (int) (int16_t) (bs & 0xffff) + c1 * (int) (int16_t) (bs >> 16));
-                acc[t] = fmaf(dw * acts[t].d[i], (float) isum, acc[t]);
+                acc[t] = fmaf(dw * acts[t].d[i], small_int_to_float(isum), acc[t]);
             }
         }
     }
@@ -214,8 +215,31 @@ __global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_ke
     const int upe = p.n_out / C::GRAN;                       // span units per expert
     const long long total = (long long) n_active * upe;
     ChunkWalker cons, prod;
-    cons.u = (int) (total * blockIdx.x / gridDim.x);
-    cons.u_end = (int) (total * (blockIdx.x + 1) / gridDim.x);
+    // Span boundaries balance WORK, not rows: a weight row of an expert with n routed rows costs ceil(n/NT) passes.
+    // Boundary i sits at work i/grid of the total; both neighbours compute it the same way, so spans tile exactly.
+    __shared__ int s_span[2];
+    if (tid < 2) {
+        const int * cw = p.cost + (NT == 1 ? 0 : NT == 2 ? 1 : 2) * (p.n_as + 1);
+        const long long total_work = (long long) cw[n_active] * upe;
+        const long long c = total_work * (blockIdx.x + tid) / gridDim.x;
+        int lo = 0, hi = n_active;  // largest a with cw[a]*upe <= c
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if ((long long) cw[mid] * upe <= c) lo = mid; else hi = mid;
+        }
+        int u;
+        if (n_active == 0) u = 0;
+        else if (blockIdx.x + tid == gridDim.x) u = (int) total;
+        else {
+            const int per = max(cw[lo + 1] - cw[lo], 1);
+            const long long uu = (c - (long long) cw[lo] * upe) / per;
+            u = lo * upe + (int) (uu < (long long) upe ? uu : (long long) upe);
+        }
+        s_span[tid] = u;
+    }
+    __syncthreads();
+    cons.u = s_span[0];
+    cons.u_end = s_span[1];
     cons.units_per_expert = upe;
     cons.gran = C::GRAN;
     cons.max_rows = C::ROWS_PER_STAGE;

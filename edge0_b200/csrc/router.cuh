@@ -252,6 +252,7 @@ struct Groups {
     int * perm;     // [rows]
     int * active;   // [E]
     int * meta;     // [4]
+    int * cost;     // [3][E+1]: prefix over active experts of ceil(rows/nt) for nt = 1, 2, 4 (work per weight row)
 };
 
 // Single block.  counts must be final (selection kernel finished).
@@ -272,6 +273,14 @@ __global__ void __launch_bounds__(1024) group_scan_kernel(Groups g, const int32_
             if (act[e]) g.active[na++] = e;
         }
         off[E] = run;
+        int c1 = 0, c2 = 0, c4 = 0;
+        for (int a = 0; a < na; ++a) {
+            const int e = g.active[a];
+            const int n = off[e + 1 <= E ? e + 1 : E] - off[e];
+            g.cost[a] = c1; g.cost[(E + 1) + a] = c2; g.cost[2 * (E + 1) + a] = c4;
+            c1 += n; c2 += (n + 1) / 2; c4 += (n + 3) / 4;
+        }
+        g.cost[na] = c1; g.cost[(E + 1) + na] = c2; g.cost[2 * (E + 1) + na] = c4;
         g.meta[0] = na;
         g.meta[1] = run;
         if (run != rows) report_error(err, DEV_ERR_BAD_SHAPE);
