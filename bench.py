@@ -40,6 +40,7 @@ def parse():
     ap.add_argument("--weight-sets", type=int, default=3, help="distinct weight copies rotated over (L2 defeat)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every step's kernels from the host instead of replaying CUDA graphs")
     return ap.parse_args()
 
 
@@ -183,8 +184,32 @@ def run_b200_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    def step(i):
-        layers[i % n_sets].forward(xs[i % n_sets], out=out)
+    def make_stepper(x_list, out_t):
+        """Returns (step, eager_step).  step replays one CUDA graph per weight set (the step's kernel launches captured
+        once, so the host's launch cost is off the critical path) unless --no-graph; the library's calls are plain
+        stream work and capture as they are."""
+        def eager(i):
+            layers[i % n_sets].forward(x_list[i % n_sets], out=out_t)
+        if args.no_graph:
+            return eager, eager
+        for i in range(n_sets):
+            eager(i)                        # sizes scratch and sets kernel attributes outside of capture
+        ctx.synchronize()
+        gs = []
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(n_sets):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    eager(i)
+                gs.append(g)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        return (lambda i: gs[i % n_sets].replay()), eager
+
+    step, eager_step = make_stepper(xs, out)
+    graphs = not args.no_graph
 
     # ---- device-resident timing: K steps between two events, barrier + synchronize on both sides
     for i in range(args.warmup):
@@ -201,6 +226,11 @@ def run_b200_arm(args):
     e1.record()
     barrier()
     launches = ctx.launches() - l0
+    if graphs:   # replays do not pass through the library's counter: count one eager step and multiply
+        c0 = ctx.launches()
+        eager_step(0)
+        ctx.synchronize()
+        launches = (ctx.launches() - c0) * args.steps
     total_ms = max_over_ranks(e0.elapsed_time(e1))
     ctx.synchronize()
     clocks_main = sampler.stop()
@@ -225,7 +255,7 @@ def run_b200_arm(args):
     ctx.enable_kernel_timing(True)
     ctx.kernel_times()
     for i in range(args.steps):
-        step(i)
+        eager_step(i)
     ctx.synchronize()
     (n_gu, ms_gu), (n_dn, ms_dn) = ctx.kernel_times()
     ctx.enable_kernel_timing(False)
@@ -263,13 +293,14 @@ def run_b200_arm(args):
         for Tx in (1, 8, 32):
             xe = [torch.from_numpy(W.make_tokens(cfg, Tx, bf16=True, seed_offset=50 + i)).to(dev).to(torch.bfloat16) for i in range(n_sets)]
             oe = torch.empty((Tx, cfg.n_embd), dtype=torch.float32, device=dev)
+            stepx, _ = make_stepper(xe, oe)
             for i in range(5):
-                layers[i % n_sets].forward(xe[i % n_sets], out=oe)
+                stepx(i)
             torch.cuda.synchronize()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             for i in range(args.steps):
-                layers[i % n_sets].forward(xe[i % n_sets], out=oe)
+                stepx(i)
             b.record()
             torch.cuda.synchronize()
             ms = a.elapsed_time(b) / args.steps
@@ -294,7 +325,7 @@ def run_b200_arm(args):
                            "n_ff": cfg.n_ff, "n_latent": cfg.n_latent, "weights": "NVFP4 (ggml block_nvfp4) + fp32 per-expert scale",
                            "activations": "bf16 in, int8 grid of the reference (Q8_0) inside, fp32 out",
                            "l2": f"{n_sets} distinct weight sets rotated ({n_sets * layers[0].weight_bytes() / 1e6:.0f} MB > 126 MB L2)",
-                           "experts_touched_per_step": U, "parallelism": f"replicas x{world}" if world > 1 else "single GPU"},
+                           "experts_touched_per_step": U, "launch": "eager" if args.no_graph else "CUDA graph replay (one graph per weight set)", "parallelism": f"replicas x{world}" if world > 1 else "single GPU"},
                 "e2e": e2e, "gpu_launches": launches, "clocks": clocks_main, "roofline": roofline, "cpu_baseline": cpu,
                 "other_batch_sizes": extras}
         print(json.dumps(line))

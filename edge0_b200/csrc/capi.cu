@@ -267,6 +267,40 @@ int launch_logits(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int 
     return check_launch(ctx, "router_logits");
 }
 
+template <int TT, typename XT>
+int launch_front_t(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, cudaStream_t st) {
+    Plan & p = ctx->plan;
+    const int64_t lwarps = (int64_t) l->n_expert * ((T + TT - 1) / TT);
+    const int lblocks = (int) ((lwarps * 32 + 255) / 256);
+    const int kind = l->wtype == TYPE_Q3_K ? 1 : 0;
+    const int64_t qwarps = (int64_t) T * (kind ? l->n_embd / 256 : l->n_embd / 32);
+    const int qblocks = (int) ((qwarps * 32 + 255) / 256);
+    route_front_kernel<TT, XT><<<lblocks + qblocks, 256, 0, st>>>(l->router_w, l->router_bias, x, p.logits, l->n_embd, l->n_expert, T,
+                                                                  p.groups.counts, l->n_expert, lblocks, p.xq, kind);
+    return check_launch(ctx, "route_front");
+}
+
+template <typename XT>
+int launch_front(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, cudaStream_t st) {
+    // few tokens: one warp per (expert, token) with deep load prefetch; otherwise 4 tokens share each weight load
+    return T <= 8 ? launch_front_t<1, XT>(ctx, l, x, T, st) : launch_front_t<4, XT>(ctx, l, x, T, st);
+}
+
+int launch_select_group(b200moe_ctx * ctx, const b200moe_layer * l, int T, float * probs, cudaStream_t st) {
+    Plan & p = ctx->plan;
+    const int E = l->n_expert, K = l->n_expert_used;
+    const size_t sh = (size_t) (2 * E + 1) * sizeof(int);
+#define SELG(EPL) route_select_group_kernel<EPL><<<1, 1024, sh, st>>>(p.logits, E, K, T, p.ids, p.wts, probs, p.groups, ctx->d_err)
+    if (E <= 32) SELG(1);
+    else if (E <= 64) SELG(2);
+    else if (E <= 128) SELG(4);
+    else if (E <= 256) SELG(8);
+    else if (E <= 512) SELG(16);
+    else SELG(32);
+#undef SELG
+    return check_launch(ctx, "route_select_group");
+}
+
 int launch_select(b200moe_ctx * ctx, const b200moe_layer * l, int T, int32_t * ids, float * wts, float * probs, bool count, cudaStream_t st) {
     Plan & p = ctx->plan;
     const int blocks = (T * 32 + 255) / 256;
@@ -404,15 +438,23 @@ template <typename XT>
 int layer_impl(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, float * out, const b200moe_observe * ob, cudaStream_t st) {
     Plan & p = ctx->plan;
     const int k = l->n_expert_used;
-    int rc = route_impl<XT>(ctx, l, x, T, p.ids, p.wts, ob, true, st);
-    if (rc) return rc;
-    if (!l->n_latent && (rc = launch_group(ctx, p.ids, l->n_expert, T * k, st))) return rc;
+    int rc;
+    const bool fused_front = !l->n_latent && T <= 128;  // decode-sized batches: 2 launches instead of 4
+    if (fused_front) {
+        if ((rc = launch_front<XT>(ctx, l, x, T, st))) return rc;
+        if ((rc = launch_select_group(ctx, l, T, (ob && ob->ffn_moe_probs) ? ob->ffn_moe_probs : nullptr, st))) return rc;
+        if (ob && ob->ffn_moe_logits)
+            CUDA_TRY(ctx, cudaMemcpyAsync(ob->ffn_moe_logits, p.logits, sizeof(float) * (size_t) T * l->n_expert, cudaMemcpyDeviceToDevice, st));
+    } else {
+        if ((rc = route_impl<XT>(ctx, l, x, T, p.ids, p.wts, ob, true, st))) return rc;
+        if (!l->n_latent && (rc = launch_group(ctx, p.ids, l->n_expert, T * k, st))) return rc;
+    }
     if (ob && ob->ffn_moe_topk) CUDA_TRY(ctx, cudaMemcpyAsync(ob->ffn_moe_topk, p.ids, sizeof(int32_t) * (size_t) T * k, cudaMemcpyDeviceToDevice, st));
     if (ob && ob->ffn_moe_weights_norm)
         CUDA_TRY(ctx, cudaMemcpyAsync(ob->ffn_moe_weights_norm, p.wts, sizeof(float) * (size_t) T * k, cudaMemcpyDeviceToDevice, st));
 
     if (!l->n_latent) {
-        if ((rc = launch_quantize<XT>(ctx, x, l->n_embd, p.xq, T, l->n_embd, l->wtype, st))) return rc;
+        if (!fused_front && (rc = launch_quantize<XT>(ctx, x, l->n_embd, p.xq, T, l->n_embd, l->wtype, st))) return rc;
         rc = experts_impl(ctx, l, p.xq, p.ids, p.wts, T, out, ob, st);
         account(ctx, l, T);
         return rc;

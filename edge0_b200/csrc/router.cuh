@@ -148,6 +148,79 @@ __global__ void __launch_bounds__(256) quantize_act_kernel(const XT * __restrict
     }
 }
 
+// Router logits and activation quantisation in one launch (decode path): blocks [0, n_logit_blocks) compute logits,
+// the rest quantise x for the expert matmuls.  Both only read x.
+template <int TT, typename XT>
+__global__ void __launch_bounds__(256) route_front_kernel(const float * __restrict__ W, const float * __restrict__ bias,
+                                                         const XT * __restrict__ x, float * __restrict__ logits, int H, int E, int T,
+                                                         int * __restrict__ zero_buf, int zero_n, int n_logit_blocks, ActQuant dst,
+                                                         int kind) {
+    if ((int) blockIdx.x < n_logit_blocks) {
+        if (blockIdx.x == 0)
+            for (int i = threadIdx.x; i < zero_n; i += blockDim.x) zero_buf[i] = 0;
+        const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+        const int lane = threadIdx.x & 31;
+        const int n_tt = (T + TT - 1) / TT;
+        if (warp >= E * n_tt) return;
+        const int e = warp % E;
+        const int t0 = (warp / E) * TT;
+        float acc[TT];
+#pragma unroll
+        for (int i = 0; i < TT; ++i) acc[i] = 0.0f;
+        const float * w = W + (size_t) e * H;
+        // The FMA chain of a lane is sequential by definition of the reference's order, but its loads are not:
+        // fetch CH steps of weights and activations at once, then run the chain over them.
+        constexpr int CH = TT == 1 ? 32 : 8;
+        for (int j0 = lane; j0 < H; j0 += 32 * CH) {
+            float wv[CH], xv[TT][CH];
+#pragma unroll
+            for (int c = 0; c < CH; ++c) {
+                const int j = j0 + 32 * c;
+                wv[c] = j < H ? __ldg(w + j) : 0.0f;
+#pragma unroll
+                for (int i = 0; i < TT; ++i) {
+                    const int t = min(t0 + i, T - 1);
+                    xv[i][c] = j < H ? (float) x[(size_t) t * H + j] : 0.0f;
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < CH; ++c)
+                if (j0 + 32 * c < H) {
+#pragma unroll
+                    for (int i = 0; i < TT; ++i) acc[i] = __fmaf_rn(wv[c], xv[i][c], acc[i]);
+                }
+        }
+#pragma unroll
+        for (int i = 0; i < TT; ++i) {
+            float v = acc[i];
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 16));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 8));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+            if (lane == 0 && t0 + i < T) {
+                if (bias) v = __fadd_rn(v, bias[e]);
+                logits[(size_t) (t0 + i) * E + e] = v;
+            }
+        }
+        return;
+    }
+    const int warp = (((int) blockIdx.x - n_logit_blocks) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (kind == 0) {
+        const int nb = H / 32;
+        if (warp >= T * nb) return;
+        const int r = warp / nb, b = warp % nb;
+        quantize_q8_0_block(x + (size_t) r * H + b * 32, dst.q + (size_t) r * H + b * 32, dst.d + (size_t) r * nb + b, lane);
+    } else {
+        const int nb = H / 256;
+        if (warp >= T * nb) return;
+        const int r = warp / nb, b = warp % nb;
+        quantize_q8_K_block(x + (size_t) r * H + b * 256, dst.q + (size_t) r * H + b * 256, dst.d + (size_t) r * nb + b,
+                            dst.bsum + (size_t) r * (H / 16) + b * 16, lane);
+    }
+}
+
 // ---- K1: softmax + top-k + renormalise, one warp per token ---------------------------------------------
 // soft_max (ggml-cpu/ops.cpp:5584-5694, vec.cpp:531-551): exp via ggml_v_expf, groups of 8 summed in fp32 as
 // ((v0+v4)+(v2+v6))+((v1+v5)+(v3+v7)), groups accumulated in double, p = exp * (float)(1/sum).
@@ -155,13 +228,10 @@ __global__ void __launch_bounds__(256) quantize_act_kernel(const XT * __restrict
 // weights = p[ids] / max((float)sum_double(p[ids]), 2^-14) (forward.cpp:268-269).
 // Also counts rows per expert and remembers each row's arrival position for the grouping kernel.
 template <int EPL>  // experts per lane; E <= 32*EPL, E % 8 == 0
-__global__ void __launch_bounds__(256) route_select_kernel(const float * __restrict__ logits, int E, int K, int T,
-                                                          int32_t * __restrict__ ids, float * __restrict__ weights,
-                                                          float * __restrict__ probs_out, int * __restrict__ counts,
-                                                          int * __restrict__ pos) {
-    const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (t >= T) return;
+__device__ __forceinline__ void route_select_token(const float * __restrict__ logits, int E, int K, int t, int lane,
+                                                   int32_t * __restrict__ ids, float * __restrict__ weights,
+                                                   float * __restrict__ probs_out, int * __restrict__ counts,
+                                                   int * __restrict__ pos) {
     const float * l = logits + (size_t) t * E;
 
     // lane owns experts e = lane*EPL + i  (contiguous, so a group of 8 experts sits in 8/EPL lanes or one lane)
@@ -239,6 +309,16 @@ __global__ void __launch_bounds__(256) route_select_kernel(const float * __restr
     }
 }
 
+template <int EPL>
+__global__ void __launch_bounds__(256) route_select_kernel(const float * __restrict__ logits, int E, int K, int T,
+                                                          int32_t * __restrict__ ids, float * __restrict__ weights,
+                                                          float * __restrict__ probs_out, int * __restrict__ counts,
+                                                          int * __restrict__ pos) {
+    const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (t >= T) return;
+    route_select_token<EPL>(logits, E, K, t, threadIdx.x & 31, ids, weights, probs_out, counts, pos);
+}
+
 // ---- K2: grouping ----------------------------------------------------------------------------------------
 // Group descriptor produced for the expert kernels (reference: matrix_rows / matrix_row_counts in
 // ggml_compute_forward_mul_mat_id, ggml-cpu/ggml-cpu.c:1648-1663):
@@ -255,35 +335,47 @@ struct Groups {
     int * cost;     // [3][E+1]: prefix over active experts of ceil(rows/nt) for nt = 1, 2, 4 (work per weight row)
 };
 
-// Single block.  counts must be final (selection kernel finished).
-__global__ void __launch_bounds__(1024) group_scan_kernel(Groups g, const int32_t * __restrict__ ids, int E, int rows, int * err) {
-    extern __shared__ int sh[];  // [E+1] offsets, [E] active flags scan
+// Block-wide: counts must be final and visible to this block.
+__device__ __forceinline__ void group_scan_body(Groups g, const int32_t * __restrict__ ids, int E, int rows, int * err, int * sh) {
     int * off = sh;
-    int * act = sh + (E + 1);
+    int * act = sh + (E + 1);  // act[a] = a-th active expert (also written to g.active)
     const int tid = threadIdx.x;
-    // exclusive scan of counts (E <= 1024): simple Hillis-Steele in shared memory
-    for (int e = tid; e < E; e += blockDim.x) { off[e] = g.counts[e]; act[e] = g.counts[e] > 0 ? 1 : 0; }
-    __syncthreads();
-    if (tid == 0) {
-        int run = 0, na = 0;
-        for (int e = 0; e < E; ++e) {
-            const int c = off[e];
-            off[e] = run;
-            run += c;
-            if (act[e]) g.active[na++] = e;
+    if (tid < 32) {
+        // warp 0: exclusive scan of counts, compaction of active experts and the three work prefixes, 32 experts a step
+        int run = 0, na = 0, c1 = 0, c2 = 0, c4 = 0;
+        for (int base = 0; base < E; base += 32) {
+            const int e = base + tid;
+            const int n = e < E ? g.counts[e] : 0;
+            int incl = n, w2 = (n + 1) / 2, w4 = (n + 3) / 4;
+            int i2 = w2, i4 = w4;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int a = __shfl_up_sync(0xffffffffu, incl, o), b = __shfl_up_sync(0xffffffffu, i2, o), c = __shfl_up_sync(0xffffffffu, i4, o);
+                if (tid >= o) { incl += a; i2 += b; i4 += c; }
+            }
+            if (e < E) off[e] = run + incl - n;
+            const unsigned m = __ballot_sync(0xffffffffu, n > 0);
+            if (n > 0) {
+                const int a = na + __popc(m & ((1u << tid) - 1));
+                act[a] = e;
+                g.active[a] = e;
+                g.cost[a] = c1 + incl - n;
+                g.cost[(E + 1) + a] = c2 + i2 - w2;
+                g.cost[2 * (E + 1) + a] = c4 + i4 - w4;
+            }
+            run += __shfl_sync(0xffffffffu, incl, 31);
+            c1 += __shfl_sync(0xffffffffu, incl, 31);
+            c2 += __shfl_sync(0xffffffffu, i2, 31);
+            c4 += __shfl_sync(0xffffffffu, i4, 31);
+            na += __popc(m);
         }
-        off[E] = run;
-        int c1 = 0, c2 = 0, c4 = 0;
-        for (int a = 0; a < na; ++a) {
-            const int e = g.active[a];
-            const int n = off[e + 1 <= E ? e + 1 : E] - off[e];
-            g.cost[a] = c1; g.cost[(E + 1) + a] = c2; g.cost[2 * (E + 1) + a] = c4;
-            c1 += n; c2 += (n + 1) / 2; c4 += (n + 3) / 4;
+        if (tid == 0) {
+            off[E] = run;
+            g.cost[na] = c1; g.cost[(E + 1) + na] = c2; g.cost[2 * (E + 1) + na] = c4;
+            g.meta[0] = na;
+            g.meta[1] = run;
+            if (run != rows) report_error(err, DEV_ERR_BAD_SHAPE);
         }
-        g.cost[na] = c1; g.cost[(E + 1) + na] = c2; g.cost[2 * (E + 1) + na] = c4;
-        g.meta[0] = na;
-        g.meta[1] = run;
-        if (run != rows) report_error(err, DEV_ERR_BAD_SHAPE);
     }
     __syncthreads();
     for (int e = tid; e <= E; e += blockDim.x) g.offsets[e] = off[e];
@@ -292,6 +384,24 @@ __global__ void __launch_bounds__(1024) group_scan_kernel(Groups g, const int32_
         if (e < 0 || e >= E) { report_error(err, DEV_ERR_BAD_EXPERT_ID); continue; }
         g.perm[off[e] + g.pos[r]] = r;
     }
+}
+
+// Single block.  counts must be final (selection kernel finished).
+__global__ void __launch_bounds__(1024) group_scan_kernel(Groups g, const int32_t * __restrict__ ids, int E, int rows, int * err) {
+    extern __shared__ int sh[];  // [E+1] offsets, [E] active flags
+    group_scan_body(g, ids, E, rows, err, sh);
+}
+
+// Small batches: selection for every token and the grouping in ONE single-block launch (one warp per token, looping).
+template <int EPL>
+__global__ void __launch_bounds__(1024) route_select_group_kernel(const float * __restrict__ logits, int E, int K, int T,
+                                                                 int32_t * __restrict__ ids, float * __restrict__ weights,
+                                                                 float * __restrict__ probs_out, Groups g, int * err) {
+    extern __shared__ int sh[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int t = warp; t < T; t += nw) route_select_token<EPL>(logits, E, K, t, lane, ids, weights, probs_out, g.counts, g.pos);
+    __syncthreads();  // global writes of this block (counts, pos, ids) are visible to the whole block afterwards
+    group_scan_body(g, ids, E, T * K, err, sh);
 }
 
 // Counting pass for routing that was not produced by route_select_kernel (ids given by the caller,
