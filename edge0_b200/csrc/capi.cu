@@ -165,7 +165,7 @@ int validate_layer(b200moe_ctx * ctx, const b200moe_layer * l) {
     return B200MOE_OK;
 }
 
-int ensure_plan(b200moe_ctx * ctx, int n_embd, int n_in, int n_expert, int k, int n_ff, int wtype, int tokens) {
+int ensure_plan(b200moe_ctx * ctx, int n_embd, int n_in, int n_expert, int k, int n_ff, int wtype, int tokens, cudaStream_t st = nullptr) {
     Plan & p = ctx->plan;
     if (p.max_tokens >= tokens && p.n_embd == n_embd && p.n_in == n_in && p.n_expert == n_expert && p.k == k && p.n_ff == n_ff &&
         p.wtype == wtype && ctx->scratch.base)
@@ -189,7 +189,7 @@ int ensure_plan(b200moe_ctx * ctx, int n_embd, int n_in, int n_expert, int k, in
         ctx->scratch.bytes = np.total;
     }
     carve(np, ctx->scratch.base);
-    CUDA_TRY(ctx, cudaMemset(np.one_group_ids, 0, sizeof(int) * np.max_tokens));
+    CUDA_TRY(ctx, cudaMemsetAsync(np.one_group_ids, 0, sizeof(int) * np.max_tokens, st));
     ctx->plan = np;
     return B200MOE_OK;
 }
@@ -379,6 +379,16 @@ int dense_matvec(b200moe_ctx * ctx, int wtype, const void * w, const float * sca
         if ((rc = check_launch(ctx, "scale_rows"))) return rc;
     }
     return B200MOE_OK;
+}
+
+__global__ void gather_rows_kernel(const float4 * __restrict__ src, const int * __restrict__ idx, float4 * __restrict__ dst, int n_rows,
+                                   int w4, int src_rows) {
+    const int r = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n_rows || c >= w4) return;
+    const int s = idx[r];
+    if (s < 0 || s >= src_rows) return;  // out-of-range index: leave the row untouched rather than read outside src
+    dst[(size_t) r * w4 + c] = src[(size_t) s * w4 + c];
 }
 
 int read_device_error(b200moe_ctx * ctx, cudaStream_t st) {
@@ -752,6 +762,42 @@ int b200moe_mul_mat_id(b200moe_ctx * ctx, int wtype, const void * as, int64_t ne
     if ((rc = launch_group(ctx, p.ids, (int) n_as, rows, st))) return rc;
     GemvParams g = gemv_params(ctx, as, nullptr, nullptr, nullptr, p.hq, dst, (int) ne01, (int) n_ids, (int) ne11, (int) n_as);
     return launch_gemv<false>(ctx, wtype, (int) ne00, g, tokens_per_pass(rows, (int) n_as), st);
+}
+
+int b200moe_mul_mat(b200moe_ctx * ctx, int wtype, const void * w, int64_t ne00, int64_t ne01, const float * x, int64_t T, const float * scale,
+                    float * dst, void * stream) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    if (T == 0) return B200MOE_OK;
+    if (!w || !x || !dst || ne00 <= 0 || ne01 <= 0 || T < 0) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer or non-positive size");
+    if ((uintptr_t) w & 15) return fail(ctx, B200MOE_ERR_INVALID_ARG, "weight tensor must be 16-byte aligned");
+    if (!gemv_supported(wtype, ne00) || ne01 % 8) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no kernel for type %d, K=%lld", wtype, (long long) ne00);
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc = ensure_plan(ctx, (int) ne00, (int) ne00, 8, 1, (int) ne00, wtype, (int) T, st);
+    if (rc) return rc;
+    return dense_matvec(ctx, wtype, w, scale, x, ctx->plan.xq, (int) ne00, (int) ne01, (int) T, dst, st);
+}
+
+int b200moe_combine(b200moe_ctx * ctx, const float * y, const float * weights, float * out, int64_t n, int64_t k, int64_t T, void * stream) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    if (T == 0) return B200MOE_OK;
+    if (!y || !weights || !out || n <= 0 || k <= 0 || T < 0 || n % 4) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer, non-positive size or width not a multiple of 4");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    dim3 grid((unsigned) ((n / 4 + 255) / 256), (unsigned) T);
+    combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(y, weights, out, (int) n, (int) k, (int) T);
+    return check_launch(ctx, "combine");
+}
+
+int b200moe_gather_rows(b200moe_ctx * ctx, const float * src, int64_t src_rows, const int32_t * idx, float * dst, int64_t n_rows, int64_t width,
+                        void * stream) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    if (n_rows == 0) return B200MOE_OK;
+    if (!src || !idx || !dst || n_rows < 0 || src_rows <= 0 || width <= 0 || width % 4) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer, bad size or width not a multiple of 4");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    dim3 grid((unsigned) ((width / 4 + 255) / 256), (unsigned) n_rows);
+    gather_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const float4 *>(src), idx, reinterpret_cast<float4 *>(dst),
+                                                                            (int) n_rows, (int) (width / 4), (int) src_rows);
+    return check_launch(ctx, "gather_rows");
 }
 
 int b200moe_ffn(b200moe_ctx * ctx, const b200moe_layer * l, const void * x, int x_type, int32_t T, const int32_t * ids, const float * weights,

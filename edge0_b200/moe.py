@@ -109,6 +109,26 @@ class Context:
         self.check(self.lib.b200moe_kernel_times(self.handle, n, ms))
         return [(int(n[0]), float(ms[0])), (int(n[1]), float(ms[1]))]
 
+    def mul_mat(self, wtype: int, w: torch.Tensor, x: torch.Tensor, ne00: int, scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """w uint8 [ne01, row_bytes]; x float32 [T, ne00] -> float32 [T, ne01] (ggml_mul_mat with a quantised matrix)."""
+        T, ne01 = x.shape[0], w.shape[0]
+        dst = torch.empty((T, ne01), dtype=torch.float32, device=x.device)
+        self.check(self.lib.b200moe_mul_mat(self.handle, wtype, _ptr(w), ne00, ne01, _ptr(x), T, _ptr(scale), _ptr(dst), self._stream()))
+        return dst
+
+    def combine(self, y: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        """y float32 [T, k, n], weights float32 [T, k] -> float32 [T, n], slots added in order."""
+        T, k, n = y.shape
+        out = torch.empty((T, n), dtype=torch.float32, device=y.device)
+        self.check(self.lib.b200moe_combine(self.handle, _ptr(y), _ptr(weights), _ptr(out), n, k, T, self._stream()))
+        return out
+
+    def gather_rows(self, src: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+        """src float32 [R, n], idx int32 [m] -> float32 [m, n]."""
+        dst = torch.empty((idx.shape[0], src.shape[1]), dtype=torch.float32, device=src.device)
+        self.check(self.lib.b200moe_gather_rows(self.handle, _ptr(src), src.shape[0], _ptr(idx), _ptr(dst), idx.shape[0], src.shape[1], self._stream()))
+        return dst
+
     def mul_mat_id(self, wtype: int, experts: torch.Tensor, b: torch.Tensor, ids: torch.Tensor, ne00: int) -> torch.Tensor:
         """experts uint8 [n_as, ne01, row_bytes]; b float32 [T, ne11, ne00]; ids int32 [T, n_ids] (may be a
         column slice of a wider tensor) -> float32 [T, n_ids, ne01]."""
@@ -135,7 +155,7 @@ class MoeLayer:
     """Weights of one MoE FFN layer on one GPU plus the calls the reference graph makes on them."""
 
     def __init__(self, ctx: Context, *, wtype: int, top_k: int, router_w, gate, up, down, router_bias=None, gate_scale=None,
-                 up_scale=None, down_scale=None, lat_down=None, lat_up=None, lat_down_scale=None, lat_up_scale=None):
+                 up_scale=None, down_scale=None, lat_down=None, lat_up=None, lat_down_scale=None, lat_up_scale=None, check_shapes=True):
         dev = torch.device("cuda", ctx.device)
 
         def put(a, dtype):
@@ -156,9 +176,9 @@ class MoeLayer:
         self.n_ff = self.gate.shape[1]
         self.n_latent = 0 if self.lat_down is None else self.lat_down.shape[0]
         self.n_in = self.n_latent or self.n_embd
-        if self.gate.shape != (self.n_expert, self.n_ff, row_size(wtype, self.n_in)):
+        if check_shapes and self.gate.shape != (self.n_expert, self.n_ff, row_size(wtype, self.n_in)):
             raise ValueError(f"gate tensor has shape {tuple(self.gate.shape)}")
-        if self.down.shape != (self.n_expert, self.n_in, row_size(wtype, self.n_ff)):
+        if check_shapes and self.down.shape != (self.n_expert, self.n_in, row_size(wtype, self.n_ff)):
             raise ValueError(f"down tensor has shape {tuple(self.down.shape)}")
         self.desc = Layer(n_embd=self.n_embd, n_latent=self.n_latent, n_expert=self.n_expert, n_expert_used=top_k, n_ff=self.n_ff,
                           wtype=wtype)

@@ -137,6 +137,22 @@ B200MOE_API int b200moe_mul_mat_id(b200moe_ctx * ctx, int wtype, const void * as
                                    const float * b, int64_t ne11, const int32_t * ids, int64_t n_ids, int64_t ids_nb1,
                                    int64_t n_tokens, float * dst, void * stream);
 
+/* ggml_mul_mat with a quantised weight matrix (ggml-cpu/ggml-cpu.c:1255-1468): dst F32 [ne01, T] = W [ne00, ne01] . x F32 [ne00, T],
+ * x quantised to the type's vec_dot_type first; optional fp32 scale[1] multiplies the result (NVFP4 tensor scale).
+ * Used for the shared latent projections of the expert-parallel layer. */
+B200MOE_API int b200moe_mul_mat(b200moe_ctx * ctx, int wtype, const void * w, int64_t ne00, int64_t ne01, const float * x, int64_t n_tokens,
+                                const float * scale, float * dst, void * stream);
+
+/* The tail of Builder::ffn (forward.cpp:308-310): out[:, t] = sum over slots s = 0..k-1, in that order, of y[:, s, t] * weights[s, t].
+ * y F32 [n, k, T], weights F32 [k, T], out F32 [n, T]. */
+B200MOE_API int b200moe_combine(b200moe_ctx * ctx, const float * y, const float * weights, float * out, int64_t n, int64_t k, int64_t n_tokens,
+                                void * stream);
+
+/* ggml_get_rows on F32 rows (ggml-cpu/ops.cpp get_rows): dst[r, :] = src[idx[r], :]; used to pack rows for token dispatch and to put
+ * returned rows back into slot order.  width must be a multiple of 4. */
+B200MOE_API int b200moe_gather_rows(b200moe_ctx * ctx, const float * src, int64_t src_rows, const int32_t * idx, float * dst, int64_t n_rows,
+                                    int64_t width, void * stream);
+
 /* Builder::ffn with given routing (forward.cpp:300-311): gate/up mul_mat_id -> silu*up -> down mul_mat_id ->
  * * weights -> sum over slots in slot order.  x: [n_in, T] in x_type; out F32 [n_in, T]. */
 B200MOE_API int b200moe_ffn(b200moe_ctx * ctx, const b200moe_layer * layer, const void * x, int x_type, int32_t n_tokens,
