@@ -333,10 +333,124 @@ def run_b200_arm(args):
         dist.destroy_process_group()
 
 
+def run_c5_arm(args):
+    """Expert-parallel latent layer (hidden 4096 -> latent 1024, 512 experts, top-10, intermediate 1024), 256 tokens in
+    total whatever N is: experts are sharded 512/N per GPU, tokens T/N per GPU, token dispatch and combine are NCCL
+    all-to-alls.  Strong scaling: value = 256 tokens / max-over-ranks step time."""
+    import torch
+    import torch.distributed as dist
+
+    from edge0_b200 import moe
+    from edge0_b200 import workloads as W
+    from edge0_b200.expert_parallel import CudaBackend, ExpertParallelLayer, token_range
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the MoE path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg, T = workload_config(args)
+    ctx = moe.Context(local)
+    per = cfg.n_expert // world
+    n_sets = max(1, args.weight_sets)
+    eps, xs = [], []
+    lo, hi = token_range(T, world, rank)
+    for i in range(n_sets):
+        host = W.make_layer(cfg, seed_offset=i, expert_range=(rank * per, (rank + 1) * per))
+        eps.append(ExpertParallelLayer(CudaBackend(ctx, host, rank, world), cfg.n_expert, cfg.top_k, rank, world))
+        x = W.make_tokens(cfg, T, bf16=True, seed_offset=i)[lo:hi]
+        xs.append(torch.from_numpy(np.ascontiguousarray(x)).to(dev))
+        del host
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step(i):
+        return eps[i % n_sets].forward(xs[i % n_sets])
+
+    for i in range(args.warmup):
+        step(i)
+    ctx.synchronize()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    l0 = ctx.launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    launches = ctx.launches() - l0
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ctx.synchronize()
+    clocks = sampler.stop()
+    # end to end: this rank's tokens start in pinned host memory and the result returns to the host every step
+    xh = [x.cpu().pin_memory() for x in xs]
+    oh = torch.empty((hi - lo, cfg.n_embd), dtype=torch.float32).pin_memory()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for i in range(args.steps):
+        xd = xh[i % n_sets].to(dev, non_blocking=True)
+        oh.copy_(eps[i % n_sets].forward(xd), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    f1.record()
+    barrier()
+    e2e_ms = f0.elapsed_time(f1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    ids, _ = eps[0].b.route(xs[0])
+    touched = torch.zeros(cfg.n_expert, device=dev)
+    touched[ids.reshape(-1).long()] = 1
+    if world > 1:
+        dist.all_reduce(touched)
+    U = int((touched > 0).sum().item())
+    alg = W.algorithmic_bytes(cfg, T, U, 4)
+    step_ms = ms / args.steps
+    if rank == 0:
+        line = {"metric": METRIC, "value": T * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "int8 x fp4 integer dots, fp32 accumulate", "data": "synthetic",
+                "config": {"workload": f"{cfg.name} T={T} total", "n_embd": cfg.n_embd, "n_latent": cfg.n_latent, "n_expert": cfg.n_expert,
+                           "top_k": cfg.top_k, "n_ff": cfg.n_ff, "parallelism": f"ep{world} (experts {per}/GPU, tokens {T // world}/GPU, NCCL all-to-all dispatch+combine)",
+                           "l2": f"{n_sets} distinct weight sets rotated", "experts_touched_per_step": U, "launch": "eager"},
+                "e2e": {"value": T * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * cfg.n_embd * 4,
+                        "d2h_bytes_per_step": T * cfg.n_embd * 4, "ms_per_step": e2e_ms / args.steps},
+                "gpu_launches": launches, "clocks": clocks,
+                "roofline": {"bound": "hbm", "kernel": "whole step (all ranks)", "achieved": alg / (step_ms * 1e-3) / 1e9, "peak": peak * world, "unit": "GB/s",
+                             "frac": alg / (step_ms * 1e-3) / 1e9 / (peak * world), "traffic": None, "algorithmic_bytes_per_step": alg,
+                             "peak_source": "measured copy bandwidth x N"},
+                "cpu_baseline": None}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "c5_latent":
+        run_c5_arm(args)
     else:
         run_b200_arm(args)
 

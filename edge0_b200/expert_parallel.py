@@ -118,7 +118,11 @@ class CudaBackend:
         self.ctx, self.cfg = ctx, cfg
         E, per = cfg.n_expert, cfg.n_expert // world
         lo, hi = rank * per, (rank + 1) * per
-        sl = lambda a: None if a is None else a[lo:hi]
+        if host_layer.gate.shape[0] == per and world > 1:      # generated for this shard only (make_layer(expert_range=...))
+            assert host_layer.expert_lo == lo
+            sl = lambda a: a
+        else:
+            sl = lambda a: None if a is None else a[lo:hi]
         dev = torch.device("cuda", ctx.device)
         put = lambda a, dt: None if a is None else torch.from_numpy(np.ascontiguousarray(a)).to(dev, dt)
         # full layer descriptor for routing (router only needs router_w; expert pointers point at the local shard)

@@ -64,6 +64,7 @@ class HostLayer:
     lat_up: Optional[np.ndarray] = None
     lat_down_scale: Optional[np.ndarray] = None
     lat_up_scale: Optional[np.ndarray] = None
+    expert_lo: int = 0   # first expert held in gate/up/down when the layer was generated for a shard
 
     def kwargs(self) -> dict:
         """Keyword arguments shared by edge0_b200.moe.MoeLayer and the checkers' moe_layer."""
@@ -89,35 +90,49 @@ def _quantize(wtype: int, w: np.ndarray, quantize_q3k: Optional[Callable]) -> np
     return quantize_q3k(w)
 
 
-def _matrix(rng, shape, wtype, scaled, quantize_q3k, chunk_experts=32):
-    """Draw and quantise [E, rows, n] in chunks of experts to bound host memory."""
+CHUNK_EXPERTS = 32
+
+
+def _matrix(seed_key, shape, wtype, scaled, quantize_q3k, expert_range=None):
+    """Draw and quantise [E, rows, n] in chunks of CHUNK_EXPERTS experts.  Every chunk has its own seeded generator, so
+    a rank that owns only some experts draws only their chunks and still gets the same bytes as a full draw."""
     E = shape[0]
+    lo, hi = expert_range if expert_range is not None else (0, E)
     outs, scales = [], []
-    for e0 in range(0, E, chunk_experts):
-        e1 = min(E, e0 + chunk_experts)
+    for e0 in range(0, E, CHUNK_EXPERTS):
+        e1 = min(E, e0 + CHUNK_EXPERTS)
+        if e1 <= lo or e0 >= hi:
+            continue
+        rng = np.random.default_rng(list(seed_key) + [e0 // CHUNK_EXPERTS])
         w = rng.normal(0.0, 0.02, (e1 - e0,) + tuple(shape[1:])).astype(np.float32)
+        a, b = max(lo, e0) - e0, min(hi, e1) - e0
+        w = w[a:b]
         if scaled:
-            s = (np.abs(w).reshape(e1 - e0, -1).max(axis=1) / np.float32(6 * 448)).astype(np.float32)
+            s = (np.abs(w).reshape(b - a, -1).max(axis=1) / np.float32(6 * 448)).astype(np.float32)
             w = w / s[:, None, None]
             scales.append(s)
         outs.append(_quantize(wtype, w, quantize_q3k))
     return np.concatenate(outs, axis=0), (np.concatenate(scales) if scaled else None)
 
 
-def make_layer(cfg: LayerConfig, quantize_q3k: Optional[Callable] = None, seed_offset: int = 0) -> HostLayer:
-    rng = np.random.default_rng(cfg.seed + 7919 * seed_offset)
+def make_layer(cfg: LayerConfig, quantize_q3k: Optional[Callable] = None, seed_offset: int = 0, expert_range=None) -> HostLayer:
+    """expert_range=(lo, hi): only those experts' gate/up/down (and scales) are generated; router and latent projections are
+    always complete."""
+    seed = cfg.seed + 7919 * seed_offset
+    rng = np.random.default_rng([seed, 0])
     E, H, I, n_in = cfg.n_expert, cfg.n_embd, cfg.n_ff, cfg.n_in
     scaled = cfg.wtype == TYPE_NVFP4 and cfg.tensor_scales
     router_w = rng.normal(0.0, 0.02, (E, H)).astype(np.float32)
-    gate, sg = _matrix(rng, (E, I, n_in), cfg.wtype, scaled, quantize_q3k)
-    up, su = _matrix(rng, (E, I, n_in), cfg.wtype, scaled, quantize_q3k)
-    down, sd = _matrix(rng, (E, n_in, I), cfg.wtype, scaled, quantize_q3k)
+    gate, sg = _matrix([seed, 1], (E, I, n_in), cfg.wtype, scaled, quantize_q3k, expert_range)
+    up, su = _matrix([seed, 2], (E, I, n_in), cfg.wtype, scaled, quantize_q3k, expert_range)
+    down, sd = _matrix([seed, 3], (E, n_in, I), cfg.wtype, scaled, quantize_q3k, expert_range)
     layer = HostLayer(cfg, router_w, gate, up, down, gate_scale=sg, up_scale=su, down_scale=sd)
+    layer.expert_lo = expert_range[0] if expert_range is not None else 0
     if cfg.router_bias:
         layer.router_bias = rng.normal(0.0, 1.0, E).astype(np.float32)
     if cfg.n_latent:
-        d, s_d = _matrix(rng, (1, cfg.n_latent, H), cfg.wtype, scaled, quantize_q3k)
-        u, s_u = _matrix(rng, (1, H, cfg.n_latent), cfg.wtype, scaled, quantize_q3k)
+        d, s_d = _matrix([seed, 4], (1, cfg.n_latent, H), cfg.wtype, scaled, quantize_q3k)
+        u, s_u = _matrix([seed, 5], (1, H, cfg.n_latent), cfg.wtype, scaled, quantize_q3k)
         layer.lat_down, layer.lat_up = d[0], u[0]
         layer.lat_down_scale, layer.lat_up_scale = s_d, s_u
     return layer
