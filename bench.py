@@ -309,6 +309,28 @@ def run_b200_arm(args):
             extras[f"T={Tx}"] = {"tokens_per_s": Tx / (ms * 1e-3), "ms_per_step": ms, "experts_touched": Ux,
                                  "hbm_gbs": by / (ms * 1e-3) / 1e9, "frac_of_peak": by / (ms * 1e-3) / 1e9 / peak}
         ctx.synchronize()
+        # the Q3_K one-token decode configuration (hidden 2048, 128 experts, top-8, intermediate 768), same rotation scheme
+        cfg1 = W.CONFIGS["c1_q3k"]
+        host1 = W.make_layer(cfg1)
+        layers_saved, layers[:] = list(layers), [roll_layer(host1, 17 * i).to_device(ctx) if i else host1.to_device(ctx) for i in range(n_sets)]
+        x1 = [torch.from_numpy(W.make_tokens(cfg1, 1, seed_offset=70 + i)).to(dev) for i in range(n_sets)]
+        o1 = torch.empty((1, cfg1.n_embd), dtype=torch.float32, device=dev)
+        step1, _ = make_stepper(x1, o1)
+        for i in range(5):
+            step1(i)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(args.steps):
+            step1(i)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / args.steps
+        by = W.algorithmic_bytes(cfg1, 1, cfg1.top_k, 4)
+        extras["c1_q3k T=1"] = {"tokens_per_s": 1 / (ms * 1e-3), "ms_per_step": ms, "experts_touched": cfg1.top_k, "algorithmic_bytes": by,
+                                "hbm_gbs": by / (ms * 1e-3) / 1e9, "frac_of_peak": by / (ms * 1e-3) / 1e9 / peak}
+        layers[:] = layers_saved
+        ctx.synchronize()
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -670,6 +670,145 @@ int b200moe_quantize_nvfp4_host(const float * src, void * dst, int64_t nrows, in
     return B200MOE_OK;
 }
 
+// ---- Q3_K weight quantiser: the algorithm of quantize_row_q3_K_ref (ggml-quants.c:1229-1303) with its helper
+// make_q3_quants (ggml-quants.c:697-754).  Per 16 values: a scale from an iterative weighted least-squares fit of codes in
+// [-4,3]; the 16 scales of a super-block are then quantised to 6 bits against the largest one and the codes re-derived.
+static inline int q3_nearest_int(float f) {
+    float v = f + 12582912.f;
+    int i;
+    memcpy(&i, &v, 4);
+    return (i & 0x007fffff) - 0x00400000;
+}
+
+static float q3_fit_scale16(const float * x, int8_t * L) {
+    const int n = 16, nmax = 4;
+    float max = 0, amax = 0;
+    for (int i = 0; i < n; ++i) { const float ax = std::fabs(x[i]); if (ax > amax) { amax = ax; max = x[i]; } }
+    if (amax < 1e-15f) { for (int i = 0; i < n; ++i) L[i] = 0; return 0.f; }
+    const float iscale = -nmax / max;
+    float sumlx = 0, suml2 = 0;
+    for (int i = 0; i < n; ++i) {
+        int l = q3_nearest_int(iscale * x[i]);
+        l = std::max(-nmax, std::min(nmax - 1, l));
+        L[i] = (int8_t) l;
+        const float w = x[i] * x[i];
+        sumlx += w * x[i] * l;
+        suml2 += w * l * l;
+    }
+    for (int itry = 0; itry < 5; ++itry) {
+        int changed = 0;
+        for (int i = 0; i < n; ++i) {
+            const float w = x[i] * x[i];
+            float slx = sumlx - w * x[i] * L[i];
+            if (slx > 0) {
+                float sl2 = suml2 - w * L[i] * L[i];
+                int nl = q3_nearest_int(x[i] * sl2 / slx);
+                nl = std::max(-nmax, std::min(nmax - 1, nl));
+                if (nl != L[i]) {
+                    slx += w * x[i] * nl;
+                    sl2 += w * nl * nl;
+                    if (sl2 > 0 && slx * slx * suml2 > sumlx * sumlx * sl2) { L[i] = (int8_t) nl; sumlx = slx; suml2 = sl2; ++changed; }
+                }
+            }
+        }
+        if (!changed) break;
+    }
+    for (int i = 0; i < n; ++i) L[i] += nmax;
+    return suml2 > 0.0f ? sumlx / suml2 : 0.0f;
+}
+
+static uint16_t f32_to_f16_rne(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    const uint16_t sign = (uint16_t) ((u >> 16) & 0x8000u);
+    const uint32_t a = u & 0x7fffffffu;
+    if (a >= 0x7f800000u) return (uint16_t) (sign | 0x7c00u | (a > 0x7f800000u ? 0x200u : 0));
+    if (a >= 0x477ff000u) return (uint16_t) (sign | 0x7c00u);
+    if (a < 0x33000001u) return sign;
+    const int exp = (int) (a >> 23) - 127;
+    uint32_t man = (a & 0x7fffffu) | 0x800000u, base;
+    int shift;
+    if (exp < -14) { shift = 13 + (-14 - exp); base = 0; } else { shift = 13; base = (uint32_t) (exp + 15) << 10; man &= 0x7fffffu; }
+    uint32_t q = man >> shift;
+    const uint32_t rem = man & ((1u << shift) - 1), half = 1u << (shift - 1);
+    if (rem > half || (rem == half && (q & 1))) q++;
+    return (uint16_t) (sign | (base + q));
+}
+
+static float f16_to_f32(uint16_t hb) {
+    const uint32_t sign = (uint32_t) (hb & 0x8000) << 16, ex = (hb >> 10) & 31, mn = hb & 1023;
+    float d;
+    if (ex == 0) d = std::ldexp((float) mn, -24);
+    else if (ex == 31) d = INFINITY;
+    else { uint32_t u = ((ex + 112) << 23) | (mn << 13); memcpy(&d, &u, 4); }
+    return sign ? -d : d;
+}
+
+static void quantize_row_q3_K(const float * x, uint8_t * y, int64_t k) {
+    int8_t L[256];
+    float scales[16];
+    for (int64_t b = 0; b < k / 256; ++b, x += 256) {
+        uint8_t * blk = y + b * 110;
+        uint8_t * hmask = blk, * qs = blk + 32, * sc12 = blk + 96;
+        float max_scale = 0, amax = 0;
+        for (int j = 0; j < 16; ++j) {
+            scales[j] = q3_fit_scale16(x + 16 * j, L + 16 * j);
+            const float sc = std::fabs(scales[j]);
+            if (sc > amax) { amax = sc; max_scale = scales[j]; }
+        }
+        memset(sc12, 0, 12);
+        uint16_t dh = 0;
+        if (max_scale) {
+            const float iscale = -32.f / max_scale;
+            for (int j = 0; j < 16; ++j) {
+                int8_t l = (int8_t) q3_nearest_int(iscale * scales[j]);
+                l = (int8_t) (std::max(-32, std::min(31, (int) l)) + 32);
+                if (j < 8) sc12[j] = l & 0xF; else sc12[j - 8] |= ((l & 0xF) << 4);
+                l >>= 4;
+                sc12[j % 4 + 8] |= (l << (2 * (j / 4)));
+            }
+            dh = f32_to_f16_rne(1 / iscale);
+        }
+        memcpy(blk + 108, &dh, 2);
+        const float dd = f16_to_f32(dh);
+        for (int j = 0; j < 16; ++j) {
+            int sc = j < 8 ? sc12[j] & 0xF : sc12[j - 8] >> 4;
+            sc = (sc | (((sc12[8 + j % 4] >> (2 * (j / 4))) & 3) << 4)) - 32;
+            const float d = dd * sc;
+            if (!d) continue;
+            for (int ii = 0; ii < 16; ++ii) {
+                int l = q3_nearest_int(x[16 * j + ii] / d);
+                l = std::max(-4, std::min(3, l));
+                L[16 * j + ii] = (int8_t) (l + 4);
+            }
+        }
+        memset(hmask, 0, 32);
+        int m = 0;
+        uint8_t hm = 1;
+        for (int j = 0; j < 256; ++j) {
+            if (L[j] > 3) { hmask[m] |= hm; L[j] -= 4; }
+            if (++m == 32) { m = 0; hm <<= 1; }
+        }
+        for (int j = 0; j < 256; j += 128)
+            for (int l = 0; l < 32; ++l) qs[j / 4 + l] = (uint8_t) (L[j + l] | (L[j + l + 32] << 2) | (L[j + l + 64] << 4) | (L[j + l + 96] << 6));
+    }
+}
+
+int b200moe_quantize_q3_K_host(const float * src, void * dst, int64_t nrows, int64_t n_per_row) {
+    if (!src || !dst || nrows < 0 || n_per_row <= 0 || n_per_row % 256) return B200MOE_ERR_INVALID_ARG;
+    const int64_t rs = n_per_row / 256 * 110;
+    const unsigned hw = std::max(1u, std::thread::hardware_concurrency());
+    const int nthreads = (int) std::min<int64_t>(hw, std::max<int64_t>(1, nrows / 16));
+    std::vector<std::thread> th;
+    for (int t = 0; t < nthreads; ++t)
+        th.emplace_back([=] {
+            for (int64_t r = nrows * t / nthreads; r < nrows * (t + 1) / nthreads; ++r)
+                quantize_row_q3_K(src + r * n_per_row, static_cast<uint8_t *>(dst) + r * rs, n_per_row);
+        });
+    for (auto & t : th) t.join();
+    return B200MOE_OK;
+}
+
 int b200moe_dequantize_host(int type, const void * src, float * dst, int64_t nrows, int64_t n_per_row) {
     if (!src || !dst || nrows < 0 || n_per_row <= 0) return B200MOE_ERR_INVALID_ARG;
     const uint8_t * s = static_cast<const uint8_t *>(src);

@@ -85,9 +85,7 @@ class HostLayer:
 def _quantize(wtype: int, w: np.ndarray, quantize_q3k: Optional[Callable]) -> np.ndarray:
     if wtype == TYPE_NVFP4:
         return moe.quantize_nvfp4(w)
-    if quantize_q3k is None:
-        raise RuntimeError("Q3_K inputs need a quantiser callback (the reference quantiser)")
-    return quantize_q3k(w)
+    return quantize_q3k(w) if quantize_q3k is not None else moe.quantize_q3_K(w)
 
 
 CHUNK_EXPERTS = 32

@@ -52,3 +52,15 @@ def test_no_device_means_no_compute():
     with pytest.raises(capi.B200MoeError):
         moe.Context(0)
     assert lib.b200moe_reserve(None, None, 1) == 1   # null context is an argument error, not a crash
+
+
+def test_q3k_quantiser_matches_reference_bytes():
+    """Product quantiser vs the compiled reference quantiser (when present) and vs the stored reference bytes of the fixture."""
+    z = np.load(os.path.join(ROOT, "tests", "golden", "kat.npz"))
+    assert np.array_equal(moe.quantize_q3_K(z["q3k_w"]), z["q3k_wq"])
+    from oracle import oracle as O
+    if O.have_reference():
+        rng = np.random.default_rng(12)
+        w = rng.normal(0, 0.02, (4, 24, 768)).astype(np.float32)
+        w[0, 0, :32] = 0
+        assert np.array_equal(moe.quantize_q3_K(w), O.reference().quantize(TYPE_Q3_K, w))

@@ -30,11 +30,8 @@ def rel_err(got, want):
 
 
 def q3k_quantizer(checker):
-    from oracle import oracle as O
-    if not O.have_reference():
-        pytest.skip("Q3_K weights at this size need the compiled reference quantiser")
-    ref = O.reference()
-    return lambda w: ref.quantize(TYPE_Q3_K, w)
+    """The product's host quantiser (bit-identical to quantize_row_q3_K_ref, see tests/test_capi_cpu.py)."""
+    return moe.quantize_q3_K
 
 
 def run_and_compare(gpu_ctx, checker, layer, x_np, bf16, tol=TIGHT):
