@@ -86,6 +86,7 @@ int ref_dequantize(int type, const void * src, float * dst, int64_t n) {
 // Activation quantiser of the CPU backend for a weight type (vec_dot_type's from_float):
 // Q8_K for Q3_K, Q8_0 for NVFP4.  Returns the byte size written.
 int64_t ref_quantize_activation(int wtype, const float * src, void * dst, int64_t n) {
+    ggml_cpu_init();  // fills the fp16 / UE4M3 lookup tables the CPU kernels read (idempotent)
     const auto * tc = ggml_get_type_traits_cpu((ggml_type) wtype);
     const ggml_type vt = tc->vec_dot_type;
     ggml_get_type_traits_cpu(vt)->from_float(src, dst, n);
@@ -93,6 +94,7 @@ int64_t ref_quantize_activation(int wtype, const float * src, void * dst, int64_
 }
 
 int ref_vec_dot(int wtype, int64_t n, const void * wrow, const void * act, float * out) {
+    ggml_cpu_init();
     const auto * tc = ggml_get_type_traits_cpu((ggml_type) wtype);
     tc->vec_dot((int) n, out, 0, wrow, 0, act, 0, 1);
     return 0;
