@@ -106,6 +106,37 @@ def test_c2_nvfp4_batched_decode_full_shape(T, gpu_ctx, checker):
     print("c2 T=%d errors" % T, errs)
 
 
+def test_c3_nvfp4_prefill_with_logit_bias(gpu_ctx, checker):
+    """4096 tokens, per-expert logit bias ~N(0,1) (skewed loads).  With the compiled reference as checker the whole batch is
+    compared; the scalar restatement alone would need minutes, so it checks the first 128 tokens (routing and experts are
+    per-token, so a prefix is a valid case of its own)."""
+    from oracle import oracle as O
+    cfg = W.CONFIGS["c3_nvfp4_prefill"]
+    layer = W.make_layer(cfg)
+    T = 4096 if O.have_reference() else 128
+    x_np = W.make_tokens(cfg, T, bf16=True)
+    errs = run_and_compare(gpu_ctx, checker, layer, x_np, bf16=True)
+    print("c3 T=%d errors" % T, errs)
+
+
+def test_c5_latent_layer_full_shape(gpu_ctx, checker):
+    from oracle import oracle as O
+    cfg = W.CONFIGS["c5_latent"]
+    if not O.have_reference():
+        pytest.skip("512-expert latent layer at 256 tokens needs the compiled reference as checker (minutes on the scalar restatement)")
+    layer = W.make_layer(cfg)
+    x_np = W.make_tokens(cfg, 256, bf16=True)
+    dl = layer.to_device(gpu_ctx)
+    out, ob = dl.forward(torch.from_numpy(x_np).cuda().to(torch.bfloat16), observe=True)
+    gpu_ctx.synchronize()
+    r = checker.moe_layer(x=x_np, n_threads=os.cpu_count() or 1, **layer.checker_kwargs())
+    assert np.array_equal(ob.topk.cpu().numpy(), r.ids)
+    assert np.array_equal(ob.weights_norm.cpu().numpy(), r.weights)
+    e = rel_err(out.cpu().numpy(), r.out)
+    print("c5 out error", e)
+    assert e <= TOL
+
+
 def test_route_and_ffn_entry_points_compose(gpu_ctx, checker):
     cfg = W.small_config(TYPE_NVFP4, seed=5)
     layer = W.make_layer(cfg)
