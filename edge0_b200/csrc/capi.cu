@@ -16,6 +16,7 @@
 
 #include "../../include/edge0_b200_moe.h"
 #include "expert_gemv.cuh"
+#include "expert_mma.cuh"
 #include "router.cuh"
 
 using namespace b200moe;
@@ -46,6 +47,7 @@ struct Plan {  // carved out of the scratch arena for one (layer shape, max_toke
     void * xin = nullptr;   // [T][n_embd] staging for the host entry point (input dtype bytes, <= 4 B/elt)
     float * outb = nullptr; // [T][n_embd] staging for the host entry point
     int * one_group_ids = nullptr;  // [T] zeros: dense matvec expressed as one expert
+    __half * afp16 = nullptr;       // [T*k][max(n_in, n_ff)] expert-sorted fp16 activations of the tensor-core path
     size_t total = 0;
 };
 
@@ -62,6 +64,7 @@ struct b200moe_ctx {
     b200moe_counters counters{};
     int64_t launches = 0;
     bool timing = false;
+    int expert_path = 0;  // 0 auto, 1 integer GEMV always, 2 tensor-core GEMM whenever the shape allows
     struct Timed { cudaEvent_t beg, end; int kind; };
     std::vector<Timed> timed;
 };
@@ -134,6 +137,7 @@ void carve(Plan & p, uint8_t * base) {
     p.xin = c.take<float>(T * H);
     p.outb = c.take<float>(T * H);
     p.one_group_ids = c.take<int>(T);
+    p.afp16 = c.take<__half>(2 * std::max(R, T) * std::max({kin, I, H}));   // hi plane, then lo plane
     p.total = align_up(c.off, 256);
 }
 
@@ -244,6 +248,55 @@ int launch_gemv(b200moe_ctx * ctx, int wtype, int k, const GemvParams & p, int n
     CASE(TYPE_Q3_K, 256) CASE(TYPE_Q3_K, 512) CASE(TYPE_Q3_K, 768) CASE(TYPE_Q3_K, 2048)
 #undef CASE
     return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no expert kernel for type %d width %d", wtype, k);
+}
+
+template <int K, bool DUAL>
+int launch_mma_t(b200moe_ctx * ctx, const MmaParams & p, cudaStream_t st) {
+    constexpr size_t smem = mma_smem_bytes<K, DUAL>();
+    auto kern = expert_mma_nvfp4_kernel<K, DUAL>;
+    static bool configured = false;
+    if (!configured) {
+        CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+        configured = true;
+    }
+    b200moe_ctx::Timed tm{};
+    if (ctx->timing) {
+        CUDA_TRY(ctx, cudaEventCreate(&tm.beg));
+        CUDA_TRY(ctx, cudaEventCreate(&tm.end));
+        tm.kind = DUAL ? 0 : 1;
+        CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
+    }
+    kern<<<ctx->sm_count, MMA_THREADS, smem, st>>>(p);
+    if (ctx->timing) {
+        CUDA_TRY(ctx, cudaEventRecord(tm.end, st));
+        ctx->timed.push_back(tm);
+    }
+    return check_launch(ctx, "expert_mma");
+}
+
+bool mma_supported(int wtype, int k, int n_out) {
+    return wtype == TYPE_NVFP4 && n_out % 128 == 0 && (k == 256 || k == 512 || k == 768 || k == 1024 || k == 2048);
+}
+
+template <bool DUAL>
+int launch_mma(b200moe_ctx * ctx, int k, const MmaParams & p, cudaStream_t st) {
+    switch (k) {
+        case 256: return launch_mma_t<256, DUAL>(ctx, p, st);
+        case 512: return launch_mma_t<512, DUAL>(ctx, p, st);
+        case 768: return launch_mma_t<768, DUAL>(ctx, p, st);
+        case 1024: return launch_mma_t<1024, DUAL>(ctx, p, st);
+        case 2048: return launch_mma_t<2048, DUAL>(ctx, p, st);
+    }
+    return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no tensor-core expert kernel for width %d", k);
+}
+
+// expert-sorted fp16 copy of quantised activations (input of the tensor-core kernels)
+int launch_sorted_act(b200moe_ctx * ctx, ActQuant act, int rows, int k, int n_ids, int ne11, cudaStream_t st) {
+    Plan & p = ctx->plan;
+    const int64_t warps = (int64_t) rows * (k / 32);
+    sorted_act_fp16_kernel<<<(unsigned) ((warps * 32 + 255) / 256), 256, 0, st>>>(act, p.groups.perm, rows, k, n_ids, ne11, p.afp16,
+                                                                                    p.afp16 + (size_t) rows * k);
+    return check_launch(ctx, "sorted_act_fp16");
 }
 
 template <typename XT>
@@ -423,11 +476,30 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
     const int k = l->n_expert_used, rows = T * k;
     const int nt = tokens_per_pass(rows, l->n_expert);
     int rc;
-    GemvParams gu = gemv_params(ctx, l->gate, l->up, l->gate_scale, l->up_scale, xq, p.hid, l->n_ff, k, 1, l->n_expert);
-    if ((rc = launch_gemv<true>(ctx, l->wtype, n_in, gu, nt, st))) return rc;
-    if ((rc = launch_quantize<float>(ctx, p.hid, l->n_ff, p.hq, rows, l->n_ff, l->wtype, st))) return rc;
-    GemvParams dn = gemv_params(ctx, l->down, nullptr, l->down_scale, nullptr, p.hq, p.y, n_in, k, k, l->n_expert);
-    if ((rc = launch_gemv<false>(ctx, l->wtype, l->n_ff, dn, nt, st))) return rc;
+    // Tensor-core grouped GEMM once experts see several rows each (its cost per expert does not grow with the rows up to 128);
+    // integer GEMV below that.  Both keep activations on the reference's int8 grid.
+    const bool can_mma = mma_supported(l->wtype, n_in, l->n_ff) && mma_supported(l->wtype, l->n_ff, n_in);
+    const bool use_mma = can_mma && (ctx->expert_path == 2 || (ctx->expert_path == 0 && rows >= 2 * l->n_expert));
+    if (use_mma) {
+        auto mp = [&](const void * w0, const void * w1, const float * s0, const float * s1, float * out, int n_out, int m_k) {
+            MmaParams m{};
+            m.w0 = static_cast<const uint8_t *>(w0); m.w1 = static_cast<const uint8_t *>(w1); m.scale0 = s0; m.scale1 = s1;
+            m.act = p.afp16; m.act_lo = p.afp16 + (size_t) rows * m_k; m.offsets = p.groups.offsets; m.perm = p.groups.perm; m.active = p.groups.active; m.meta = p.groups.meta;
+            m.out = out; m.n_out = n_out; m.n_as = l->n_expert; m.err = ctx->d_err;
+            return m;
+        };
+        if ((rc = launch_sorted_act(ctx, xq, rows, n_in, k, 1, st))) return rc;
+        if ((rc = launch_mma<true>(ctx, n_in, mp(l->gate, l->up, l->gate_scale, l->up_scale, p.hid, l->n_ff, n_in), st))) return rc;
+        if ((rc = launch_quantize<float>(ctx, p.hid, l->n_ff, p.hq, rows, l->n_ff, l->wtype, st))) return rc;
+        if ((rc = launch_sorted_act(ctx, p.hq, rows, l->n_ff, k, k, st))) return rc;
+        if ((rc = launch_mma<false>(ctx, l->n_ff, mp(l->down, nullptr, l->down_scale, nullptr, p.y, n_in, l->n_ff), st))) return rc;
+    } else {
+        GemvParams gu = gemv_params(ctx, l->gate, l->up, l->gate_scale, l->up_scale, xq, p.hid, l->n_ff, k, 1, l->n_expert);
+        if ((rc = launch_gemv<true>(ctx, l->wtype, n_in, gu, nt, st))) return rc;
+        if ((rc = launch_quantize<float>(ctx, p.hid, l->n_ff, p.hq, rows, l->n_ff, l->wtype, st))) return rc;
+        GemvParams dn = gemv_params(ctx, l->down, nullptr, l->down_scale, nullptr, p.hq, p.y, n_in, k, k, l->n_expert);
+        if ((rc = launch_gemv<false>(ctx, l->wtype, l->n_ff, dn, nt, st))) return rc;
+    }
     dim3 grid((n_in / 4 + 255) / 256, T);
     combine_kernel<<<grid, 256, 0, st>>>(p.y, wts, out, n_in, k, T);
     if ((rc = check_launch(ctx, "combine"))) return rc;
@@ -564,6 +636,12 @@ int b200moe_get_counters(const b200moe_ctx * ctx, b200moe_counters * out) {
     if (!ctx || !out) return B200MOE_ERR_INVALID_ARG;
     *out = ctx->counters;
     out->kernel_launches = ctx->launches;
+    return B200MOE_OK;
+}
+
+int b200moe_set_expert_path(b200moe_ctx * ctx, int path) {
+    if (!ctx || path < 0 || path > 2) return B200MOE_ERR_INVALID_ARG;
+    ctx->expert_path = path;
     return B200MOE_OK;
 }
 

@@ -110,6 +110,10 @@ class Context:
         self.check(self.lib.b200moe_get_counters(self.handle, C.byref(c)))
         return int(c.kernel_launches)
 
+    def set_expert_path(self, path: int):
+        """0 automatic, 1 integer GEMV always, 2 tensor-core grouped GEMM whenever the shape allows."""
+        self.check(self.lib.b200moe_set_expert_path(self.handle, path))
+
     def enable_kernel_timing(self, on: bool = True):
         self.check(self.lib.b200moe_enable_kernel_timing(self.handle, int(on)))
 

@@ -107,6 +107,13 @@ B200MOE_API int  b200moe_device_memory(int device, size_t * free_bytes, size_t *
 B200MOE_API int  b200moe_get_counters(const b200moe_ctx * ctx, b200moe_counters * out);
 B200MOE_API int  b200moe_synchronize(b200moe_ctx * ctx, void * stream); /* ggml_backend_synchronize */
 
+/* Which kernels run the expert matmuls (reference: model option switches such as `routing` / `experts`,
+ * edge0-infer/docs/configuration.md:62-72; plain struct-style option, no environment variables):
+ *   0  automatic: integer GEMV for decode-sized batches, tcgen05 grouped GEMM once experts see several rows each
+ *   1  integer GEMV always
+ *   2  tcgen05 grouped GEMM whenever the type and widths allow (NVFP4, n_ff and n_in multiples of 128) */
+B200MOE_API int  b200moe_set_expert_path(b200moe_ctx * ctx, int path);
+
 /* Per-kernel device timing (reference: DecodeTiming with an injectable clock, include/edge0/timing.h:4-9).
  * When enabled, every expert-matmul launch is bracketed by CUDA events on its stream; b200moe_kernel_times
  * waits for them and returns, for kind 0 (fused gate+up+SwiGLU) and kind 1 (single indexed matmul / down),
