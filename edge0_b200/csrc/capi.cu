@@ -250,10 +250,10 @@ int launch_gemv(b200moe_ctx * ctx, int wtype, int k, const GemvParams & p, int n
     return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no expert kernel for type %d width %d", wtype, k);
 }
 
-template <int K, bool DUAL>
+template <int K, bool DUAL, int NT>
 int launch_mma_t(b200moe_ctx * ctx, const MmaParams & p, cudaStream_t st) {
-    constexpr size_t smem = mma_smem_bytes<K, DUAL>();
-    auto kern = expert_mma_nvfp4_kernel<K, DUAL>;
+    constexpr size_t smem = mma_smem_bytes<K, DUAL, NT>();
+    auto kern = expert_mma_nvfp4_kernel<K, DUAL, NT>;
     static bool configured = false;
     if (!configured) {
         CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
@@ -266,7 +266,7 @@ int launch_mma_t(b200moe_ctx * ctx, const MmaParams & p, cudaStream_t st) {
         tm.kind = DUAL ? 0 : 1;
         CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
     }
-    kern<<<ctx->sm_count, MMA_THREADS, smem, st>>>(p);
+    kern<<<ctx->sm_count * (NT <= 32 ? 2 : 1), MMA_THREADS, smem, st>>>(p);
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventRecord(tm.end, st));
         ctx->timed.push_back(tm);
@@ -278,15 +278,12 @@ bool mma_supported(int wtype, int k, int n_out) {
     return wtype == TYPE_NVFP4 && n_out % 128 == 0 && (k == 256 || k == 512 || k == 768 || k == 1024 || k == 2048);
 }
 
+// small_tiles: experts see few rows each (batched decode) -> 32-row token tiles, two CTAs per SM
 template <bool DUAL>
-int launch_mma(b200moe_ctx * ctx, int k, const MmaParams & p, cudaStream_t st) {
-    switch (k) {
-        case 256: return launch_mma_t<256, DUAL>(ctx, p, st);
-        case 512: return launch_mma_t<512, DUAL>(ctx, p, st);
-        case 768: return launch_mma_t<768, DUAL>(ctx, p, st);
-        case 1024: return launch_mma_t<1024, DUAL>(ctx, p, st);
-        case 2048: return launch_mma_t<2048, DUAL>(ctx, p, st);
-    }
+int launch_mma(b200moe_ctx * ctx, int k, const MmaParams & p, bool small_tiles, cudaStream_t st) {
+#define MMA_CASE(KK) case KK: return small_tiles ? launch_mma_t<KK, DUAL, 32>(ctx, p, st) : launch_mma_t<KK, DUAL, 128>(ctx, p, st);
+    switch (k) { MMA_CASE(256) MMA_CASE(512) MMA_CASE(768) MMA_CASE(1024) MMA_CASE(2048) }
+#undef MMA_CASE
     return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no tensor-core expert kernel for width %d", k);
 }
 
@@ -478,25 +475,36 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
     int rc;
     // Tensor-core grouped GEMM once experts see several rows each (its cost per expert does not grow with the rows up to 128);
     // integer GEMV below that.  Both keep activations on the reference's int8 grid.
+    // Which engine runs which matmul.  The tensor-core grouped GEMM (tcgen05, kind::f16) adds ~3e-5 of RMS of its own
+    // accumulation error.  After `down` nothing is re-quantised, so that error is harmless there; on gate/up it moves
+    // values of `hidden` across int8 rounding boundaries of the re-quantisation, which the output bar tolerates for
+    // batches up to a few hundred tokens (measured 1.7e-3 at 64, 2.7e-3 at 200) but not at 4096 (1.05e-2).
+    //   path 0 (auto): down on tensor cores once experts see several rows; gate/up on tensor cores only for 16 < T <= 512
+    //   path 1: integer everywhere; path 2: tensor cores wherever the shape allows; path 3: integer gate/up, tensor-core down
     const bool can_mma = mma_supported(l->wtype, n_in, l->n_ff) && mma_supported(l->wtype, l->n_ff, n_in);
-    const bool use_mma = can_mma && (ctx->expert_path == 2 || (ctx->expert_path == 0 && rows >= 2 * l->n_expert));
-    if (use_mma) {
-        auto mp = [&](const void * w0, const void * w1, const float * s0, const float * s1, float * out, int n_out, int m_k) {
-            MmaParams m{};
-            m.w0 = static_cast<const uint8_t *>(w0); m.w1 = static_cast<const uint8_t *>(w1); m.scale0 = s0; m.scale1 = s1;
-            m.act = p.afp16; m.act_lo = p.afp16 + (size_t) rows * m_k; m.offsets = p.groups.offsets; m.perm = p.groups.perm; m.active = p.groups.active; m.meta = p.groups.meta;
-            m.out = out; m.n_out = n_out; m.n_as = l->n_expert; m.err = ctx->d_err;
-            return m;
-        };
+    const bool many_rows = rows >= 2 * l->n_expert;
+    const bool mma_down = can_mma && (ctx->expert_path == 2 || ctx->expert_path == 3 || (ctx->expert_path == 0 && many_rows));
+    const bool mma_gu = can_mma && (ctx->expert_path == 2 || (ctx->expert_path == 0 && many_rows && T <= 512));
+    const bool small_tiles = rows < 24 * l->n_expert;   // on average fewer than 24 rows per expert
+    auto mp = [&](const void * w0, const void * w1, const float * s0, const float * s1, float * out, int n_out, int m_k) {
+        MmaParams m{};
+        m.w0 = static_cast<const uint8_t *>(w0); m.w1 = static_cast<const uint8_t *>(w1); m.scale0 = s0; m.scale1 = s1;
+        m.act = p.afp16; m.act_lo = p.afp16 + (size_t) rows * m_k; m.offsets = p.groups.offsets; m.perm = p.groups.perm;
+        m.active = p.groups.active; m.meta = p.groups.meta; m.out = out; m.n_out = n_out; m.n_as = l->n_expert; m.err = ctx->d_err;
+        return m;
+    };
+    if (mma_gu) {
         if ((rc = launch_sorted_act(ctx, xq, rows, n_in, k, 1, st))) return rc;
-        if ((rc = launch_mma<true>(ctx, n_in, mp(l->gate, l->up, l->gate_scale, l->up_scale, p.hid, l->n_ff, n_in), st))) return rc;
-        if ((rc = launch_quantize<float>(ctx, p.hid, l->n_ff, p.hq, rows, l->n_ff, l->wtype, st))) return rc;
-        if ((rc = launch_sorted_act(ctx, p.hq, rows, l->n_ff, k, k, st))) return rc;
-        if ((rc = launch_mma<false>(ctx, l->n_ff, mp(l->down, nullptr, l->down_scale, nullptr, p.y, n_in, l->n_ff), st))) return rc;
+        if ((rc = launch_mma<true>(ctx, n_in, mp(l->gate, l->up, l->gate_scale, l->up_scale, p.hid, l->n_ff, n_in), small_tiles, st))) return rc;
     } else {
         GemvParams gu = gemv_params(ctx, l->gate, l->up, l->gate_scale, l->up_scale, xq, p.hid, l->n_ff, k, 1, l->n_expert);
         if ((rc = launch_gemv<true>(ctx, l->wtype, n_in, gu, nt, st))) return rc;
-        if ((rc = launch_quantize<float>(ctx, p.hid, l->n_ff, p.hq, rows, l->n_ff, l->wtype, st))) return rc;
+    }
+    if ((rc = launch_quantize<float>(ctx, p.hid, l->n_ff, p.hq, rows, l->n_ff, l->wtype, st))) return rc;
+    if (mma_down) {
+        if ((rc = launch_sorted_act(ctx, p.hq, rows, l->n_ff, k, k, st))) return rc;
+        if ((rc = launch_mma<false>(ctx, l->n_ff, mp(l->down, nullptr, l->down_scale, nullptr, p.y, n_in, l->n_ff), small_tiles, st))) return rc;
+    } else {
         GemvParams dn = gemv_params(ctx, l->down, nullptr, l->down_scale, nullptr, p.hq, p.y, n_in, k, k, l->n_expert);
         if ((rc = launch_gemv<false>(ctx, l->wtype, l->n_ff, dn, nt, st))) return rc;
     }
@@ -640,7 +648,7 @@ int b200moe_get_counters(const b200moe_ctx * ctx, b200moe_counters * out) {
 }
 
 int b200moe_set_expert_path(b200moe_ctx * ctx, int path) {
-    if (!ctx || path < 0 || path > 2) return B200MOE_ERR_INVALID_ARG;
+    if (!ctx || path < 0 || path > 3) return B200MOE_ERR_INVALID_ARG;
     ctx->expert_path = path;
     return B200MOE_OK;
 }

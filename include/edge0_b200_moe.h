@@ -109,9 +109,12 @@ B200MOE_API int  b200moe_synchronize(b200moe_ctx * ctx, void * stream); /* ggml_
 
 /* Which kernels run the expert matmuls (reference: model option switches such as `routing` / `experts`,
  * edge0-infer/docs/configuration.md:62-72; plain struct-style option, no environment variables):
- *   0  automatic: integer GEMV for decode-sized batches, tcgen05 grouped GEMM once experts see several rows each
+ *   0  automatic: integer GEMV for a handful of rows; once experts see several rows each, `down` runs on the tcgen05
+ *      grouped GEMM, and gate/up does too for batches up to 512 tokens (beyond that its ~3e-5 accumulation error, amplified
+ *      by the re-quantisation of the hidden activations, approaches the 1e-2 output bar)
  *   1  integer GEMV always
- *   2  tcgen05 grouped GEMM whenever the type and widths allow (NVFP4, n_ff and n_in multiples of 128) */
+ *   2  tcgen05 grouped GEMM wherever the type and widths allow (NVFP4, n_ff and n_in multiples of 128)
+ *   3  integer gate/up, tcgen05 down */
 B200MOE_API int  b200moe_set_expert_path(b200moe_ctx * ctx, int path);
 
 /* Per-kernel device timing (reference: DecodeTiming with an injectable clock, include/edge0/timing.h:4-9).
