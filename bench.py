@@ -40,6 +40,7 @@ def parse():
     ap.add_argument("--weight-sets", type=int, default=3, help="distinct weight copies rotated over (L2 defeat)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--expert-path", type=int, default=0, help="0 library default, 1 integer (bit-exact) kernels, 2 tcgen05 GEMM, 3 integer gate/up + tcgen05 down")
     ap.add_argument("--no-graph", action="store_true", help="launch every step's kernels from the host instead of replaying CUDA graphs")
     return ap.parse_args()
 
@@ -161,6 +162,7 @@ def run_b200_arm(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg, T = workload_config(args)
     ctx = moe.Context(local)
+    ctx.set_expert_path(args.expert_path)
     dev = torch.device("cuda", local)
 
     host = W.make_layer(cfg)
@@ -347,7 +349,7 @@ def run_b200_arm(args):
                            "n_ff": cfg.n_ff, "n_latent": cfg.n_latent, "weights": "NVFP4 (ggml block_nvfp4) + fp32 per-expert scale",
                            "activations": "bf16 in, int8 grid of the reference (Q8_0) inside, fp32 out",
                            "l2": f"{n_sets} distinct weight sets rotated ({n_sets * layers[0].weight_bytes() / 1e6:.0f} MB > 126 MB L2)",
-                           "experts_touched_per_step": U, "launch": "eager" if args.no_graph else "CUDA graph replay (one graph per weight set)", "parallelism": f"replicas x{world}" if world > 1 else "single GPU"},
+                           "experts_touched_per_step": U, "expert_path": args.expert_path, "launch": "eager" if args.no_graph else "CUDA graph replay (one graph per weight set)", "parallelism": f"replicas x{world}" if world > 1 else "single GPU"},
                 "e2e": e2e, "gpu_launches": launches, "clocks": clocks_main, "roofline": roofline, "cpu_baseline": cpu,
                 "other_batch_sizes": extras}
         print(json.dumps(line))
@@ -454,7 +456,7 @@ def run_c5_arm(args):
                 "dtype": "int8 x fp4 integer dots, fp32 accumulate", "data": "synthetic",
                 "config": {"workload": f"{cfg.name} T={T} total", "n_embd": cfg.n_embd, "n_latent": cfg.n_latent, "n_expert": cfg.n_expert,
                            "top_k": cfg.top_k, "n_ff": cfg.n_ff, "parallelism": f"ep{world} (experts {per}/GPU, tokens {T // world}/GPU, NCCL all-to-all dispatch+combine)",
-                           "l2": f"{n_sets} distinct weight sets rotated", "experts_touched_per_step": U, "launch": "eager"},
+                           "l2": f"{n_sets} distinct weight sets rotated", "experts_touched_per_step": U, "expert_path": args.expert_path, "launch": "eager"},
                 "e2e": {"value": T * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * cfg.n_embd * 4,
                         "d2h_bytes_per_step": T * cfg.n_embd * 4, "ms_per_step": e2e_ms / args.steps},
                 "gpu_launches": launches, "clocks": clocks,

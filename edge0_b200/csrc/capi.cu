@@ -209,7 +209,7 @@ int check_launch(b200moe_ctx * ctx, const char * what) {
 template <int WT, int K, bool DUAL, int NT>
 int launch_gemv_t(b200moe_ctx * ctx, const GemvParams & p, cudaStream_t st) {
     constexpr int GEMV_STAGES = gemv_stages<WT, K, DUAL>();
-    constexpr size_t smem = gemv_smem_bytes<WT, K, DUAL, GEMV_STAGES>();
+    constexpr size_t smem = gemv_smem_bytes<WT, K, DUAL, NT, GEMV_STAGES>();
     static_assert(smem <= 227 * 1024, "ring does not fit shared memory");
     auto kern = expert_gemv_kernel<WT, K, DUAL, NT, GEMV_STAGES>;
     static bool configured = false;  // per instantiation
@@ -234,10 +234,12 @@ int launch_gemv_t(b200moe_ctx * ctx, const GemvParams & p, cudaStream_t st) {
 
 template <int WT, int K, bool DUAL>
 int launch_gemv_k(b200moe_ctx * ctx, const GemvParams & p, int nt, cudaStream_t st) {
-    // token rows held in registers per pass: 4, or 2 where a lane owns three or more units (register budget)
-    constexpr int NTB = GemvCfg<WT, K>::UPL >= 3 ? 2 : 4;
-    if (nt <= 1) return launch_gemv_t<WT, K, DUAL, 1>(ctx, p, st);
-    return launch_gemv_t<WT, K, DUAL, NTB>(ctx, p, st);
+    if constexpr (DUAL && K > 2048) {
+        return fail(ctx, B200MOE_ERR_UNSUPPORTED, "fused gate/up kernel is not built for K=%d", K);
+    } else {
+        if (nt <= 1) return launch_gemv_t<WT, K, DUAL, 1>(ctx, p, st);
+        return launch_gemv_t<WT, K, DUAL, 4>(ctx, p, st);
+    }
 }
 
 template <bool DUAL>
@@ -475,16 +477,18 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
     int rc;
     // Tensor-core grouped GEMM once experts see several rows each (its cost per expert does not grow with the rows up to 128);
     // integer GEMV below that.  Both keep activations on the reference's int8 grid.
-    // Which engine runs which matmul.  The tensor-core grouped GEMM (tcgen05, kind::f16) adds ~3e-5 of RMS of its own
-    // accumulation error.  After `down` nothing is re-quantised, so that error is harmless there; on gate/up it moves
-    // values of `hidden` across int8 rounding boundaries of the re-quantisation, which the output bar tolerates for
-    // batches up to a few hundred tokens (measured 1.7e-3 at 64, 2.7e-3 at 200) but not at 4096 (1.05e-2).
-    //   path 0 (auto): down on tensor cores once experts see several rows; gate/up on tensor cores only for 16 < T <= 512
-    //   path 1: integer everywhere; path 2: tensor cores wherever the shape allows; path 3: integer gate/up, tensor-core down
+    // Which engine runs which matmul.  The integer kernels reproduce the reference's fp32 summation order and are
+    // bit-identical to the CPU path.  The tensor-core grouped GEMM (tcgen05, kind::f16) adds ~3e-5 of RMS of its own
+    // accumulation error: after `down` nothing is re-quantised, so there it only costs ~1e-5 on the output; on gate/up it
+    // moves values of `hidden` across int8 rounding boundaries of the re-quantisation (output error 1.7e-3 at 64 tokens,
+    // 1.05e-2 at 4096), so gate/up only goes to the tensor cores when asked for.
+    //   path 0 (default): bit-exact integer gate/up; down on tensor cores once experts see several rows
+    //   path 1: integer everywhere (whole layer bit-identical to the reference)
+    //   path 2: tensor cores wherever the shape allows;  path 3: integer gate/up, tensor-core down at any batch size
     const bool can_mma = mma_supported(l->wtype, n_in, l->n_ff) && mma_supported(l->wtype, l->n_ff, n_in);
     const bool many_rows = rows >= 2 * l->n_expert;
     const bool mma_down = can_mma && (ctx->expert_path == 2 || ctx->expert_path == 3 || (ctx->expert_path == 0 && many_rows));
-    const bool mma_gu = can_mma && (ctx->expert_path == 2 || (ctx->expert_path == 0 && many_rows && T <= 512));
+    const bool mma_gu = can_mma && ctx->expert_path == 2;
     const bool small_tiles = rows < 24 * l->n_expert;   // on average fewer than 24 rows per expert
     auto mp = [&](const void * w0, const void * w1, const float * s0, const float * s1, float * out, int n_out, int m_k) {
         MmaParams m{};

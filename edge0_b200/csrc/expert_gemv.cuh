@@ -1,16 +1,23 @@
-// Grouped expert GEMV for decode / batched decode: streams only the routed experts' quantised rows
-// from HBM through a shared-memory ring filled by 1-D bulk async copies (TMA), decodes in registers,
-// integer dot products against the int8 activation grid of the reference, warp-shuffle reductions.
+// Grouped expert GEMV for decode / batched decode: streams only the routed experts' quantised rows from HBM through
+// a shared-memory ring filled by 1-D bulk async copies (TMA), integer dot products against the reference's int8
+// activation grid, and fp32 accumulation in EXACTLY the order of the reference's AVX2 kernels, so every dot product
+// is bit-identical to the CPU path (and with it every later re-quantisation of activations).
+//
+// How the reference sums (ggml-cpu/arch/x86/quants.c, AVX2 branches): eight fp32 lanes; lane L collects, block after
+// block, fma(scale, (float) p_L, acc_L) where p_L is the integer dot of a fixed group of 4 elements per 32
+// (NVFP4: group L of each Q8_0 block; Q3_K: elements 4L..4L+3 of every 32-group of the super-block, scale-weighted and
+// summed over the super-block first); the eight lanes are folded at the end as ((a0+a4)+(a2+a6))+((a1+a5)+(a3+a7)).
+// Here 8 GPU lanes play the 8 AVX lanes of one weight row (4 rows per warp), each running its chain over K in
+// order; three xor-shuffles reproduce the fold.
 //
 // One kernel template serves
 //   DUAL = true : gate and up projections of the same rows + SwiGLU epilogue  -> hidden[row][n_out]
 //   DUAL = false: one indexed matmul (ggml MUL_MAT_ID semantics)               -> dst[row][n_out]
 // "row" is a routed row: token*n_ids + slot.
 //
-// Work distribution: the rows of all active experts form one flat list (active expert a, output row r);
-// every CTA of the persistent grid takes an equal contiguous span of it, so HBM bytes per SM are equal
-// whatever the routing looks like.  A span is walked in chunks of at most ROWS_PER_STAGE rows of one
-// expert; chunk c lives in ring stage c % STAGES.
+// Work distribution: the rows of all active experts form one flat list (active expert a, output row r); every CTA of
+// the persistent grid takes a contiguous span of equal WORK (rows x passes over the expert's routed rows).  A span is
+// walked in chunks of at most ROWS_PER_STAGE rows of one expert; chunk c lives in ring stage c % STAGES.
 #pragma once
 #include "common.cuh"
 #include "formats.cuh"
@@ -39,128 +46,115 @@ struct GemvParams {
 
 template <int WT, int K>
 struct GemvCfg {
-    static constexpr int UNITS = K / 32;
-    static constexpr int LPR = (UNITS % 32 == 0) ? 32 : (UNITS % 16 == 0) ? 16 : (UNITS % 8 == 0) ? 8 : 0;  // lanes per row
-    static_assert(LPR != 0, "K must be a multiple of 256");
-    static constexpr int UPL = UNITS / LPR;  // units per lane
-    static constexpr int RPP = 32 / LPR;     // rows per warp pass
+    static constexpr int LPR = 8;            // lanes per row = the reference's 8 SIMD lanes
+    static constexpr int RPP = 4;            // rows per warp pass
     static constexpr int ROW_BYTES = WT == TYPE_NVFP4 ? K / 64 * 36 : K / 256 * 110;
     static constexpr int GRAN = (ROW_BYTES % 16 == 0) ? 1 : 8;  // span granularity in rows (16-byte rule of bulk copies)
-    static constexpr int NWARPS = 16;
-    // passes per warp per stage chosen so a (single-tensor) stage is roughly 16-32 KB
+    static constexpr int NWARPS = 8;
+    // passes per warp per stage chosen so a (single-tensor) stage is roughly 12-40 KB
     static constexpr int PASSES = (ROW_BYTES * RPP * NWARPS >= 12288) ? 1 : (ROW_BYTES * RPP * NWARPS >= 6144) ? 2 : 4;
     static constexpr int ROWS_PER_STAGE = NWARPS * RPP * PASSES;
     static constexpr int TENSOR_STAGE_BYTES = ROWS_PER_STAGE * ROW_BYTES;
     static_assert(TENSOR_STAGE_BYTES % 16 == 0, "stage must keep 16-byte alignment");
-    static_assert(WT != TYPE_Q3_K || UPL <= 4, "unsupported width");
+    // activations of one token in shared memory: K int8, then the block scales as floats (padded to 16 bytes)
+    static constexpr int ACT_D = WT == TYPE_NVFP4 ? K / 32 : K / 256;
+    static constexpr int ACT_TOKEN_BYTES = K + ((ACT_D * 4 + 15) / 16) * 16;
 };
-
-// ---- per-token activation registers of one lane --------------------------------------------------------
-template <int WT, int UPL>
-struct LaneAct {
-    uint32_t q[UPL][8];  // NVFP4: permuted to the decode order; Q3_K: natural order
-    float d[UPL];        // NVFP4: Q8_0 block scale; Q3_K: Q8_K super-block scale
-    int bs[UPL];         // Q3_K: bsums of sub-blocks 2p, 2p+1 packed as two int16
-};
-
-template <int WT, int K>
-__device__ __forceinline__ void load_lane_act(LaneAct<WT, GemvCfg<WT, K>::UPL> & a, const ActQuant & act, int act_row, int lir, bool valid) {
-    using C = GemvCfg<WT, K>;
-#pragma unroll
-    for (int i = 0; i < C::UPL; ++i) {
-        const int u = i * C::LPR + lir;  // units of a lane are strided by LPR: neighbouring lanes read neighbouring units
-        uint32_t w[8];
-        if (valid) {
-            const int4 * src = reinterpret_cast<const int4 *>(act.q + (size_t) act_row * K + u * 32);
-            const int4 v0 = __ldg(src), v1 = __ldg(src + 1);
-            w[0] = v0.x; w[1] = v0.y; w[2] = v0.z; w[3] = v0.w; w[4] = v1.x; w[5] = v1.y; w[6] = v1.z; w[7] = v1.w;
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) w[j] = 0;
-        }
-        if (WT == TYPE_NVFP4) {
-            fp4_permute_act16(&w[0], &a.q[i][0]);
-            fp4_permute_act16(&w[4], &a.q[i][4]);
-            a.d[i] = valid ? __ldg(act.d + (size_t) act_row * (K / 32) + u) : 0.0f;
-            a.bs[i] = 0;
-        } else {
-            // Q3_K unit (sb, p): needs elements 128*j + 32*s + 4p..4p+3 of super-block sb -> that is one word out
-            // of each 32-element group; they are NOT contiguous, so fetch them individually.
-            const int sb = u >> 3, p = u & 7;
-            const int8_t * base = act.q + (size_t) act_row * K + sb * 256 + 4 * p;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) a.q[i][j] = valid ? __ldg(reinterpret_cast<const uint32_t *>(base + 32 * j)) : 0u;
-            a.d[i] = valid ? __ldg(act.d + (size_t) act_row * (K / 256) + sb) : 0.0f;
-            a.bs[i] = valid ? __ldg(reinterpret_cast<const int *>(act.bsum + (size_t) act_row * (K / 16) + sb * 16 + 2 * p)) : 0;
-        }
-    }
-}
 
 __device__ __forceinline__ uint32_t lds_u32_a2(const uint8_t * p) {  // 2-byte aligned 32-bit load from shared memory
     const uint16_t * h = reinterpret_cast<const uint16_t *>(p);
     return (uint32_t) h[0] | ((uint32_t) h[1] << 16);
 }
 
-// Lane-partial dot products of one weight row against NT tokens.
+// One SIMD lane (L = 0..7) of the reference's dot product of one weight row with NT activation rows.
+//   row   : the quantised weight row in shared memory
+//   acts  : NT activation records (ACT_TOKEN_BYTES apart): K int8 followed by the block scales
 template <int WT, int K, int NT>
-__device__ __forceinline__ void row_partial(const uint8_t * __restrict__ row, int lir, const LaneAct<WT, GemvCfg<WT, K>::UPL> (&acts)[NT],
-                                            const float * __restrict__ ue_tab, float (&acc)[NT]) {
+__device__ __forceinline__ void lane_chain(const uint8_t * __restrict__ row, int L, const uint8_t * __restrict__ acts,
+                                           const float * __restrict__ ue_tab, float (&acc)[NT]) {
     using C = GemvCfg<WT, K>;
 #pragma unroll
     for (int t = 0; t < NT; ++t) acc[t] = 0.0f;
-#pragma unroll
-    for (int i = 0; i < C::UPL; ++i) {
-        const int u = i * C::LPR + lir;
-        if (WT == TYPE_NVFP4) {
-            const uint8_t * blk = row + (u >> 1) * NVFP4_BLOCK_BYTES;
-            const int hf = u & 1;
+    if (WT == TYPE_NVFP4) {
+        // lane L: sub-block (L>>2) of each half block, elements 4*(L&3) .. +3 of it = the low (L&3 < 2) or high nibbles of
+        // one qs word; they meet word L of the Q8_0 block.  ggml_vec_dot_nvfp4_q8_0, ggml-cpu/arch/x86/quants.c:1004-1062.
+        const int sub_in_half = L >> 2, mp = L & 3;
+        const int word_off = 4 + 8 * sub_in_half + 4 * (mp & 1);
+        const int nib_shift = 4 * (mp >> 1);
+#pragma unroll 2
+        for (int b = 0; b < K / 64; ++b) {
+            const uint8_t * blk = row + b * NVFP4_BLOCK_BYTES;
             const uint32_t dw = *reinterpret_cast<const uint32_t *>(blk);
-            const uint32_t * qs = reinterpret_cast<const uint32_t *>(blk + 4 + 16 * hf);
-            const uint32_t w0 = qs[0], w1 = qs[1], w2 = qs[2], w3 = qs[3];
-            const float s0 = ue_tab[(dw >> (16 * hf)) & 0xff];
-            const float s1 = ue_tab[(dw >> (16 * hf + 8)) & 0xff];
-            const Fp4Word a0 = fp4_decode_word(w0), a1 = fp4_decode_word(w1), b0 = fp4_decode_word(w2), b1 = fp4_decode_word(w3);
 #pragma unroll
-            for (int t = 0; t < NT; ++t) {
-                const uint32_t * q = acts[t].q[i];
-                int pa = dot4((int) a0.pos_a, (int) q[0], 0);
-                pa = dot4((int) a0.pos_b, (int) q[1], pa);
-                pa = dot4((int) a1.pos_a, (int) q[2], pa);
-                pa = dot4((int) a1.pos_b, (int) q[3], pa);
-                int na = dot4((int) a0.neg_a, (int) q[0], 0);
-                na = dot4((int) a0.neg_b, (int) q[1], na);
-                na = dot4((int) a1.neg_a, (int) q[2], na);
-                na = dot4((int) a1.neg_b, (int) q[3], na);
-                int pb = dot4((int) b0.pos_a, (int) q[4], 0);
-                pb = dot4((int) b0.pos_b, (int) q[5], pb);
-                pb = dot4((int) b1.pos_a, (int) q[6], pb);
-                pb = dot4((int) b1.pos_b, (int) q[7], pb);
-                int nb = dot4((int) b0.neg_a, (int) q[4], 0);
-                nb = dot4((int) b0.neg_b, (int) q[5], nb);
-                nb = dot4((int) b1.neg_a, (int) q[6], nb);
-                nb = dot4((int) b1.neg_b, (int) q[7], nb);
-                const float dy = acts[t].d[i];
-                acc[t] = fmaf(s0 * dy, small_int_to_float(pa - na), acc[t]);
-                acc[t] = fmaf(s1 * dy, small_int_to_float(pb - nb), acc[t]);
+            for (int hf = 0; hf < 2; ++hf) {
+                const uint32_t w = *reinterpret_cast<const uint32_t *>(blk + 16 * hf + word_off);
+                const uint32_t t4 = (w >> nib_shift) & 0x0f0f0f0fu;          // four codes, one per byte
+                const uint32_t u = t4 | (t4 >> 4);
+                const uint32_t sel = (u & 0xffff00ffu) | ((u >> 8) & 0x0000ff00u);   // the four codes packed into 16 bits
+                const uint32_t pos = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel);
+                const uint32_t neg = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel ^ 0x8888u);
+                const float sw = ue_tab[(dw >> (8 * (2 * hf + sub_in_half))) & 0xff];
+                const int unit = 2 * b + hf;
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    const uint8_t * a = acts + t * C::ACT_TOKEN_BYTES;
+                    const uint32_t aw = reinterpret_cast<const uint32_t *>(a)[unit * 8 + L];
+                    const float dy = reinterpret_cast<const float *>(a + K)[unit];
+                    const int p = dot4((int) pos, (int) aw, 0) - dot4((int) neg, (int) aw, 0);
+                    acc[t] = __fmaf_rn(__fmul_rn(sw, dy), small_int_to_float(p), acc[t]);
+                }
             }
-        } else {
-            const int sb = u >> 3, p = u & 7;
+        }
+    } else {
+        // lane L: byte columns 4L..4L+3 of every super-block; integer sum over the super-block with the signed 6-bit
+        // sub-block scales, then one fma with d_w*d_x.  ggml_vec_dot_q3_K_q8_K, ggml-cpu/arch/x86/quants.c:1766-1880.
+        const int hi = L >= 4 ? 1 : 0;
+#pragma unroll 1
+        for (int sb = 0; sb < K / 256; ++sb) {
             const uint8_t * blk = row + sb * Q3K_BLOCK_BYTES;  // 2-byte aligned
-            const uint32_t hm = lds_u32_a2(blk + 4 * p);
-            const uint32_t qs0 = lds_u32_a2(blk + 32 + 4 * p);
-            const uint32_t qs1 = lds_u32_a2(blk + 64 + 4 * p);
+            const uint32_t hm = lds_u32_a2(blk + 4 * L);
+            const uint32_t qs0 = lds_u32_a2(blk + 32 + 4 * L);
+            const uint32_t qs1 = lds_u32_a2(blk + 64 + 4 * L);
             uint32_t sc[4];
             q3k_unpack_scales(lds_u32_a2(blk + 96), lds_u32_a2(blk + 100), lds_u32_a2(blk + 104), sc);
             const float dw = __half2float(*reinterpret_cast<const __half *>(blk + 108));
-            const int c0 = q3k_scale_at(sc, 2 * p), c1 = q3k_scale_at(sc, 2 * p + 1);
+            int sumi[NT];
+#pragma unroll
+            for (int t = 0; t < NT; ++t) sumi[t] = 0;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const uint32_t w = j ? qs1 : qs0;
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    const int bit = 4 * j + s;
+                    const uint32_t lo2 = (w >> (2 * s)) & 0x03030303u;
+                    const uint32_t hb4 = bit >= 2 ? ((hm >> (bit - 2)) & 0x04040404u) : ((hm << (2 - bit)) & 0x04040404u);
+                    // codes 0..7 -> signed -4..3 in every byte without borrows between bytes
+                    const uint32_t code = (((lo2 | hb4) | 0x80808080u) - 0x04040404u) ^ 0x80808080u;
+                    const int scale = q3k_scale_at(sc, 8 * j + 2 * s + hi);
+#pragma unroll
+                    for (int t = 0; t < NT; ++t) {
+                        const uint8_t * a = acts + t * C::ACT_TOKEN_BYTES;
+                        const uint32_t aw = *reinterpret_cast<const uint32_t *>(a + sb * 256 + 32 * (4 * j + s) + 4 * L);
+                        sumi[t] += scale * dot4((int) code, (int) aw, 0);
+                    }
+                }
+            }
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
-                int isum = q3k_unit_dot(qs0, qs1, hm, sc, p, acts[t].q[i]);
-                const int bs = acts[t].bs[i];
-                isum -= 4 * (c0 * (int) (int16_t) (bs & 0xffff) + c1 * (int) (int16_t) (bs >> 16));
-                acc[t] = fmaf(dw * acts[t].d[i], small_int_to_float(isum), acc[t]);
+                const float dx = reinterpret_cast<const float *>(acts + t * C::ACT_TOKEN_BYTES + K)[sb];
+                acc[t] = __fmaf_rn(__fmul_rn(dx, dw), small_int_to_float(sumi[t]), acc[t]);
             }
         }
+    }
+    // hsum_float_8: (a4+a0, a5+a1, a6+a2, a7+a3) -> (r0+r2, r1+r3) -> s0+s1
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        float v = acc[t];
+        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
+        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+        acc[t] = v;
     }
 }
 
@@ -191,16 +185,19 @@ __global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_ke
     using C = GemvCfg<WT, K>;
     constexpr int NTENS = DUAL ? 2 : 1;
     constexpr int STAGE_BYTES = C::TENSOR_STAGE_BYTES * NTENS;
+    constexpr int NTHREADS = C::NWARPS * 32;
 
     extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t * ring = smem;                                                   // STAGES * STAGE_BYTES
-    uint64_t * full = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);  // STAGES barriers
-    float * ue_tab = reinterpret_cast<float *>(full + STAGES);               // 256 floats (NVFP4 only)
+    uint8_t * ring = smem;                                                        // STAGES * STAGE_BYTES
+    uint8_t * acts = smem + STAGES * STAGE_BYTES;                                 // NT * ACT_TOKEN_BYTES (16-byte aligned)
+    uint64_t * full = reinterpret_cast<uint64_t *>(acts + NT * C::ACT_TOKEN_BYTES);  // STAGES barriers
+    float * ue_tab = reinterpret_cast<float *>(full + STAGES);                    // 256 floats (NVFP4 only)
     __shared__ int s_abort;
+    __shared__ int s_span[2];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int lir = lane % C::LPR;   // lane in row group
-    const int rgrp = lane / C::LPR;  // which of the RPP rows of a pass
+    const int L = lane & 7;       // SIMD lane of the reference this thread plays
+    const int rgrp = lane >> 3;   // which of the 4 rows of a warp pass
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
@@ -208,16 +205,14 @@ __global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_ke
         s_abort = 0;
     }
     if (WT == TYPE_NVFP4)
-        for (int i = tid; i < 256; i += blockDim.x) ue_tab[i] = ue4m3_half_to_f32(i);
+        for (int i = tid; i < 256; i += NTHREADS) ue_tab[i] = ue4m3_half_to_f32(i);
     __syncthreads();
 
     const int n_active = p.meta[0];
     const int upe = p.n_out / C::GRAN;                       // span units per expert
     const long long total = (long long) n_active * upe;
-    ChunkWalker cons, prod;
     // Span boundaries balance WORK, not rows: a weight row of an expert with n routed rows costs ceil(n/NT) passes.
     // Boundary i sits at work i/grid of the total; both neighbours compute it the same way, so spans tile exactly.
-    __shared__ int s_span[2];
     if (tid < 2) {
         const int * cw = p.cost + (NT == 1 ? 0 : NT == 2 ? 1 : 2) * (p.n_as + 1);
         const long long total_work = (long long) cw[n_active] * upe;
@@ -238,6 +233,7 @@ __global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_ke
         s_span[tid] = u;
     }
     __syncthreads();
+    ChunkWalker cons, prod;
     cons.u = s_span[0];
     cons.u_end = s_span[1];
     cons.units_per_expert = upe;
@@ -262,9 +258,7 @@ __global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_ke
             if (prod.next(c)) { issue(c, s); ++issued; }
     }
 
-    LaneAct<WT, C::UPL> acts[NT];
     int loaded_e = -1, loaded_tc = -1;
-
     Chunk ck;
     int ci = 0;
     bool failed = false;
@@ -291,12 +285,20 @@ __global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_ke
                 rows[t] = i < n_e ? p.perm[row_beg + i] : -1;
             }
             if (loaded_e != e || loaded_tc != tc) {
+                // the NT activation rows of this pass into shared memory (all warps use the same ones)
+                __syncthreads();
 #pragma unroll
                 for (int t = 0; t < NT; ++t) {
                     const int r = rows[t];
                     const int arow = r >= 0 ? (r / p.n_ids) * p.ne11 + (r % p.n_ids) % p.ne11 : 0;
-                    load_lane_act<WT, K>(acts[t], p.act, arow, lir, r >= 0);
+                    uint8_t * dst = acts + t * C::ACT_TOKEN_BYTES;
+                    const int4 * srcq = reinterpret_cast<const int4 *>(p.act.q + (size_t) arow * K);
+                    for (int i = tid; i < K / 16; i += NTHREADS)
+                        reinterpret_cast<int4 *>(dst)[i] = r >= 0 ? __ldg(srcq + i) : make_int4(0, 0, 0, 0);
+                    for (int i = tid; i < C::ACT_D; i += NTHREADS)
+                        reinterpret_cast<float *>(dst + K)[i] = r >= 0 ? __ldg(p.act.d + (size_t) arow * C::ACT_D + i) : 0.0f;
                 }
+                __syncthreads();
                 loaded_e = e;
                 loaded_tc = tc;
             }
@@ -306,24 +308,17 @@ __global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_ke
                 const bool row_ok = lr < ck.n;
                 const uint8_t * wrow = st + (size_t) (row_ok ? lr : 0) * C::ROW_BYTES;
                 float g[NT], uacc[NT];
-                row_partial<WT, K, NT>(wrow, lir, acts, ue_tab, g);
-                if (DUAL) row_partial<WT, K, NT>(wrow + C::TENSOR_STAGE_BYTES, lir, acts, ue_tab, uacc);
-                group_reduce<NT, C::LPR>(g, lir);
-                if (DUAL) group_reduce<NT, C::LPR>(uacc, lir);
-                const int tv = group_reduce_owner_value<NT, C::LPR>(lir);
-                constexpr int LOWMASK = (C::LPR / NT) - 1;  // lanes sharing the same value; the one with low bits 0 writes
-                if (row_ok && (lir & LOWMASK) == 0) {
-                    int r = -1;
+                lane_chain<WT, K, NT>(wrow, L, acts, ue_tab, g);
+                if (DUAL) lane_chain<WT, K, NT>(wrow + C::TENSOR_STAGE_BYTES, L, acts, ue_tab, uacc);
+                if (row_ok && L == 0) {
 #pragma unroll
-                    for (int t = 0; t < NT; ++t)
-                        if (t == tv) r = rows[t];
-                    if (r >= 0) {
-                        float v = g[0] * sc0;
-                        if (DUAL) {
-                            const float uv = uacc[0] * sc1;
-                            v = __fmul_rn(ggml_silu(v), uv);
+                    for (int t = 0; t < NT; ++t) {
+                        const int r = rows[t];
+                        if (r >= 0) {
+                            float v = __fmul_rn(g[t], sc0);
+                            if (DUAL) v = __fmul_rn(ggml_silu(v), __fmul_rn(uacc[t], sc1));
+                            p.out[(size_t) r * p.n_out + ck.r0 + lr] = v;
                         }
-                        p.out[(size_t) r * p.n_out + ck.r0 + lr] = v;
                     }
                 }
             }
@@ -346,12 +341,13 @@ __global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_ke
 template <int WT, int K, bool DUAL>
 constexpr int gemv_stages() {
     constexpr int stage = GemvCfg<WT, K>::TENSOR_STAGE_BYTES * (DUAL ? 2 : 1);
-    return (4 * stage <= 200 * 1024) ? 4 : (3 * stage <= 200 * 1024) ? 3 : 2;
+    return (4 * stage <= 190 * 1024) ? 4 : (3 * stage <= 190 * 1024) ? 3 : 2;
 }
 
-template <int WT, int K, bool DUAL, int STAGES>
+template <int WT, int K, bool DUAL, int NT, int STAGES>
 constexpr size_t gemv_smem_bytes() {
-    return (size_t) STAGES * GemvCfg<WT, K>::TENSOR_STAGE_BYTES * (DUAL ? 2 : 1) + STAGES * 8 + 256 * 4 + 64;
+    return (size_t) STAGES * GemvCfg<WT, K>::TENSOR_STAGE_BYTES * (DUAL ? 2 : 1) + NT * GemvCfg<WT, K>::ACT_TOKEN_BYTES + STAGES * 8 +
+           256 * 4 + 64;
 }
 
 // ---- weighted combine: out[t][i] = sum over slots in slot order of y[t*k+s][i] * w[t][s] (forward.cpp:308-310)

@@ -1,12 +1,12 @@
 """Parity of the CUDA path (through the C ABI) with the CPU checker on identical seeded inputs.
 
-Bar: routing ids, router logits, probabilities and route weights bit-exact; every FFN output within
-max-abs <= 1e-2 * RMS(reference output), the bound stated for this path.  What is actually observed:
-* hidden = silu(gate)*up agrees to ~1e-6 (integer dots are exact, only the fp32 summation order differs);
-* the reference re-quantises hidden to int8 before the down matmul; a 1e-7 difference in hidden occasionally
-  moves one value across a rounding boundary, which shifts that one routed row of `down` by a few 1e-3 of the
-  RMS.  The 1e-2 bar is asserted on the layer output; the per-route intermediate `down` gets a sanity bound of 3e-2
-  and, on the integer path, the share of routed rows that moved at all is bounded as well.
+* Routing (logits, probabilities, ids, weights) is bit-exact.
+* The integer expert kernels follow the reference's fp32 summation order: with them (expert path 1) `hidden`, `down` and
+  the layer output are BIT-IDENTICAL to the CPU path, for NVFP4 and Q3_K, plain and latent layers, 1 to 4096 tokens.
+* The default path sends `down` to the tcgen05 grouped GEMM once experts see several rows: `hidden` stays bit-identical,
+  `down`/output differ by the tensor core's accumulation error (bar here 2e-4 of RMS; measured ~3e-5).
+* Expert path 2 (tensor cores for gate/up too) is checked against the stated bar of the path, max-abs <= 1e-2 * RMS of the
+  reference output; its `hidden` error is re-quantised by the reference algorithm, which amplifies it.
 """
 import os
 
@@ -34,29 +34,32 @@ def q3k_quantizer(checker):
     return moe.quantize_q3_K
 
 
-def run_and_compare(gpu_ctx, checker, layer, x_np, bf16, tol=5e-4):
-    dl = layer.to_device(gpu_ctx)
-    x = torch.from_numpy(x_np).cuda()
-    if bf16:
-        x = x.to(torch.bfloat16)
-    out, ob = dl.forward(x, observe=True)
-    gpu_ctx.synchronize()
+def run_and_compare(gpu_ctx, checker, layer, x_np, bf16, path=0):
+    gpu_ctx.set_expert_path(path)
+    try:
+        dl = layer.to_device(gpu_ctx)
+        x = torch.from_numpy(x_np).cuda()
+        if bf16:
+            x = x.to(torch.bfloat16)
+        out, ob = dl.forward(x, observe=True)
+        gpu_ctx.synchronize()
+    finally:
+        gpu_ctx.set_expert_path(0)
     r = checker.moe_layer(x=x_np, n_threads=os.cpu_count() or 1, **layer.checker_kwargs())
     assert np.array_equal(ob.topk.cpu().numpy(), r.ids), "routing ids must be bit-exact"
     assert np.array_equal(ob.logits.cpu().numpy(), r.logits), "router logits follow the reference summation order bit for bit"
     assert np.array_equal(ob.probs.cpu().numpy(), r.probs)
     assert np.array_equal(ob.weights_norm.cpu().numpy(), r.weights)
-    down = ob.down.cpu().numpy()
-    errs = dict(hidden=rel_err(ob.hidden.cpu().numpy(), r.hidden), down=rel_err(down, r.down_out), out=rel_err(out.cpu().numpy(), r.out))
-    assert errs["hidden"] <= tol, errs
-    assert errs["out"] <= TOL, errs              # the bar: FFN output within 1e-2 of its RMS
-    assert errs["down"] <= 3 * TOL, errs         # per-route intermediate: one requantisation flip in 32768 rows can reach ~1e-2 here
-    rms = np.sqrt(np.mean(r.down_out.astype(np.float64) ** 2))
-    moved = (np.abs(down - r.down_out).max(axis=2) > TIGHT * rms).mean()   # routed rows touched by a requantisation flip
-    tensor_path = layer.cfg.wtype == TYPE_NVFP4 and x_np.shape[0] * layer.cfg.top_k >= 2 * layer.cfg.n_expert
-    if not tensor_path:   # integer path: hidden differs by ~1e-7 only, so flips must be rare
-        assert errs["hidden"] <= TIGHT and moved <= 0.05, (moved, errs)
-    errs["rows_moved"] = float(moved)
+    hidden, down, o = ob.hidden.cpu().numpy(), ob.down.cpu().numpy(), out.cpu().numpy()
+    errs = dict(hidden=rel_err(hidden, r.hidden), down=rel_err(down, r.down_out), out=rel_err(o, r.out))
+    if path in (0, 1, 3):
+        assert np.array_equal(hidden, r.hidden), ("hidden must be bit-identical on the integer gate/up kernels", errs)
+    if path == 1:
+        assert np.array_equal(down, r.down_out) and np.array_equal(o, r.out), ("integer path must be bit-identical", errs)
+    elif path in (0, 3):
+        assert errs["down"] <= 2e-4 and errs["out"] <= 2e-4, errs       # tensor-core down: accumulation error only
+    else:
+        assert errs["hidden"] <= 5e-4 and errs["down"] <= 3 * TOL and errs["out"] <= TOL, errs
     return errs
 
 
@@ -71,19 +74,23 @@ def test_golden_fixtures(name, gpu_ctx):
     cfg, layer, x_np, z = load_golden(name)
     from tests.golden.make_golden import CASES
     bf16 = CASES[name][2]
-    dl = layer.to_device(gpu_ctx)
-    x = torch.from_numpy(x_np).cuda()
-    if bf16:
-        x = x.to(torch.bfloat16)
-    out, ob = dl.forward(x, observe=True)
-    gpu_ctx.synchronize()
+    gpu_ctx.set_expert_path(1)
+    try:
+        dl = layer.to_device(gpu_ctx)
+        x = torch.from_numpy(x_np).cuda()
+        if bf16:
+            x = x.to(torch.bfloat16)
+        out, ob = dl.forward(x, observe=True)
+        gpu_ctx.synchronize()
+    finally:
+        gpu_ctx.set_expert_path(0)
     assert np.array_equal(ob.topk.cpu().numpy(), z["ids"])
     assert np.array_equal(ob.logits.cpu().numpy(), z["logits"])
     assert np.array_equal(ob.probs.cpu().numpy(), z["probs"])
     assert np.array_equal(ob.weights_norm.cpu().numpy(), z["weights"])
-    assert rel_err(ob.hidden.cpu().numpy(), z["hidden"]) <= TIGHT
-    assert rel_err(ob.down.cpu().numpy(), z["down_out"]) <= TOL
-    assert rel_err(out.cpu().numpy(), z["out"]) <= TOL
+    assert np.array_equal(ob.hidden.cpu().numpy(), z["hidden"])       # bit-identical to what the compiled reference produced
+    assert np.array_equal(ob.down.cpu().numpy(), z["down_out"])
+    assert np.array_equal(out.cpu().numpy(), z["out"])
 
 
 @pytest.mark.parametrize("T", [1, 2, 5, 33])
@@ -91,13 +98,14 @@ def test_golden_fixtures(name, gpu_ctx):
 def test_small_layers_vs_checker(wtype, T, gpu_ctx, checker):
     cfg = W.small_config(wtype, n_embd=512, n_expert=16, top_k=4, n_ff=256, seed=21 + T)
     layer = W.make_layer(cfg, quantize_q3k=q3k_quantizer(checker) if wtype == TYPE_Q3_K else None)
-    run_and_compare(gpu_ctx, checker, layer, W.make_tokens(cfg, T), bf16=False)
+    run_and_compare(gpu_ctx, checker, layer, W.make_tokens(cfg, T), bf16=False, path=1)
+    run_and_compare(gpu_ctx, checker, layer, W.make_tokens(cfg, T), bf16=False, path=0)
 
 
 def test_c1_q3k_decode_full_shape(gpu_ctx, checker):
     cfg = W.CONFIGS["c1_q3k"]
     layer = W.make_layer(cfg, quantize_q3k=q3k_quantizer(checker))
-    errs = run_and_compare(gpu_ctx, checker, layer, W.make_tokens(cfg, 1), bf16=False)
+    errs = run_and_compare(gpu_ctx, checker, layer, W.make_tokens(cfg, 1), bf16=False, path=1)
     print("c1 errors", errs)
 
 
@@ -105,8 +113,10 @@ def test_c1_q3k_decode_full_shape(gpu_ctx, checker):
 def test_c2_nvfp4_batched_decode_full_shape(T, gpu_ctx, checker):
     cfg = W.CONFIGS["c2_nvfp4"]
     layer = W.make_layer(cfg)
-    errs = run_and_compare(gpu_ctx, checker, layer, W.make_tokens(cfg, T, bf16=True), bf16=True)
-    print("c2 T=%d errors" % T, errs)
+    x_np = W.make_tokens(cfg, T, bf16=True)
+    run_and_compare(gpu_ctx, checker, layer, x_np, bf16=True, path=1)
+    errs = run_and_compare(gpu_ctx, checker, layer, x_np, bf16=True, path=0)
+    print("c2 T=%d default-path errors" % T, errs)
 
 
 def test_c3_nvfp4_prefill_with_logit_bias(gpu_ctx, checker):
@@ -118,8 +128,9 @@ def test_c3_nvfp4_prefill_with_logit_bias(gpu_ctx, checker):
     layer = W.make_layer(cfg)
     T = 4096 if O.have_reference() else 128
     x_np = W.make_tokens(cfg, T, bf16=True)
-    errs = run_and_compare(gpu_ctx, checker, layer, x_np, bf16=True)
-    print("c3 T=%d errors" % T, errs)
+    errs = run_and_compare(gpu_ctx, checker, layer, x_np, bf16=True, path=0)
+    print("c3 T=%d default-path errors" % T, errs)
+    run_and_compare(gpu_ctx, checker, layer, x_np[:512], bf16=True, path=1)
 
 
 def test_c5_latent_layer_full_shape(gpu_ctx, checker):
@@ -129,15 +140,10 @@ def test_c5_latent_layer_full_shape(gpu_ctx, checker):
         pytest.skip("512-expert latent layer at 256 tokens needs the compiled reference as checker (minutes on the scalar restatement)")
     layer = W.make_layer(cfg)
     x_np = W.make_tokens(cfg, 256, bf16=True)
-    dl = layer.to_device(gpu_ctx)
-    out, ob = dl.forward(torch.from_numpy(x_np).cuda().to(torch.bfloat16), observe=True)
-    gpu_ctx.synchronize()
-    r = checker.moe_layer(x=x_np, n_threads=os.cpu_count() or 1, **layer.checker_kwargs())
-    assert np.array_equal(ob.topk.cpu().numpy(), r.ids)
-    assert np.array_equal(ob.weights_norm.cpu().numpy(), r.weights)
-    e = rel_err(out.cpu().numpy(), r.out)
-    print("c5 out error", e)
-    assert e <= TOL
+    # three int8 re-quantisation stages (latent input, hidden, latent output) make this layer chaotic: a 1e-6 difference in
+    # the latent projection moved the output by 3.6e-2 of RMS before the kernels were made bit-exact.  Integer path only.
+    errs = run_and_compare(gpu_ctx, checker, layer, x_np, bf16=True, path=1)
+    print("c5 errors", errs)
 
 
 @pytest.mark.parametrize("T,shape", [(3, (512, 16, 4, 256)), (40, (512, 16, 4, 256)), (200, (256, 8, 2, 256)), (64, (2048, 128, 8, 768))])
@@ -197,7 +203,7 @@ def test_mul_mat_id_matches_ggml_semantics(gpu_ctx, checker):
                 aq = checker.quantize_activation(wtype, b[t, s % ne11])
                 for r in range(N):
                     want[t, s, r] = checker.vec_dot(wtype, K, wq[ids_full[t, s], r], aq)
-        assert rel_err(dst.cpu().numpy(), want) <= TIGHT
+        assert np.array_equal(dst.cpu().numpy(), want), 'mul_mat_id is bit-identical to the reference dot products'
 
 
 def test_expert_slot_remap_is_bitwise_identical(gpu_ctx):
@@ -229,7 +235,7 @@ def test_host_entry_point_and_determinism(gpu_ctx, checker):
     assert torch.equal(o1, o2), "two runs must give identical bytes"
     r = checker.moe_layer(x=x_np, **layer.checker_kwargs())
     assert np.array_equal(ids.numpy(), r.ids)
-    assert rel_err(o1.numpy(), r.out) <= TOL
+    assert rel_err(o1.numpy(), r.out) <= 2e-4
 
 
 def test_argument_errors_do_not_launch(gpu_ctx):
