@@ -19,6 +19,8 @@
 // the persistent grid takes a contiguous span of equal WORK (rows x passes over the expert's routed rows).  A span is
 // walked in chunks of at most ROWS_PER_STAGE rows of one expert; chunk c lives in ring stage c % STAGES.
 #pragma once
+#include <type_traits>
+
 #include "common.cuh"
 #include "formats.cuh"
 #include "router.cuh"
@@ -211,7 +213,7 @@ __global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_ke
     const int n_active = p.meta[0];
     const int upe = p.n_out / C::GRAN;                       // span units per expert
     const long long total = (long long) n_active * upe;
-    // Span boundaries balance WORK, not rows: a weight row of an expert with n routed rows costs ceil(n/NT) passes.
+    // Span boundaries balance WORK, not rows: a weight row of an expert with n routed rows costs 3 per pass (decode) + 2 per routed row.
     // Boundary i sits at work i/grid of the total; both neighbours compute it the same way, so spans tile exactly.
     if (tid < 2) {
         const int * cw = p.cost + (NT == 1 ? 0 : NT == 2 ? 1 : 2) * (p.n_as + 1);
@@ -277,18 +279,23 @@ __global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_ke
         const float sc0 = p.scale0 ? p.scale0[e] : 1.0f;
         const float sc1 = (DUAL && p.scale1) ? p.scale1[e] : 1.0f;
 
-        for (int tc = 0; tc * NT < n_e; ++tc) {
+        // Routed rows of this expert are taken NT at a time; a remainder of 1 or 2 runs the narrower chains instead of
+        // padding to NT (the weight decode is shared by the rows of a pass, the per-row work is not).
+        for (int t0 = 0, tc = 0; t0 < n_e; ++tc) {
+            const int left = n_e - t0;
+            const int ntc = (NT >= 4 && left >= 3) ? 4 : (NT >= 2 && left >= 2) ? 2 : 1;
             int rows[NT];
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
-                const int i = tc * NT + t;
-                rows[t] = i < n_e ? p.perm[row_beg + i] : -1;
+                const int i = t0 + t;
+                rows[t] = (t < ntc && i < n_e) ? p.perm[row_beg + i] : -1;
             }
             if (loaded_e != e || loaded_tc != tc) {
-                // the NT activation rows of this pass into shared memory (all warps use the same ones)
+                // the activation rows of this pass into shared memory (all warps use the same ones)
                 __syncthreads();
 #pragma unroll
                 for (int t = 0; t < NT; ++t) {
+                    if (t >= ntc) break;
                     const int r = rows[t];
                     const int arow = r >= 0 ? (r / p.n_ids) * p.ne11 + (r % p.n_ids) % p.ne11 : 0;
                     uint8_t * dst = acts + t * C::ACT_TOKEN_BYTES;
@@ -308,13 +315,22 @@ __global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_ke
                 const bool row_ok = lr < ck.n;
                 const uint8_t * wrow = st + (size_t) (row_ok ? lr : 0) * C::ROW_BYTES;
                 float g[NT], uacc[NT];
-                lane_chain<WT, K, NT>(wrow, L, acts, ue_tab, g);
-                if (DUAL) lane_chain<WT, K, NT>(wrow + C::TENSOR_STAGE_BYTES, L, acts, ue_tab, uacc);
+                auto run = [&](auto ntag) {
+                    constexpr int NTC = decltype(ntag)::value;
+                    float gg[NTC], uu[NTC];
+                    lane_chain<WT, K, NTC>(wrow, L, acts, ue_tab, gg);
+                    if (DUAL) lane_chain<WT, K, NTC>(wrow + C::TENSOR_STAGE_BYTES, L, acts, ue_tab, uu);
+#pragma unroll
+                    for (int t = 0; t < NTC; ++t) { g[t] = gg[t]; uacc[t] = DUAL ? uu[t] : 0.0f; }
+                };
+                if (NT >= 4 && ntc == 4) run(std::integral_constant<int, (NT >= 4 ? 4 : 1)>{});
+                else if (NT >= 2 && ntc == 2) run(std::integral_constant<int, (NT >= 2 ? 2 : 1)>{});
+                else run(std::integral_constant<int, 1>{});
                 if (row_ok && L == 0) {
 #pragma unroll
                     for (int t = 0; t < NT; ++t) {
                         const int r = rows[t];
-                        if (r >= 0) {
+                        if (t < ntc && r >= 0) {
                             float v = __fmul_rn(g[t], sc0);
                             if (DUAL) v = __fmul_rn(ggml_silu(v), __fmul_rn(uacc[t], sc1));
                             p.out[(size_t) r * p.n_out + ck.r0 + lr] = v;
@@ -322,6 +338,7 @@ __global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_ke
                     }
                 }
             }
+            t0 += ntc;
         }
         __syncthreads();  // everyone is done reading this stage
         if (tid == 0) {

@@ -332,7 +332,7 @@ struct Groups {
     int * perm;     // [rows]
     int * active;   // [E]
     int * meta;     // [4]
-    int * cost;     // [3][E+1]: prefix over active experts of ceil(rows/nt) for nt = 1, 2, 4 (work per weight row)
+    int * cost;     // [3][E+1]: prefix over active experts of the work per weight row for the nt = 1, 2, 4 kernels
 };
 
 // Block-wide: counts must be final and visible to this block.
@@ -346,7 +346,8 @@ __device__ __forceinline__ void group_scan_body(Groups g, const int32_t * __rest
         for (int base = 0; base < E; base += 32) {
             const int e = base + tid;
             const int n = e < E ? g.counts[e] : 0;
-            int incl = n, w2 = (n + 1) / 2, w4 = (n + 3) / 4;
+            // work per weight row: nt=1 kernels: one pass per routed row; nt=4 kernels: 3 per pass (decode) + 2 per routed row
+            int incl = n, w2 = (n + 1) / 2, w4 = 3 * ((n + 3) / 4) + 2 * n;
             int i2 = w2, i4 = w4;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
