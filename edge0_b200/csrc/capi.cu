@@ -536,7 +536,13 @@ int layer_impl(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, 
     const bool fused_front = !l->n_latent && T <= 128;  // decode-sized batches: 2 launches instead of 4
     if (fused_front) {
         if ((rc = launch_front<XT>(ctx, l, x, T, st))) return rc;
-        if ((rc = launch_select_group(ctx, l, T, (ob && ob->ffn_moe_probs) ? ob->ffn_moe_probs : nullptr, st))) return rc;
+        float * probs = (ob && ob->ffn_moe_probs) ? ob->ffn_moe_probs : nullptr;
+        if (T <= 32) {   // one warp per token fits one block: selection and grouping in a single launch
+            if ((rc = launch_select_group(ctx, l, T, probs, st))) return rc;
+        } else {
+            if ((rc = launch_select(ctx, l, T, p.ids, p.wts, probs, true, st))) return rc;
+            if ((rc = launch_group(ctx, p.ids, l->n_expert, T * k, st))) return rc;
+        }
         if (ob && ob->ffn_moe_logits)
             CUDA_TRY(ctx, cudaMemcpyAsync(ob->ffn_moe_logits, p.logits, sizeof(float) * (size_t) T * l->n_expert, cudaMemcpyDeviceToDevice, st));
     } else {

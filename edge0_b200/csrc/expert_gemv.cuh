@@ -70,8 +70,24 @@ __device__ __forceinline__ uint32_t lds_u32_a2(const uint8_t * p) {  // 2-byte a
 
 // One SIMD lane (L = 0..7) of the reference's dot product of one weight row with NT activation rows.
 //   row   : the quantised weight row in shared memory
-//   acts  : NT activation records (ACT_TOKEN_BYTES apart): K int8 followed by the block scales
-template <int WT, int K, int NT>
+//   acts  : the activations of NTS rows, token-interleaved: words [K/4][NTS] of int8x4, then block scales [ACT_D][NTS];
+//           the first NT of the NTS rows are used
+template <int N, typename T>
+__device__ __forceinline__ void load_vec(T (&dst)[N], const T * src) {
+    static_assert(sizeof(T) == 4, "32-bit elements");
+    if (N == 4) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(src);
+        memcpy(&dst[0], &v, 16);
+    } else if (N == 2) {
+        const uint2 v = *reinterpret_cast<const uint2 *>(src);
+        memcpy(&dst[0], &v, 8);
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) dst[i] = src[i];
+    }
+}
+
+template <int WT, int K, int NT, int NTS>
 __device__ __forceinline__ void lane_chain(const uint8_t * __restrict__ row, int L, const uint8_t * __restrict__ acts,
                                            const float * __restrict__ ue_tab, float (&acc)[NT]) {
     using C = GemvCfg<WT, K>;
@@ -95,15 +111,19 @@ __device__ __forceinline__ void lane_chain(const uint8_t * __restrict__ row, int
                 const uint32_t sel = (u & 0xffff00ffu) | ((u >> 8) & 0x0000ff00u);   // the four codes packed into 16 bits
                 const uint32_t pos = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel);
                 const uint32_t neg = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel ^ 0x8888u);
+                // signed bytes: a byte of `neg` is a magnitude 0..12, 0x80 - it never borrows, the xor drops the guard bit
+                const uint32_t code = pos | ((0x80808080u - neg) ^ 0x80808080u);
                 const float sw = ue_tab[(dw >> (8 * (2 * hf + sub_in_half))) & 0xff];
                 const int unit = 2 * b + hf;
+                // activations are stored [unit][lane word][token] and [unit][token]: one vector load serves all NT rows
+                uint32_t aw[NT];
+                float dy[NT];
+                load_vec<NT>(aw, reinterpret_cast<const uint32_t *>(acts) + (size_t) (unit * 8 + L) * NTS);
+                load_vec<NT>(dy, reinterpret_cast<const float *>(acts + (size_t) K * NTS) + (size_t) unit * NTS);
 #pragma unroll
                 for (int t = 0; t < NT; ++t) {
-                    const uint8_t * a = acts + t * C::ACT_TOKEN_BYTES;
-                    const uint32_t aw = reinterpret_cast<const uint32_t *>(a)[unit * 8 + L];
-                    const float dy = reinterpret_cast<const float *>(a + K)[unit];
-                    const int p = dot4((int) pos, (int) aw, 0) - dot4((int) neg, (int) aw, 0);
-                    acc[t] = __fmaf_rn(__fmul_rn(sw, dy), small_int_to_float(p), acc[t]);
+                    const int p = dot4((int) code, (int) aw[t], 0);
+                    acc[t] = __fmaf_rn(__fmul_rn(sw, dy[t]), small_int_to_float(p), acc[t]);
                 }
             }
         }
@@ -134,19 +154,16 @@ __device__ __forceinline__ void lane_chain(const uint8_t * __restrict__ row, int
                     // codes 0..7 -> signed -4..3 in every byte without borrows between bytes
                     const uint32_t code = (((lo2 | hb4) | 0x80808080u) - 0x04040404u) ^ 0x80808080u;
                     const int scale = q3k_scale_at(sc, 8 * j + 2 * s + hi);
+                    uint32_t aw[NT];
+                    load_vec<NT>(aw, reinterpret_cast<const uint32_t *>(acts) + (size_t) (sb * 64 + 8 * (4 * j + s) + L) * NTS);
 #pragma unroll
-                    for (int t = 0; t < NT; ++t) {
-                        const uint8_t * a = acts + t * C::ACT_TOKEN_BYTES;
-                        const uint32_t aw = *reinterpret_cast<const uint32_t *>(a + sb * 256 + 32 * (4 * j + s) + 4 * L);
-                        sumi[t] += scale * dot4((int) code, (int) aw, 0);
-                    }
+                    for (int t = 0; t < NT; ++t) sumi[t] += scale * dot4((int) code, (int) aw[t], 0);
                 }
             }
+            float dx[NT];
+            load_vec<NT>(dx, reinterpret_cast<const float *>(acts + (size_t) K * NTS) + (size_t) sb * NTS);
 #pragma unroll
-            for (int t = 0; t < NT; ++t) {
-                const float dx = reinterpret_cast<const float *>(acts + t * C::ACT_TOKEN_BYTES + K)[sb];
-                acc[t] = __fmaf_rn(__fmul_rn(dx, dw), small_int_to_float(sumi[t]), acc[t]);
-            }
+            for (int t = 0; t < NT; ++t) acc[t] = __fmaf_rn(__fmul_rn(dx[t], dw), small_int_to_float(sumi[t]), acc[t]);
         }
     }
     // hsum_float_8: (a4+a0, a5+a1, a6+a2, a7+a3) -> (r0+r2, r1+r3) -> s0+s1
@@ -298,12 +315,11 @@ __global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_ke
                     if (t >= ntc) break;
                     const int r = rows[t];
                     const int arow = r >= 0 ? (r / p.n_ids) * p.ne11 + (r % p.n_ids) % p.ne11 : 0;
-                    uint8_t * dst = acts + t * C::ACT_TOKEN_BYTES;
-                    const int4 * srcq = reinterpret_cast<const int4 *>(p.act.q + (size_t) arow * K);
-                    for (int i = tid; i < K / 16; i += NTHREADS)
-                        reinterpret_cast<int4 *>(dst)[i] = r >= 0 ? __ldg(srcq + i) : make_int4(0, 0, 0, 0);
-                    for (int i = tid; i < C::ACT_D; i += NTHREADS)
-                        reinterpret_cast<float *>(dst + K)[i] = r >= 0 ? __ldg(p.act.d + (size_t) arow * C::ACT_D + i) : 0.0f;
+                    const uint32_t * srcq = reinterpret_cast<const uint32_t *>(p.act.q + (size_t) arow * K);
+                    uint32_t * dq = reinterpret_cast<uint32_t *>(acts);
+                    for (int i = tid; i < K / 4; i += NTHREADS) dq[(size_t) i * NT + t] = r >= 0 ? __ldg(srcq + i) : 0u;
+                    float * dd = reinterpret_cast<float *>(acts + (size_t) K * NT);
+                    for (int i = tid; i < C::ACT_D; i += NTHREADS) dd[(size_t) i * NT + t] = r >= 0 ? __ldg(p.act.d + (size_t) arow * C::ACT_D + i) : 0.0f;
                 }
                 __syncthreads();
                 loaded_e = e;
@@ -318,8 +334,8 @@ __global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_ke
                 auto run = [&](auto ntag) {
                     constexpr int NTC = decltype(ntag)::value;
                     float gg[NTC], uu[NTC];
-                    lane_chain<WT, K, NTC>(wrow, L, acts, ue_tab, gg);
-                    if (DUAL) lane_chain<WT, K, NTC>(wrow + C::TENSOR_STAGE_BYTES, L, acts, ue_tab, uu);
+                    lane_chain<WT, K, NTC, NT>(wrow, L, acts, ue_tab, gg);
+                    if (DUAL) lane_chain<WT, K, NTC, NT>(wrow + C::TENSOR_STAGE_BYTES, L, acts, ue_tab, uu);
 #pragma unroll
                     for (int t = 0; t < NTC; ++t) { g[t] = gg[t]; uacc[t] = DUAL ? uu[t] : 0.0f; }
                 };
