@@ -147,7 +147,8 @@ bool gemv_supported(int wtype, int64_t k) {
     return false;
 }
 
-int validate_layer(b200moe_ctx * ctx, const b200moe_layer * l) {
+// need_router / need_experts: which weight pointers the entry point is going to read
+int validate_layer(b200moe_ctx * ctx, const b200moe_layer * l, bool need_router = true, bool need_experts = true) {
     if (!ctx) return B200MOE_ERR_INVALID_ARG;
     if (!l) return fail(ctx, B200MOE_ERR_INVALID_ARG, "layer is null");
     if (l->n_embd <= 0 || l->n_expert <= 0 || l->n_expert_used <= 0 || l->n_ff <= 0 || l->n_latent < 0)
@@ -162,8 +163,10 @@ int validate_layer(b200moe_ctx * ctx, const b200moe_layer * l) {
         return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no kernel for widths n_in=%d n_ff=%d of type %d", n_in, l->n_ff, l->wtype);
     if (l->n_latent && !gemv_supported(l->wtype, l->n_embd)) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no kernel for n_embd=%d", l->n_embd);
     if (l->n_ff % 8 || n_in % 8) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "row counts must be multiples of 8");
-    if (!l->router_w || !l->gate || !l->up || !l->down) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null weight pointer");
-    if (l->n_latent && (!l->lat_down || !l->lat_up)) return fail(ctx, B200MOE_ERR_INVALID_ARG, "latent layer without projections");
+    if (need_router && !l->router_w) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null router weight pointer");
+    if (need_experts && (!l->gate || !l->up || !l->down)) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null weight pointer");
+    if (need_router && need_experts && l->n_latent && (!l->lat_down || !l->lat_up))
+        return fail(ctx, B200MOE_ERR_INVALID_ARG, "latent layer without projections");
     const uintptr_t al = (uintptr_t) l->gate | (uintptr_t) l->up | (uintptr_t) l->down | (uintptr_t) l->lat_down | (uintptr_t) l->lat_up;
     if (al & 15) return fail(ctx, B200MOE_ERR_INVALID_ARG, "quantised tensors must be 16-byte aligned");
     return B200MOE_OK;
@@ -955,14 +958,14 @@ int b200moe_dequantize_host(int type, const void * src, float * dst, int64_t nro
 
 int b200moe_route(b200moe_ctx * ctx, const b200moe_layer * l, const void * x, int x_type, int32_t T, int32_t * ids, float * weights,
                   const b200moe_observe * ob, void * stream) {
-    int rc = validate_layer(ctx, l);
+    int rc = validate_layer(ctx, l, true, false);
     if (rc) return rc;
     if (T == 0) return B200MOE_OK;
     if (!x || !ids || !weights || T < 0) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer or negative token count");
     if (x_type != TYPE_F32 && x_type != TYPE_BF16) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "activations must be F32 or BF16");
     if (T == 0) return B200MOE_OK;
     CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-    if ((rc = b200moe_reserve(ctx, l, T))) return rc;
+    if ((rc = ensure_plan(ctx, l->n_embd, l->n_latent ? l->n_latent : l->n_embd, l->n_expert, l->n_expert_used, l->n_ff, l->wtype, T))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (x_type == TYPE_F32) return route_impl<float>(ctx, l, static_cast<const float *>(x), T, ids, weights, ob, false, st);
     return route_impl<__nv_bfloat16>(ctx, l, static_cast<const __nv_bfloat16 *>(x), T, ids, weights, ob, false, st);
@@ -1037,14 +1040,14 @@ int b200moe_gather_rows(b200moe_ctx * ctx, const float * src, int64_t src_rows, 
 
 int b200moe_ffn(b200moe_ctx * ctx, const b200moe_layer * l, const void * x, int x_type, int32_t T, const int32_t * ids, const float * weights,
                 float * out, const b200moe_observe * ob, void * stream) {
-    int rc = validate_layer(ctx, l);
+    int rc = validate_layer(ctx, l, false, true);
     if (rc) return rc;
     if (T == 0) return B200MOE_OK;
     if (!x || !ids || !weights || !out || T < 0) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer or negative token count");
     if (x_type != TYPE_F32 && x_type != TYPE_BF16) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "activations must be F32 or BF16");
     if (T == 0) return B200MOE_OK;
     CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-    if ((rc = b200moe_reserve(ctx, l, T))) return rc;
+    if ((rc = ensure_plan(ctx, l->n_embd, l->n_latent ? l->n_latent : l->n_embd, l->n_expert, l->n_expert_used, l->n_ff, l->wtype, T))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     Plan & p = ctx->plan;
     const int n_in = l->n_latent ? l->n_latent : l->n_embd, k = l->n_expert_used;

@@ -137,7 +137,8 @@ B200MOE_API int  b200moe_dequantize_host(int type, const void * src, float * dst
 
 /* Builder::route (forward.cpp:262-271) = mul_mat(F32) -> soft_max -> argsort_top_k -> get_rows ->
  * sum_rows -> clamp(2^-14) -> div.  x: x_type (F32 or BF16) [n_embd, T].
- * ids I32 [k, T] (expert indices, descending probability); weights F32 [k, T]. */
+ * ids I32 [k, T] (expert indices, descending probability); weights F32 [k, T].
+ * Reads router_w / router_bias only: the expert pointers of `layer` may be NULL here (the dimensions must still be valid). */
 B200MOE_API int b200moe_route(b200moe_ctx * ctx, const b200moe_layer * layer, const void * x, int x_type,
                               int32_t n_tokens, int32_t * ids, float * weights,
                               const b200moe_observe * observe, void * stream);
@@ -167,7 +168,8 @@ B200MOE_API int b200moe_gather_rows(b200moe_ctx * ctx, const float * src, int64_
                                     int64_t width, void * stream);
 
 /* Builder::ffn with given routing (forward.cpp:300-311): gate/up mul_mat_id -> silu*up -> down mul_mat_id ->
- * * weights -> sum over slots in slot order.  x: [n_in, T] in x_type; out F32 [n_in, T]. */
+ * * weights -> sum over slots in slot order.  x: [n_in, T] in x_type; out F32 [n_in, T].
+ * Reads the expert tensors only: router_w and the latent projections of `layer` may be NULL here. */
 B200MOE_API int b200moe_ffn(b200moe_ctx * ctx, const b200moe_layer * layer, const void * x, int x_type, int32_t n_tokens,
                             const int32_t * ids, const float * weights, float * out,
                             const b200moe_observe * observe, void * stream);

@@ -69,9 +69,9 @@ class LayerResult:
 class _Checker:
     prefix = ""
 
-    def __init__(self, path: str):
+    def __init__(self, path: str, mode: int = C.DEFAULT_MODE):
         self.path = path
-        self.lib = C.CDLL(path)
+        self.lib = C.CDLL(path, mode=mode)
         p = self.prefix
         getattr(self.lib, p + "moe_layer").argtypes = [C.POINTER(MoeArgs)]
         getattr(self.lib, p + "moe_layer").restype = C.c_int
@@ -128,7 +128,9 @@ class _Checker:
     # -- the layer
     def moe_layer(self, *, wtype, x, router_w, gate, up, down, top_k, router_bias=None,
                   s_gate=None, s_up=None, s_down=None, lat_d=None, lat_u=None, s_lat_d=None, s_lat_u=None,
-                  n_threads=1, repeats=0) -> LayerResult:
+                  n_threads=1, repeats=0, backend=None, use_gallocr=False) -> LayerResult:
+        """backend: a ggml_backend_t (ctypes void pointer) to run the reference's graph on instead of its CPU backend
+        (compiled reference only); use_gallocr: let ggml's graph allocator place the intermediate tensors."""
         x = np.ascontiguousarray(x, dtype=np.float32)
         T, H = x.shape
         E = router_w.shape[0]
@@ -158,7 +160,10 @@ class _Checker:
             setattr(a, k, _ptr(getattr(res, k)))
         a.ms_best = C.cast(C.pointer(best), C.c_void_p)
         a.ms_median = C.cast(C.pointer(med), C.c_void_p)
-        rc = getattr(self.lib, self.prefix + "moe_layer")(C.byref(a))
+        if backend is not None:
+            rc = self.lib.ref_moe_layer_backend(C.byref(a), backend, int(use_gallocr))
+        else:
+            rc = getattr(self.lib, self.prefix + "moe_layer")(C.byref(a))
         if rc:
             raise RuntimeError(f"{self.prefix}moe_layer failed with {rc}")
         res.ms_best, res.ms_median = best.value, med.value
@@ -187,8 +192,13 @@ class Reference(_Checker):
     kind = "reference"
 
     def __init__(self):
-        super().__init__(REFERENCE_SO)
+        # RTLD_GLOBAL: a ggml backend library under test resolves its ggml symbols against this build of ggml
+        super().__init__(REFERENCE_SO, mode=C.RTLD_GLOBAL)
         self.lib.ref_isa.restype = C.c_char_p
+        self.lib.ref_moe_layer_backend.argtypes = [C.POINTER(MoeArgs), C.c_void_p, C.c_int]
+        self.lib.ref_moe_layer_backend.restype = C.c_int
+        self.lib.ref_backend_free.argtypes = [C.c_void_p]
+        self.lib.ref_backend_free.restype = None
 
     def isa(self) -> str:
         return self.lib.ref_isa().decode()

@@ -108,27 +108,33 @@ static ggml_tensor * scaled(ggml_context * c, ggml_tensor * mm, ggml_tensor * sc
     return ggml_mul(c, mm, s);
 }
 
-int ref_moe_layer(const ref_moe_args * a) {
+// backend == null: the reference's CPU backend (created and freed here).  Otherwise the same graph is computed on the
+// given ggml backend (the caller keeps ownership) - this is how a ggml backend under test is driven by the reference's
+// own graph.  use_gallocr != 0 allocates the graph's intermediate tensors with ggml's graph allocator (memory reused
+// between tensors, as in edge0-infer's exec::build_plan) instead of giving every tensor its own memory.
+static int run_layer(const ref_moe_args * a, ggml_backend_t backend, int use_gallocr) {
     const int H = a->H, L = a->latent ? a->L : a->H, E = a->E, K = a->K, I = a->I, T = a->T;
     const ggml_type wt = (ggml_type) a->wtype;
 
-    ggml_init_params ip = { ggml_tensor_overhead() * 256 + ggml_graph_overhead_custom(512, false), nullptr, true };
-    ggml_context * c = ggml_init(ip);
-    if (!c) return 1;
+    ggml_init_params ipw = { ggml_tensor_overhead() * 32, nullptr, true };
+    ggml_init_params ip  = { ggml_tensor_overhead() * 256 + ggml_graph_overhead_custom(512, false), nullptr, true };
+    ggml_context * cw = ggml_init(ipw);
+    ggml_context * c  = ggml_init(ip);
+    if (!c || !cw) return 1;
 
-    ggml_tensor * x   = ggml_new_tensor_2d(c, GGML_TYPE_F32, H, T);
-    ggml_tensor * rw  = ggml_new_tensor_2d(c, GGML_TYPE_F32, H, E);
-    ggml_tensor * rb  = a->router_bias ? ggml_new_tensor_1d(c, GGML_TYPE_F32, E) : nullptr;
-    ggml_tensor * wg  = ggml_new_tensor_3d(c, wt, L, I, E);
-    ggml_tensor * wu  = ggml_new_tensor_3d(c, wt, L, I, E);
-    ggml_tensor * wd  = ggml_new_tensor_3d(c, wt, I, L, E);
-    ggml_tensor * sg  = a->s_gate ? ggml_new_tensor_1d(c, GGML_TYPE_F32, E) : nullptr;
-    ggml_tensor * su  = a->s_up   ? ggml_new_tensor_1d(c, GGML_TYPE_F32, E) : nullptr;
-    ggml_tensor * sd  = a->s_down ? ggml_new_tensor_1d(c, GGML_TYPE_F32, E) : nullptr;
-    ggml_tensor * ld  = a->latent ? ggml_new_tensor_2d(c, wt, H, L) : nullptr;
-    ggml_tensor * lu  = a->latent ? ggml_new_tensor_2d(c, wt, L, H) : nullptr;
-    ggml_tensor * sld = (a->latent && a->s_lat_d) ? ggml_new_tensor_1d(c, GGML_TYPE_F32, 1) : nullptr;
-    ggml_tensor * slu = (a->latent && a->s_lat_u) ? ggml_new_tensor_1d(c, GGML_TYPE_F32, 1) : nullptr;
+    ggml_tensor * x   = ggml_new_tensor_2d(cw, GGML_TYPE_F32, H, T);
+    ggml_tensor * rw  = ggml_new_tensor_2d(cw, GGML_TYPE_F32, H, E);
+    ggml_tensor * rb  = a->router_bias ? ggml_new_tensor_1d(cw, GGML_TYPE_F32, E) : nullptr;
+    ggml_tensor * wg  = ggml_new_tensor_3d(cw, wt, L, I, E);
+    ggml_tensor * wu  = ggml_new_tensor_3d(cw, wt, L, I, E);
+    ggml_tensor * wd  = ggml_new_tensor_3d(cw, wt, I, L, E);
+    ggml_tensor * sg  = a->s_gate ? ggml_new_tensor_1d(cw, GGML_TYPE_F32, E) : nullptr;
+    ggml_tensor * su  = a->s_up   ? ggml_new_tensor_1d(cw, GGML_TYPE_F32, E) : nullptr;
+    ggml_tensor * sd  = a->s_down ? ggml_new_tensor_1d(cw, GGML_TYPE_F32, E) : nullptr;
+    ggml_tensor * ld  = a->latent ? ggml_new_tensor_2d(cw, wt, H, L) : nullptr;
+    ggml_tensor * lu  = a->latent ? ggml_new_tensor_2d(cw, wt, L, H) : nullptr;
+    ggml_tensor * sld = (a->latent && a->s_lat_d) ? ggml_new_tensor_1d(cw, GGML_TYPE_F32, 1) : nullptr;
+    ggml_tensor * slu = (a->latent && a->s_lat_u) ? ggml_new_tensor_1d(cw, GGML_TYPE_F32, 1) : nullptr;
 
     // ---- route (forward.cpp:262-271)
     ggml_tensor * logits = ggml_mul_mat(c, rw, x);                       // [E, T]
@@ -170,13 +176,29 @@ int ref_moe_layer(const ref_moe_args * a) {
     ggml_tensor * keep[] = { logits, probs, wts, hid, down, moe, out, ids_c };
     for (ggml_tensor * t : keep) ggml_set_output(t);
 
-    ggml_backend_t be = ggml_backend_cpu_init();
-    if (!be) { ggml_free(c); return 2; }
-    ggml_backend_cpu_set_n_threads(be, a->n_threads > 0 ? a->n_threads : 1);
+    ggml_backend_t be = backend ? backend : ggml_backend_cpu_init();
+    if (!be) { ggml_free(c); ggml_free(cw); return 2; }
+    if (!backend) ggml_backend_cpu_set_n_threads(be, a->n_threads > 0 ? a->n_threads : 1);
 
-    // leaf tensors and graph results both live in one backend buffer
-    ggml_backend_buffer_t buf = ggml_backend_alloc_ctx_tensors(c, be);
-    if (!buf) { ggml_backend_free(be); ggml_free(c); return 3; }
+    // weights and the input in one backend buffer; graph results in a second one or under the graph allocator
+    ggml_backend_buffer_t bufw = ggml_backend_alloc_ctx_tensors(cw, be);
+    ggml_backend_buffer_t buf  = nullptr;
+    ggml_gallocr_t galloc = nullptr;
+    bool ok = bufw != nullptr;
+    if (ok && use_gallocr) {
+        galloc = ggml_gallocr_new(ggml_backend_get_default_buffer_type(be));
+        ok = galloc && ggml_gallocr_alloc_graph(galloc, g);
+    } else if (ok) {
+        buf = ggml_backend_alloc_ctx_tensors(c, be);
+        ok = buf != nullptr;
+    }
+    if (!ok) {
+        if (galloc) ggml_gallocr_free(galloc);
+        if (bufw) ggml_backend_buffer_free(bufw);
+        if (!backend) ggml_backend_free(be);
+        ggml_free(c); ggml_free(cw);
+        return 3;
+    }
 
     auto set = [](ggml_tensor * t, const void * p) { if (t && p) ggml_backend_tensor_set(t, p, 0, ggml_nbytes(t)); };
     set(x, a->x); set(rw, a->router_w); set(rb, a->router_bias);
@@ -214,11 +236,22 @@ int ref_moe_layer(const ref_moe_args * a) {
         }
     }
 
-    ggml_backend_buffer_free(buf);
-    ggml_backend_free(be);
+    if (galloc) ggml_gallocr_free(galloc);
+    if (buf) ggml_backend_buffer_free(buf);
+    ggml_backend_buffer_free(bufw);
+    if (!backend) ggml_backend_free(be);
     ggml_free(c);
+    ggml_free(cw);
     return rc;
 }
+
+int ref_moe_layer(const ref_moe_args * a) { return run_layer(a, nullptr, 0); }
+
+int ref_moe_layer_backend(const ref_moe_args * a, void * backend, int use_gallocr) {
+    return run_layer(a, (ggml_backend_t) backend, use_gallocr);
+}
+
+void ref_backend_free(void * backend) { if (backend) ggml_backend_free((ggml_backend_t) backend); }
 
 const char * ref_isa(void) {
     static char buf[256];

@@ -64,3 +64,24 @@ def test_q3k_quantiser_matches_reference_bytes():
         w = rng.normal(0, 0.02, (4, 24, 768)).astype(np.float32)
         w[0, 0, :32] = 0
         assert np.array_equal(moe.quantize_q3_K(w), O.reference().quantize(TYPE_Q3_K, w))
+
+
+def test_ggml_adapter_loads_without_gpu():
+    """libggml-b200.so (built where the host application's ggml headers are present) loads next to that ggml, exports
+    the entry points include/ggml-b200.h declares, and reports no device on a machine without a B200."""
+    import ctypes as C
+    import os
+    from oracle import oracle as O
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    adapter = os.path.join(root, "edge0_b200", "lib", "libggml-b200.so")
+    if not os.path.exists(adapter) or not O.have_reference():
+        pytest.skip("adapter or compiled reference ggml not built here")
+    O.reference()   # ggml symbols, RTLD_GLOBAL
+    lib = C.CDLL(adapter)
+    for name in ("ggml_backend_b200_reg", "ggml_backend_b200_init", "ggml_backend_is_b200", "ggml_backend_b200_buffer_type",
+                 "ggml_backend_b200_set_expert_path", "ggml_backend_b200_graph_stats", "ggml_backend_b200_last_error"):
+        assert hasattr(lib, name), name
+    import torch
+    if not torch.cuda.is_available():
+        lib.ggml_backend_b200_init.restype = C.c_void_p
+        assert lib.ggml_backend_b200_init(0) is None
