@@ -151,6 +151,7 @@ def run_b200_arm(args):
 
     from edge0_b200 import moe
     from edge0_b200 import workloads as W
+    from edge0_b200.capi import TYPE_NVFP4
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -281,7 +282,13 @@ def run_b200_arm(args):
     gu_us = ms_gu / max(n_gu, 1) * 1e3
     dn_us = ms_dn / max(n_dn, 1) * 1e3
     achieved = gu_bytes / (gu_us * 1e-6) / 1e9 if n_gu else 0.0
-    roofline = {"bound": "hbm", "kernel": "expert_gemv_kernel<DUAL> (gate+up+SwiGLU)", "achieved": achieved, "peak": peak, "unit": "GB/s",
+    # which engine the library's policy picked for gate/up (documented at b200moe_set_expert_path)
+    rows = T * cfg.top_k
+    can_tc = cfg.wtype == TYPE_NVFP4 and cfg.n_ff % 128 == 0 and cfg.n_in % 128 == 0
+    gu_tensor = can_tc and (args.expert_path == 2 or (args.expert_path == 0 and rows >= 2 * cfg.n_expert and T <= 512))
+    gu_kernel = ("expert_gemm_nvfp4_kernel<DUAL> (tcgen05 grouped GEMM: gate+up+SwiGLU)" if gu_tensor
+                 else "expert_gemv_kernel<DUAL> (integer GEMV: gate+up+SwiGLU)")
+    roofline = {"bound": "hbm", "kernel": gu_kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": None, "peak_source": peak_kind, "algorithmic_bytes_per_launch": gu_bytes,
                 "avg_launch_us": gu_us,
                 "down_kernel": {"achieved": dn_bytes / (dn_us * 1e-6) / 1e9 if n_dn else 0.0, "avg_launch_us": dn_us,
@@ -344,7 +351,8 @@ def run_b200_arm(args):
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                "dtype": "int8 x fp4 integer dots, fp32 accumulate", "data": "synthetic",
+                "dtype": ("fp16 (int8-grid activations as hi+lo, NVFP4 weights exact) on tcgen05, fp32 accumulate" if gu_tensor
+                          else "int8 x fp4 integer dots, fp32 accumulate"), "data": "synthetic",
                 "config": {"workload": f"{cfg.name} T={T} per GPU", "n_embd": cfg.n_embd, "n_expert": cfg.n_expert, "top_k": cfg.top_k,
                            "n_ff": cfg.n_ff, "n_latent": cfg.n_latent, "weights": "NVFP4 (ggml block_nvfp4) + fp32 per-expert scale",
                            "activations": "bf16 in, int8 grid of the reference (Q8_0) inside, fp32 out",

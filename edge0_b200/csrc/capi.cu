@@ -1,6 +1,7 @@
 // C ABI of the B200 MoE-FFN path (declared in include/edge0_b200_moe.h): context, device scratch,
 // argument validation and kernel dispatch.  No torch types, no host fallback: without a CUDA device
 // every compute entry point fails with B200MOE_ERR_NO_DEVICE / B200MOE_ERR_CUDA.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -15,6 +16,7 @@
 #include <vector>
 
 #include "../../include/edge0_b200_moe.h"
+#include "expert_gemm.cuh"
 #include "expert_gemv.cuh"
 #include "expert_mma.cuh"
 #include "router.cuh"
@@ -255,15 +257,63 @@ int launch_gemv(b200moe_ctx * ctx, int wtype, int k, const GemvParams & p, int n
     return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no expert kernel for type %d width %d", wtype, k);
 }
 
+// ---- tensor maps for the warp-specialised grouped GEMM (the encoder is a host-side driver entry point; looked up
+// once through the runtime so the library does not link against the driver library)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void * ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+        else
+            cudaGetLastError();
+    }
+    return fn;
+}
+
+// 2-D map over a row-major [outer][inner] array whose rows are pitch_bytes apart
+int make_map_2d(b200moe_ctx * ctx, CUtensorMap * m, CUtensorMapDataType dt, const void * base, uint64_t inner, uint64_t outer,
+                uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(ctx, B200MOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+    const cuuint64_t dims[2] = { inner, outer };
+    const cuuint64_t strides[1] = { pitch_bytes };
+    const cuuint32_t box[2] = { box_inner, box_outer };
+    const cuuint32_t estr[2] = { 1, 1 };
+    const CUresult r = fn(m, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ctx, B200MOE_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int) r);
+    return B200MOE_OK;
+}
+
 template <int K, bool DUAL, int NT>
-int launch_mma_t(b200moe_ctx * ctx, const MmaParams & p, cudaStream_t st) {
-    constexpr size_t smem = mma_smem_bytes<K, DUAL, NT>();
-    auto kern = expert_mma_nvfp4_kernel<K, DUAL, NT>;
+int launch_gemm_t(b200moe_ctx * ctx, const MmaParams & p, int rows, cudaStream_t st) {
+    using C = GemmCfg<K, DUAL, NT>;
+    auto kern = expert_gemm_nvfp4_kernel<K, DUAL, NT>;
     static bool configured = false;
     if (!configured) {
-        CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+        CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) C::SMEM));
         configured = true;
     }
+    constexpr uint64_t ROW_BYTES = K / 64 * 36;
+    CUtensorMap mw0, mw1, mhi, mlo;
+    int rc;
+    const uint64_t wrows = (uint64_t) p.n_as * p.n_out;
+    if ((rc = make_map_2d(ctx, &mw0, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.w0, ROW_BYTES, wrows, ROW_BYTES, GEMM_RAW_ROW, 128, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+    if (DUAL) {
+        if ((rc = make_map_2d(ctx, &mw1, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.w1, ROW_BYTES, wrows, ROW_BYTES, GEMM_RAW_ROW, 128, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+    } else {
+        mw1 = mw0;
+    }
+    if ((rc = make_map_2d(ctx, &mhi, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.act, K, (uint64_t) rows, (uint64_t) K * 2, 64, NT, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    if ((rc = make_map_2d(ctx, &mlo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.act_lo, K, (uint64_t) rows, (uint64_t) K * 2, 64, NT, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
     b200moe_ctx::Timed tm{};
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventCreate(&tm.beg));
@@ -271,25 +321,25 @@ int launch_mma_t(b200moe_ctx * ctx, const MmaParams & p, cudaStream_t st) {
         tm.kind = DUAL ? 0 : 1;
         CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
     }
-    kern<<<ctx->sm_count * (NT <= 32 ? 2 : 1), MMA_THREADS, smem, st>>>(p);
+    kern<<<ctx->sm_count, GEMM_THREADS, C::SMEM, st>>>(p, mw0, mw1, mhi, mlo);
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventRecord(tm.end, st));
         ctx->timed.push_back(tm);
     }
-    return check_launch(ctx, "expert_mma");
+    return check_launch(ctx, "expert_gemm");
+}
+
+// small_tiles: experts see few rows each (batched decode) -> 32-row token tiles, else 128
+template <bool DUAL>
+int launch_gemm(b200moe_ctx * ctx, int k, const MmaParams & p, int rows, bool small_tiles, cudaStream_t st) {
+#define GEMM_CASE(KK) case KK: return small_tiles ? launch_gemm_t<KK, DUAL, 32>(ctx, p, rows, st) : launch_gemm_t<KK, DUAL, 128>(ctx, p, rows, st);
+    switch (k) { GEMM_CASE(256) GEMM_CASE(512) GEMM_CASE(768) GEMM_CASE(1024) GEMM_CASE(2048) }
+#undef GEMM_CASE
+    return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no tensor-core expert kernel for width %d", k);
 }
 
 bool mma_supported(int wtype, int k, int n_out) {
     return wtype == TYPE_NVFP4 && n_out % 128 == 0 && (k == 256 || k == 512 || k == 768 || k == 1024 || k == 2048);
-}
-
-// small_tiles: experts see few rows each (batched decode) -> 32-row token tiles, two CTAs per SM
-template <bool DUAL>
-int launch_mma(b200moe_ctx * ctx, int k, const MmaParams & p, bool small_tiles, cudaStream_t st) {
-#define MMA_CASE(KK) case KK: return small_tiles ? launch_mma_t<KK, DUAL, 32>(ctx, p, st) : launch_mma_t<KK, DUAL, 128>(ctx, p, st);
-    switch (k) { MMA_CASE(256) MMA_CASE(512) MMA_CASE(768) MMA_CASE(1024) MMA_CASE(2048) }
-#undef MMA_CASE
-    return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no tensor-core expert kernel for width %d", k);
 }
 
 // expert-sorted fp16 copy of quantised activations (input of the tensor-core kernels)
@@ -478,20 +528,21 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
     const int k = l->n_expert_used, rows = T * k;
     const int nt = tokens_per_pass(rows, l->n_expert);
     int rc;
-    // Tensor-core grouped GEMM once experts see several rows each (its cost per expert does not grow with the rows up to 128);
-    // integer GEMV below that.  Both keep activations on the reference's int8 grid.
     // Which engine runs which matmul.  The integer kernels reproduce the reference's fp32 summation order and are
-    // bit-identical to the CPU path.  The tensor-core grouped GEMM (tcgen05, kind::f16) adds ~3e-5 of RMS of its own
+    // bit-identical to the CPU path; their cost grows with the rows an expert receives.  The tensor-core grouped GEMM
+    // (tcgen05, kind::f16; cost per expert independent of its rows up to the tile size) adds ~3e-5 of RMS of its own
     // accumulation error: after `down` nothing is re-quantised, so there it only costs ~1e-5 on the output; on gate/up it
-    // moves values of `hidden` across int8 rounding boundaries of the re-quantisation (output error 1.7e-3 at 64 tokens,
-    // 1.05e-2 at 4096), so gate/up only goes to the tensor cores when asked for.
-    //   path 0 (default): bit-exact integer gate/up; down on tensor cores once experts see several rows
+    // moves a few values of `hidden` across int8 rounding boundaries of the re-quantisation (output error 2e-3 of RMS at
+    // 64 tokens, 4e-3 at 256, 1.05e-2 at 4096 against the bar of 1e-2), so by default gate/up goes to the tensor
+    // cores only up to 512 tokens.
+    //   path 0 (default): tensor cores for down, and for gate/up up to 512 tokens, once experts see several rows each
     //   path 1: integer everywhere (whole layer bit-identical to the reference)
     //   path 2: tensor cores wherever the shape allows;  path 3: integer gate/up, tensor-core down at any batch size
     const bool can_mma = mma_supported(l->wtype, n_in, l->n_ff) && mma_supported(l->wtype, l->n_ff, n_in);
     const bool many_rows = rows >= 2 * l->n_expert;
-    const bool mma_down = can_mma && (ctx->expert_path == 2 || ctx->expert_path == 3 || (ctx->expert_path == 0 && many_rows));
-    const bool mma_gu = can_mma && ctx->expert_path == 2;
+    const int path = ctx->expert_path;
+    const bool mma_down = can_mma && (path == 2 || path == 3 || (path == 0 && many_rows));
+    const bool mma_gu = can_mma && (path == 2 || (path == 0 && many_rows && T <= 512));
     const bool small_tiles = rows < 24 * l->n_expert;   // on average fewer than 24 rows per expert
     auto mp = [&](const void * w0, const void * w1, const float * s0, const float * s1, float * out, int n_out, int m_k) {
         MmaParams m{};
@@ -502,7 +553,8 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
     };
     if (mma_gu) {
         if ((rc = launch_sorted_act(ctx, xq, rows, n_in, k, 1, st))) return rc;
-        if ((rc = launch_mma<true>(ctx, n_in, mp(l->gate, l->up, l->gate_scale, l->up_scale, p.hid, l->n_ff, n_in), small_tiles, st))) return rc;
+        const MmaParams m = mp(l->gate, l->up, l->gate_scale, l->up_scale, p.hid, l->n_ff, n_in);
+        if ((rc = launch_gemm<true>(ctx, n_in, m, rows, small_tiles, st))) return rc;
     } else {
         GemvParams gu = gemv_params(ctx, l->gate, l->up, l->gate_scale, l->up_scale, xq, p.hid, l->n_ff, k, 1, l->n_expert);
         if ((rc = launch_gemv<true>(ctx, l->wtype, n_in, gu, nt, st))) return rc;
@@ -510,7 +562,8 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
     if ((rc = launch_quantize<float>(ctx, p.hid, l->n_ff, p.hq, rows, l->n_ff, l->wtype, st))) return rc;
     if (mma_down) {
         if ((rc = launch_sorted_act(ctx, p.hq, rows, l->n_ff, k, k, st))) return rc;
-        if ((rc = launch_mma<false>(ctx, l->n_ff, mp(l->down, nullptr, l->down_scale, nullptr, p.y, n_in, l->n_ff), small_tiles, st))) return rc;
+        const MmaParams m = mp(l->down, nullptr, l->down_scale, nullptr, p.y, n_in, l->n_ff);
+        if ((rc = launch_gemm<false>(ctx, l->n_ff, m, rows, small_tiles, st))) return rc;
     } else {
         GemvParams dn = gemv_params(ctx, l->down, nullptr, l->down_scale, nullptr, p.hq, p.y, n_in, k, k, l->n_expert);
         if ((rc = launch_gemv<false>(ctx, l->wtype, l->n_ff, dn, nt, st))) return rc;

@@ -109,12 +109,13 @@ B200MOE_API int  b200moe_synchronize(b200moe_ctx * ctx, void * stream); /* ggml_
 
 /* Which kernels run the expert matmuls (reference: model option switches such as `routing` / `experts`,
  * edge0-infer/docs/configuration.md:62-72; plain struct-style option, no environment variables):
- *   0  default: gate/up on the integer kernels, which follow the reference's fp32 summation order and are bit-identical to
- *      the CPU path; `down` on the tcgen05 grouped GEMM once experts see several rows each (its ~3e-5 accumulation error is
- *      not re-quantised afterwards and costs ~1e-5 of RMS on the output)
+ *   0  default: below two routed rows per expert everything runs on the integer kernels, which follow the reference's fp32
+ *      summation order and are bit-identical to the CPU path.  Above that `down` runs on the tcgen05 grouped GEMM (its ~3e-5
+ *      accumulation error is not re-quantised afterwards: ~1e-5 of RMS on the output) and, up to 512 tokens, so does gate/up
+ *      (re-quantisation of `hidden` amplifies the GEMM's error: 2e-3 of RMS on the output at 64 tokens, 4e-3 at 256)
  *   1  integer kernels everywhere: the whole layer is bit-identical to the reference CPU path
  *   2  tcgen05 grouped GEMM wherever the type and widths allow (NVFP4, n_ff and n_in multiples of 128); fastest for prefill,
- *      output error 2e-3 of RMS at 64 tokens growing to 1e-2 at 4096 (re-quantisation of `hidden` amplifies the GEMM's error)
+ *      output error growing to 1e-2 of RMS at 4096 tokens
  *   3  integer gate/up, tcgen05 down at any batch size */
 B200MOE_API int  b200moe_set_expert_path(b200moe_ctx * ctx, int path);
 

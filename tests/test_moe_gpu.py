@@ -3,10 +3,11 @@
 * Routing (logits, probabilities, ids, weights) is bit-exact.
 * The integer expert kernels follow the reference's fp32 summation order: with them (expert path 1) `hidden`, `down` and
   the layer output are BIT-IDENTICAL to the CPU path, for NVFP4 and Q3_K, plain and latent layers, 1 to 4096 tokens.
-* The default path sends `down` to the tcgen05 grouped GEMM once experts see several rows: `hidden` stays bit-identical,
-  `down`/output differ by the tensor core's accumulation error (bar here 2e-4 of RMS; measured ~3e-5).
-* Expert path 2 (tensor cores for gate/up too) is checked against the stated bar of the path, max-abs <= 1e-2 * RMS of the
-  reference output; its `hidden` error is re-quantised by the reference algorithm, which amplifies it.
+* The default path keeps everything on the integer kernels below two routed rows per expert (bit-identical).  Above that
+  `down` goes to the tcgen05 grouped GEMM (`down`/output differ by the tensor core's accumulation error: bar here 2e-4 of
+  RMS, measured ~3e-5) and, up to 512 tokens, so does gate/up: then `hidden` carries that error too, the reference's
+  re-quantisation of `hidden` amplifies it, and the outputs are held to the stated bar of the path, max-abs <= 1e-2 * RMS.
+* Expert path 2 forces the tensor cores wherever the shape allows; path 3 keeps gate/up on the integer kernels.
 """
 import os
 
@@ -34,6 +35,17 @@ def q3k_quantizer(checker):
     return moe.quantize_q3_K
 
 
+def expected_engines(cfg, T, path):
+    """(gate/up on tensor cores, down on tensor cores) under the library's documented policy for b200moe_set_expert_path."""
+    rows = T * cfg.top_k
+    can = cfg.wtype == TYPE_NVFP4 and cfg.n_ff % 128 == 0 and cfg.n_in % 128 == 0 and \
+        all(k in (256, 512, 768, 1024, 2048) for k in (cfg.n_ff, cfg.n_in))
+    many = rows >= 2 * cfg.n_expert
+    gu = can and (path == 2 or (path == 0 and many and T <= 512))
+    down = can and (path in (2, 3) or (path == 0 and many))
+    return gu, down
+
+
 def run_and_compare(gpu_ctx, checker, layer, x_np, bf16, path=0):
     gpu_ctx.set_expert_path(path)
     try:
@@ -52,11 +64,12 @@ def run_and_compare(gpu_ctx, checker, layer, x_np, bf16, path=0):
     assert np.array_equal(ob.weights_norm.cpu().numpy(), r.weights)
     hidden, down, o = ob.hidden.cpu().numpy(), ob.down.cpu().numpy(), out.cpu().numpy()
     errs = dict(hidden=rel_err(hidden, r.hidden), down=rel_err(down, r.down_out), out=rel_err(o, r.out))
-    if path in (0, 1, 3):
+    gu_tensor, down_tensor = expected_engines(layer.cfg, x_np.shape[0], path)
+    if not gu_tensor:
         assert np.array_equal(hidden, r.hidden), ("hidden must be bit-identical on the integer gate/up kernels", errs)
-    if path == 1:
+    if not gu_tensor and not down_tensor:
         assert np.array_equal(down, r.down_out) and np.array_equal(o, r.out), ("integer path must be bit-identical", errs)
-    elif path in (0, 3):
+    elif not gu_tensor:
         assert errs["down"] <= 2e-4 and errs["out"] <= 2e-4, errs       # tensor-core down: accumulation error only
     else:
         assert errs["hidden"] <= 5e-4 and errs["down"] <= 3 * TOL and errs["out"] <= TOL, errs
@@ -235,7 +248,8 @@ def test_host_entry_point_and_determinism(gpu_ctx, checker):
     assert torch.equal(o1, o2), "two runs must give identical bytes"
     r = checker.moe_layer(x=x_np, **layer.checker_kwargs())
     assert np.array_equal(ids.numpy(), r.ids)
-    assert rel_err(o1.numpy(), r.out) <= 2e-4
+    # 48 routed rows over 16 experts: the default policy runs gate/up and down on the tensor cores (bar of that path)
+    assert rel_err(o1.numpy(), r.out) <= TOL
 
 
 def test_argument_errors_do_not_launch(gpu_ctx):
