@@ -17,7 +17,7 @@
 //
 // Rings and their barriers (count of arrivals that complete a phase):
 //   raw_full[RS]  (1 + bytes)  producer arms with the byte count      raw_empty[RS]  (8)  one arrival per dequant warp
-//   tile_full[TS] (8 + 1 + bytes) dequant warps + activation producer  tile_empty[TS] (1)  tcgen05.commit
+//   tile_full[TS] (256 + 1 + bytes) dequant threads + activation producer  tile_empty[TS] (1)  tcgen05.commit
 //   acc_full[2]   (1)  tcgen05.commit after the last K step           acc_empty[2]   (4)  one arrival per epilogue warp
 // Every wait is bounded in time and also gives up as soon as any role has reported a failure.
 #pragma once
@@ -42,11 +42,16 @@ __device__ __forceinline__ void tma_load_2d(void * dst_smem, const CUtensorMap *
                  : "memory");
 }
 
-// bounded wait that also returns when another role has given up; reports a timeout itself
+// Bounded wait that also returns when another role has given up; reports a timeout itself.
+// SLEEP_NS > 0: the warp sleeps between polls.  A polling warp otherwise competes for issue slots with the dequantising
+// warps of its scheduler (measured: more than half of all issued instructions were polls); roles that wait most of the
+// time (producers, epilogue, MMA issuer) therefore back off.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool wait_or_abort(uint64_t * bar, uint32_t parity, volatile int * abort_flag, int * err) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     for (uint32_t i = 0; i < (1u << 30); ++i) {
+        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63) == 63) {
             if (*abort_flag) return false;
@@ -138,7 +143,7 @@ expert_gemm_nvfp4_kernel(const MmaParams p, const __grid_constant__ CUtensorMap 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 8); }
-        for (int i = 0; i < TS; ++i) { mbar_init(&tile_full[i], 9); mbar_init(&tile_empty[i], 1); }
+        for (int i = 0; i < TS; ++i) { mbar_init(&tile_full[i], 256 + 1); mbar_init(&tile_empty[i], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
         mbar_fence_init();
         s_abort = 0;
@@ -171,7 +176,7 @@ expert_gemm_nvfp4_kernel(const MmaParams p, const __grid_constant__ CUtensorMap 
                 const int row0 = e * p.n_out + mt * 128;
                 for (int t0 = 0; t0 < n_e && !s_abort; t0 += NT) {
                     for (int kc = 0; kc < KC; ++kc) {
-                        if (!wait_or_abort(&raw_empty[raw.stage], raw.phase ^ 1u, &s_abort, p.err)) break;
+                        if (!wait_or_abort<200>(&raw_empty[raw.stage], raw.phase ^ 1u, &s_abort, p.err)) break;
                         uint8_t * dst = raws + (size_t) raw.stage * C::RAW_STAGE;
                         mbar_arrive_expect_tx(&raw_full[raw.stage], C::RAW_STAGE);
                         tma_load_2d(dst, &map_w0, kc * GEMM_RAW_ROW, row0, &raw_full[raw.stage]);
@@ -190,7 +195,7 @@ expert_gemm_nvfp4_kernel(const MmaParams p, const __grid_constant__ CUtensorMap 
                 const int row_beg = p.offsets[e], n_e = p.offsets[e + 1] - row_beg;
                 for (int t0 = 0; t0 < n_e && !s_abort; t0 += NT) {
                     for (int ks = 0; ks < K / 64; ++ks) {
-                        if (!wait_or_abort(&tile_empty[tile.stage], tile.phase ^ 1u, &s_abort, p.err)) break;
+                        if (!wait_or_abort<100>(&tile_empty[tile.stage], tile.phase ^ 1u, &s_abort, p.err)) break;
                         uint8_t * st = tiles + (size_t) tile.stage * C::STAGE + NTENS * C::A_TILE;
                         mbar_arrive_expect_tx(&tile_full[tile.stage], 2 * C::B_TILE);
                         tma_load_2d(st, &map_hi, ks * 64, row_beg + t0, &tile_full[tile.stage]);
@@ -211,11 +216,11 @@ expert_gemm_nvfp4_kernel(const MmaParams p, const __grid_constant__ CUtensorMap 
                     const int nt = min(NT, n_e - t0);
                     const int n_mma = max(16, (nt + 15) & ~15);
                     const uint32_t idesc = umma_idesc_f16(n_mma);
-                    if (!wait_or_abort(&acc_empty[acc.stage], acc.phase ^ 1u, &s_abort, p.err)) break;
+                    if (!wait_or_abort<40>(&acc_empty[acc.stage], acc.phase ^ 1u, &s_abort, p.err)) break;
                     tc_fence_after();
                     const uint32_t d0 = tmem + (uint32_t) acc.stage * (NTENS * NT);
                     for (int ks = 0; ks < K / 64; ++ks) {
-                        if (!wait_or_abort(&tile_full[tile.stage], tile.phase, &s_abort, p.err)) break;
+                        if (!wait_or_abort<40>(&tile_full[tile.stage], tile.phase, &s_abort, p.err)) break;
                         tc_fence_after();
                         // Descriptors differ only in their 14-bit start-address field (16-byte units): one 32-bit add each.
                         const uint32_t da = DESC_LO | (smem_u32(tiles + (size_t) tile.stage * C::STAGE) >> 4);
@@ -252,7 +257,9 @@ expert_gemm_nvfp4_kernel(const MmaParams p, const __grid_constant__ CUtensorMap 
             const int feature = mt * 128 + q * 32 + lane;
             for (int t0 = 0; t0 < n_e && !s_abort; t0 += NT) {
                 const int nt = min(NT, n_e - t0);
-                if (!wait_or_abort(&acc_full[acc.stage], acc.phase, &s_abort, p.err)) break;
+                // lanes leave the polling loop one by one: the vote reconverges the warp (tcgen05.ld below needs all of it)
+                // and makes the outcome uniform
+                if (!__all_sync(0xffffffffu, wait_or_abort<200>(&acc_full[acc.stage], acc.phase, &s_abort, p.err))) break;
                 tc_fence_after();
                 const uint32_t d0 = tmem + (uint32_t) acc.stage * (NTENS * NT) + ((uint32_t) (q * 32) << 16);
                 for (int cb = 0; cb < nt; cb += 16) {
@@ -294,7 +301,7 @@ expert_gemm_nvfp4_kernel(const MmaParams p, const __grid_constant__ CUtensorMap 
             const int n_e = p.offsets[e + 1] - p.offsets[e];
             for (int t0 = 0; t0 < n_e && !s_abort; t0 += NT) {
                 for (int kc = 0; kc < KC && !s_abort; ++kc) {
-                    if (!wait_or_abort(&raw_full[raw.stage], raw.phase, &s_abort, p.err)) break;
+                    if (!__all_sync(0xffffffffu, wait_or_abort(&raw_full[raw.stage], raw.phase, &s_abort, p.err))) break;
                     uint32_t R[36];                // 4 blocks of [scale word][8 qs words]
                     {
                         const uint4 * src = reinterpret_cast<const uint4 *>(raws + (size_t) raw.stage * C::RAW_STAGE + raw_off);
@@ -309,7 +316,7 @@ expert_gemm_nvfp4_kernel(const MmaParams p, const __grid_constant__ CUtensorMap 
                     raw.template advance<RS>();
 #pragma unroll
                     for (int kb = 0; kb < 4; ++kb) {
-                        if (!wait_or_abort(&tile_empty[tile.stage], tile.phase ^ 1u, &s_abort, p.err)) break;
+                        if (!__all_sync(0xffffffffu, wait_or_abort(&tile_empty[tile.stage], tile.phase ^ 1u, &s_abort, p.err))) break;
                         uint8_t * st = tiles + (size_t) tile.stage * C::STAGE;
                         const uint32_t wd = R[9 * kb] >> (8 * sb0);
 #pragma unroll
@@ -332,9 +339,11 @@ expert_gemm_nvfp4_kernel(const MmaParams p, const __grid_constant__ CUtensorMap 
                             *reinterpret_cast<uint4 *>(st + a_off[2 * i]) = make_uint4(h[0], h[1], h[2], h[3]);
                             *reinterpret_cast<uint4 *>(st + a_off[2 * i + 1]) = make_uint4(h[4], h[5], h[6], h[7]);
                         }
-                        fence_async_smem();   // generic-proxy writes -> visible to the tensor core's reads
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&tile_full[tile.stage]);
+                        // Every writer orders its own stores against the tensor core's (async proxy) reads and then arrives
+                        // itself.  (One elected arrival per warp after __syncwarp was measured to let the MMA read rows of the
+                        // last-arriving warp before they were visible.)
+                        fence_async_smem();
+                        mbar_arrive(&tile_full[tile.stage]);
                         tile.template advance<TS>();
                     }
                 }

@@ -80,9 +80,11 @@ __device__ __forceinline__ uint32_t sw128_offset(int r, int c) { return (uint32_
 // fp16(q * d) of the routed rows, gathered into expert order (row i of the output is routed row perm[i]) so every expert's
 // rows are contiguous.  Within each group of 16 K positions the elements are stored in the order
 // [0,8,1,9,2,10,3,11,4,12,5,13,6,14,7,15], the order in which the NVFP4 nibbles of a sub-block unpack.
-// One warp per (sorted row, 32-element activation block).
+// One warp per (sorted row, 32-element activation block).  Rows are row_stride halfs apart in both planes: K with the lo
+// plane stored after the hi plane, 2K with out_lo = out_hi + K when hi and lo rows alternate.
 __global__ void __launch_bounds__(256) sorted_act_fp16_kernel(ActQuant act, const int * __restrict__ perm, int rows, int K, int n_ids,
-                                                             int ne11, __half * __restrict__ out_hi, __half * __restrict__ out_lo) {
+                                                             int ne11, __half * __restrict__ out_hi, __half * __restrict__ out_lo,
+                                                             int row_stride) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     const int nb = K / 32;
     if (warp >= rows * nb) return;
@@ -95,7 +97,7 @@ __global__ void __launch_bounds__(256) sorted_act_fp16_kernel(ActQuant act, cons
     const int pos = (e < 8) ? 2 * e : 2 * (e - 8) + 1;        // 0->0, 8->1, 1->2, 9->3, ...
     const float v = __fmul_rn((float) q, d);
     const __half hi = __float2half_rn(v);
-    const size_t o = (size_t) i * K + b * 32 + (lane & 16) + pos;
+    const size_t o = (size_t) i * row_stride + b * 32 + (lane & 16) + pos;
     out_hi[o] = hi;
     out_lo[o] = __float2half_rn(__fsub_rn(v, __half2float(hi)));
 }
