@@ -285,7 +285,7 @@ def run_b200_arm(args):
     # which engine the library's policy picked for gate/up (documented at b200moe_set_expert_path)
     rows = T * cfg.top_k
     can_tc = cfg.wtype == TYPE_NVFP4 and cfg.n_ff % 128 == 0 and cfg.n_in % 128 == 0
-    gu_tensor = can_tc and (args.expert_path == 2 or (args.expert_path == 0 and rows >= 2 * cfg.n_expert and T <= 512))
+    gu_tensor = can_tc and (args.expert_path == 2 or (args.expert_path == 0 and rows >= 2 * cfg.n_expert and rows <= 4096))
     gu_kernel = ("expert_gemm_nvfp4_kernel<DUAL> (tcgen05 grouped GEMM: gate+up+SwiGLU)" if gu_tensor
                  else "expert_gemv_kernel<DUAL> (integer GEMV: gate+up+SwiGLU)")
     roofline = {"bound": "hbm", "kernel": gu_kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -444,6 +444,16 @@ def run_c5_arm(args):
         t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
+    # per-phase device times of a few more steps (rank 0's view; not part of the timed region)
+    phases = {}
+    n_ph = min(8, max(1, args.steps))
+    for i in range(n_ph):
+        eps[i % n_sets].enable_phase_timing(True)
+        step(i)
+        for k, v in eps[i % n_sets].phase_times_ms().items():
+            phases[k] = phases.get(k, 0.0) + v / n_ph
+        eps[i % n_sets].enable_phase_timing(False)
+    barrier()
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -461,12 +471,13 @@ def run_c5_arm(args):
     if rank == 0:
         line = {"metric": METRIC, "value": T * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "int8 x fp4 integer dots, fp32 accumulate", "data": "synthetic",
+                "dtype": "int8-grid activations x NVFP4 weights (integer dots or fp16 hi+lo on tcgen05 by the library's policy), fp32 accumulate", "data": "synthetic",
                 "config": {"workload": f"{cfg.name} T={T} total", "n_embd": cfg.n_embd, "n_latent": cfg.n_latent, "n_expert": cfg.n_expert,
                            "top_k": cfg.top_k, "n_ff": cfg.n_ff, "parallelism": f"ep{world} (experts {per}/GPU, tokens {T // world}/GPU, NCCL all-to-all dispatch+combine)",
                            "l2": f"{n_sets} distinct weight sets rotated", "experts_touched_per_step": U, "expert_path": args.expert_path, "launch": "eager"},
                 "e2e": {"value": T * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * cfg.n_embd * 4,
                         "d2h_bytes_per_step": T * cfg.n_embd * 4, "ms_per_step": e2e_ms / args.steps},
+                "phases_ms": {k: round(v, 4) for k, v in phases.items()},
                 "gpu_launches": launches, "clocks": clocks,
                 "roofline": {"bound": "hbm", "kernel": "whole step (all ranks)", "achieved": alg / (step_ms * 1e-3) / 1e9, "peak": peak * world, "unit": "GB/s",
                              "frac": alg / (step_ms * 1e-3) / 1e9 / (peak * world), "traffic": None, "algorithmic_bytes_per_step": alg,

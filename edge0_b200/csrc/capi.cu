@@ -580,15 +580,19 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
     // accumulation error: after `down` nothing is re-quantised, so there it only costs ~1e-5 on the output; on gate/up it
     // moves a few values of `hidden` across int8 rounding boundaries of the re-quantisation (output error 2e-3 of RMS at
     // 64 tokens, 4e-3 at 256, 1.05e-2 at 4096 against the bar of 1e-2), so by default gate/up goes to the tensor
-    // cores only up to 512 tokens.
-    //   path 0 (default): tensor cores for down, and for gate/up up to 512 tokens, once experts see several rows each
+    // cores only up to 4096 routed rows (512 tokens at top-8).
+    //   path 0 (default): tensor cores for down, and for gate/up up to 4096 routed rows, once experts see several rows each
     //   path 1: integer everywhere (whole layer bit-identical to the reference)
     //   path 2: tensor cores wherever the shape allows;  path 3: integer gate/up, tensor-core down at any batch size
     const bool can_mma = mma_supported(l->wtype, n_in, l->n_ff) && mma_supported(l->wtype, l->n_ff, n_in);
     const bool many_rows = rows >= 2 * l->n_expert;
     const int path = ctx->expert_path;
-    const bool mma_down = can_mma && (path == 2 || path == 3 || (path == 0 && many_rows));
-    const bool mma_gu = can_mma && (path == 2 || (path == 0 && many_rows && T <= 512));
+    // A latent layer re-quantises once more after `down` (the up-projection), which amplifies the GEMM's error a second time
+    // (measured 1.7e-2 of RMS on the 512-expert latent configuration, 2.2e-3 with only `down` on tensor cores): by default
+    // latent layers stay on the integer kernels.
+    const bool dflt = path == 0 && many_rows && l->n_latent == 0;
+    const bool mma_down = can_mma && (path == 2 || path == 3 || dflt);
+    const bool mma_gu = can_mma && (path == 2 || (dflt && rows <= 4096));
     const bool small_tiles = rows < 24 * l->n_expert;   // on average fewer than 24 rows per expert
     auto mp = [&](const void * w0, const void * w1, const float * s0, const float * s1, float * out, int n_out, int m_k) {
         MmaParams m{};

@@ -88,8 +88,11 @@ class ExpertParallelLayer:
         """x_local: this rank's tokens [T_local, H] -> out [T_local, H]."""
         b, k = self.b, self.k
         T = x_local.shape[0]
+        mark = self._mark
+        mark("start")
         ids, w = b.route(x_local)                                    # [T,k]
         xl = b.project_down(x_local)                                 # [T,L] float32
+        mark("route+D")
         plan = plan_dispatch(ids, self.E, self.world, self.group)
         # pack: routed row r = t*k+s carries token t's latent row and its expert id
         tok = torch.div(plan.order, k, rounding_mode="floor").to(torch.int32)
@@ -98,15 +101,42 @@ class ExpertParallelLayer:
         recv_rows = exchange_rows(send_rows, plan.send_counts, plan.recv_counts, self.world, self.group)
         recv_eid = exchange_rows(send_eid, plan.send_counts, plan.recv_counts, self.world, self.group)
         local_eid = (recv_eid.reshape(-1) - self.rank * (self.E // self.world)).to(torch.int32)
+        mark("dispatch")
         y_rows = b.expert_rows(recv_rows, local_eid)                 # [R', L]
+        mark("experts")
         back = exchange_rows(y_rows, plan.recv_counts, plan.send_counts, self.world, self.group)   # ordered like send_rows
         # unpack: back[i] is routed row plan.order[i]; bring rows into (t, s) order
         inv = torch.empty_like(plan.order)
         inv[plan.order.long()] = torch.arange(plan.order.numel(), dtype=torch.int32, device=plan.order.device)
         y = b.gather_rows(back, inv).reshape(T, k, -1)
+        mark("return")
         moe = b.combine(y, w)                                        # slot-order weighted sum on the token's rank
         out = b.project_up(moe)
+        mark("combine+U")
         return (out, ids, w) if return_routing else out
+
+    # ---- per-phase device timing (off by default): CUDA events on the current stream at the phase boundaries
+    def enable_phase_timing(self, on: bool = True):
+        self._events = [] if on else None
+
+    def _mark(self, name: str):
+        ev = getattr(self, "_events", None)
+        if ev is None or not torch.cuda.is_available():
+            return
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        ev.append((name, e))
+
+    def phase_times_ms(self):
+        """{phase: milliseconds} of the last forward() since enable_phase_timing(); waits for the device."""
+        ev = getattr(self, "_events", None) or []
+        torch.cuda.synchronize()
+        out = {}
+        for (_, a), (name, bb) in zip(ev[:-1], ev[1:]):
+            if name != "start":
+                out[name] = out.get(name, 0.0) + a.elapsed_time(bb)
+        self._events = []
+        return out
 
 
 class CudaBackend:
@@ -116,6 +146,11 @@ class CudaBackend:
         from . import moe
         cfg = host_layer.cfg
         self.ctx, self.cfg = ctx, cfg
+        if cfg.n_latent:
+            # The owner of an expert sees a plain layer of the latent width and cannot know that its rows are re-quantised
+            # again by the up-projection on the token's rank: pin the bit-exact integer kernels, as the library does by
+            # default for a latent layer it sees whole.
+            ctx.set_expert_path(1)
         E, per = cfg.n_expert, cfg.n_expert // world
         lo, hi = rank * per, (rank + 1) * per
         if host_layer.gate.shape[0] == per and world > 1:      # generated for this shard only (make_layer(expert_range=...))

@@ -942,7 +942,7 @@ Registry * registry() {
             if (prop.major != 10) break;   // device indices stay equal to CUDA ordinals: stop at the first foreign device
             DeviceCtx c;
             c.index = i;
-            c.name = std::string(GGML_B200_NAME) + std::to_string(i);
+            c.name = std::string(GGML_B200_NAME) + "_" + std::to_string(i);
             c.description = prop.name;
             r->ctxs.push_back(c);
             r->devices.push_back(ggml_backend_device{ device_iface, &r->reg, &r->ctxs.back() });

@@ -111,8 +111,10 @@ B200MOE_API int  b200moe_synchronize(b200moe_ctx * ctx, void * stream); /* ggml_
  * edge0-infer/docs/configuration.md:62-72; plain struct-style option, no environment variables):
  *   0  default: below two routed rows per expert everything runs on the integer kernels, which follow the reference's fp32
  *      summation order and are bit-identical to the CPU path.  Above that `down` runs on the tcgen05 grouped GEMM (its ~3e-5
- *      accumulation error is not re-quantised afterwards: ~1e-5 of RMS on the output) and, up to 512 tokens, so does gate/up
+ *      accumulation error is not re-quantised afterwards: ~1e-5 of RMS on the output) and, up to 4096 routed rows (512 tokens at
+ *      top-8), so does gate/up
  *      (re-quantisation of `hidden` amplifies the GEMM's error: 2e-3 of RMS on the output at 64 tokens, 4e-3 at 256)
+ *      Latent layers (n_latent > 0) re-quantise once more after `down` and stay on the integer kernels by default.
  *   1  integer kernels everywhere: the whole layer is bit-identical to the reference CPU path
  *   2  tcgen05 grouped GEMM wherever the type and widths allow (NVFP4, n_ff and n_in multiples of 128); fastest for prefill,
  *      output error growing to 1e-2 of RMS at 4096 tokens

@@ -5,7 +5,7 @@
   the layer output are BIT-IDENTICAL to the CPU path, for NVFP4 and Q3_K, plain and latent layers, 1 to 4096 tokens.
 * The default path keeps everything on the integer kernels below two routed rows per expert (bit-identical).  Above that
   `down` goes to the tcgen05 grouped GEMM (`down`/output differ by the tensor core's accumulation error: bar here 2e-4 of
-  RMS, measured ~3e-5) and, up to 512 tokens, so does gate/up: then `hidden` carries that error too, the reference's
+  RMS, measured ~3e-5) and, up to 4096 routed rows, so does gate/up: then `hidden` carries that error too, the reference's
   re-quantisation of `hidden` amplifies it, and the outputs are held to the stated bar of the path, max-abs <= 1e-2 * RMS.
 * Expert path 2 forces the tensor cores wherever the shape allows; path 3 keeps gate/up on the integer kernels.
 """
@@ -40,8 +40,8 @@ def expected_engines(cfg, T, path):
     rows = T * cfg.top_k
     can = cfg.wtype == TYPE_NVFP4 and cfg.n_ff % 128 == 0 and cfg.n_in % 128 == 0 and \
         all(k in (256, 512, 768, 1024, 2048) for k in (cfg.n_ff, cfg.n_in))
-    many = rows >= 2 * cfg.n_expert
-    gu = can and (path == 2 or (path == 0 and many and T <= 512))
+    many = rows >= 2 * cfg.n_expert and not cfg.n_latent      # latent layers stay on the integer kernels by default
+    gu = can and (path == 2 or (path == 0 and many and rows <= 4096))
     down = can and (path in (2, 3) or (path == 0 and many))
     return gu, down
 
