@@ -40,7 +40,8 @@ def parse():
     ap.add_argument("--weight-sets", type=int, default=3, help="distinct weight copies rotated over (L2 defeat)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
-    ap.add_argument("--expert-path", type=int, default=0, help="0 library default, 1 integer (bit-exact) kernels, 2 tcgen05 GEMM, 3 integer gate/up + tcgen05 down")
+    ap.add_argument("--overlap", action="store_true", help="programmatic dependent launches between the kernels of a step (library default: off)")
+    ap.add_argument("--expert-path", type=int, default=0, help="0 library default, 1 integer (bit-exact) kernels, 2 tcgen05 GEMM, 3 integer gate/up + tcgen05 down, 4 tcgen05 GEMM + exact re-quantisation fix-up")
     ap.add_argument("--no-graph", action="store_true", help="launch every step's kernels from the host instead of replaying CUDA graphs")
     return ap.parse_args()
 
@@ -164,6 +165,7 @@ def run_b200_arm(args):
     cfg, T = workload_config(args)
     ctx = moe.Context(local)
     ctx.set_expert_path(args.expert_path)
+    ctx.set_launch_overlap(args.overlap)
     dev = torch.device("cuda", local)
 
     host = W.make_layer(cfg)
@@ -285,7 +287,7 @@ def run_b200_arm(args):
     # which engine the library's policy picked for gate/up (documented at b200moe_set_expert_path)
     rows = T * cfg.top_k
     can_tc = cfg.wtype == TYPE_NVFP4 and cfg.n_ff % 128 == 0 and cfg.n_in % 128 == 0
-    gu_tensor = can_tc and (args.expert_path == 2 or (args.expert_path == 0 and rows >= 2 * cfg.n_expert and rows <= 4096))
+    gu_tensor = can_tc and (args.expert_path in (2, 4) or (args.expert_path == 0 and rows >= 2 * cfg.n_expert))
     gu_kernel = ("expert_gemm_nvfp4_kernel<DUAL> (tcgen05 grouped GEMM: gate+up+SwiGLU)" if gu_tensor
                  else "expert_gemv_kernel<DUAL> (integer GEMV: gate+up+SwiGLU)")
     roofline = {"bound": "hbm", "kernel": gu_kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",

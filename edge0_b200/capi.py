@@ -43,6 +43,7 @@ SIGNATURES = {
     "b200moe_get_counters": (C.c_int, [C.c_void_p, C.POINTER(Counters)]),
     "b200moe_synchronize": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200moe_set_expert_path": (C.c_int, [C.c_void_p, C.c_int]),
+    "b200moe_set_launch_overlap": (C.c_int, [C.c_void_p, C.c_int]),
     "b200moe_enable_kernel_timing": (C.c_int, [C.c_void_p, C.c_int]),
     "b200moe_kernel_times": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_double)]),
     "b200moe_row_size": (C.c_int64, [C.c_int, C.c_int64]),

@@ -20,6 +20,7 @@
 #include "expert_gemm_tm.cuh"
 #include "expert_gemv.cuh"
 #include "expert_mma.cuh"
+#include "requant_fixup.cuh"
 #include "router.cuh"
 
 using namespace b200moe;
@@ -68,6 +69,8 @@ struct b200moe_ctx {
     int64_t launches = 0;
     bool timing = false;
     int expert_path = 0;  // 0 auto, 1 integer GEMV always, 2 tensor-core GEMM whenever the shape allows
+    bool overlap = false; // launch the layer's kernels as programmatic dependents of one another (opt-in)
+    bool overlap_now = false;  // set per call: only the small-batch regime uses it (see layer_overlap)
     struct Timed { cudaEvent_t beg, end; int kind; };
     std::vector<Timed> timed;
 };
@@ -150,6 +153,32 @@ bool gemv_supported(int wtype, int64_t k) {
     return false;
 }
 
+// Programmatic dependent launch (opt-in, b200moe_set_launch_overlap) is applied in the batched-decode regime only (few routed
+// rows per expert), where launch latency and kernel prologues are a visible share of an eagerly launched step.  Measured:
+// +7 % end to end through the host entry point, nothing under CUDA-graph replay (and slower at 8 tokens), which is why it is
+// off by default.  With prefill-sized grids it gains nothing, and the gate/up grouped GEMM with 128-token tiles was measured
+// to return wrong values when a large dependent grid was resident beside it (cause not found by reading; serial launches are
+// correct), so large calls always launch serially.
+void layer_overlap(b200moe_ctx * ctx, int64_t rows, int n_expert) { ctx->overlap_now = rows < (int64_t) 24 * n_expert; }
+
+// Launch with programmatic stream serialisation: the kernel may start while its predecessor in the stream is still running;
+// every kernel of this library calls griddepcontrol.wait before it touches global memory, so only prologues (barrier and
+// table set-up, tensor-memory allocation) and launch latency overlap.  Falls back to an ordinary launch when switched off.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_k(const b200moe_ctx * ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (ctx->overlap && ctx->overlap_now) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // need_router / need_experts: which weight pointers the entry point is going to read
 int validate_layer(b200moe_ctx * ctx, const b200moe_layer * l, bool need_router = true, bool need_experts = true) {
     if (!ctx) return B200MOE_ERR_INVALID_ARG;
@@ -230,7 +259,7 @@ int launch_gemv_t(b200moe_ctx * ctx, const GemvParams & p, cudaStream_t st) {
         tm.kind = DUAL ? 0 : 1;
         CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
     }
-    kern<<<ctx->sm_count, GemvCfg<WT, K>::NWARPS * 32, smem, st>>>(p);
+    launch_k(ctx, kern, dim3(ctx->sm_count), dim3(GemvCfg<WT, K>::NWARPS * 32), smem, st, p);
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventRecord(tm.end, st));
         ctx->timed.push_back(tm);
@@ -322,7 +351,7 @@ int launch_gemm_t(b200moe_ctx * ctx, const MmaParams & p, int rows, cudaStream_t
         tm.kind = DUAL ? 0 : 1;
         CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
     }
-    kern<<<ctx->sm_count, GEMM_THREADS, C::SMEM, st>>>(p, mw0, mw1, mhi, mlo);
+    launch_k(ctx, kern, dim3(ctx->sm_count), dim3(GEMM_THREADS), C::SMEM, st, p, mw0, mw1, mhi, mlo);
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventRecord(tm.end, st));
         ctx->timed.push_back(tm);
@@ -358,7 +387,7 @@ int launch_gemm_tm_t(b200moe_ctx * ctx, const MmaParams & p, int rows, cudaStrea
         tm.kind = DUAL ? 0 : 1;
         CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
     }
-    kern<<<ctx->sm_count, GEMM_TM_THREADS, C::SMEM, st>>>(p, mw0, mw1, mact);
+    launch_k(ctx, kern, dim3(ctx->sm_count), dim3(GEMM_TM_THREADS), C::SMEM, st, p, mw0, mw1, mact);
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventRecord(tm.end, st));
         ctx->timed.push_back(tm);
@@ -392,8 +421,8 @@ int launch_sorted_act(b200moe_ctx * ctx, ActQuant act, int rows, int k, int n_id
     Plan & p = ctx->plan;
     const int64_t warps = (int64_t) rows * (k / 32);
     __half * lo = interleaved ? p.afp16 + k : p.afp16 + (size_t) rows * k;
-    sorted_act_fp16_kernel<<<(unsigned) ((warps * 32 + 255) / 256), 256, 0, st>>>(act, p.groups.perm, rows, k, n_ids, ne11, p.afp16, lo,
-                                                                                    interleaved ? 2 * k : k);
+    launch_k(ctx, sorted_act_fp16_kernel, dim3((unsigned) ((warps * 32 + 255) / 256)), dim3(256), 0, st, act, p.groups.perm, rows, k, n_ids, ne11,
+             p.afp16, lo, interleaved ? 2 * k : k);
     return check_launch(ctx, "sorted_act_fp16");
 }
 
@@ -403,7 +432,7 @@ int launch_quantize(b200moe_ctx * ctx, const XT * src, int64_t stride, ActQuant 
     const int64_t warps = (int64_t) rows * (kind ? k / 256 : k / 32);
     if (warps == 0) return B200MOE_OK;
     const int blocks = (int) ((warps * 32 + 255) / 256);
-    quantize_act_kernel<XT><<<blocks, 256, 0, st>>>(src, stride, dst, rows, k, kind);
+    launch_k(ctx, quantize_act_kernel<XT>, dim3(blocks), dim3(256), 0, st, src, stride, dst, rows, k, kind);
     return check_launch(ctx, "quantize_act");
 }
 
@@ -426,8 +455,8 @@ int launch_front_t(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int
     const int kind = l->wtype == TYPE_Q3_K ? 1 : 0;
     const int64_t qwarps = (int64_t) T * (kind ? l->n_embd / 256 : l->n_embd / 32);
     const int qblocks = (int) ((qwarps * 32 + 255) / 256);
-    route_front_kernel<TT, XT><<<lblocks + qblocks, 256, 0, st>>>(l->router_w, l->router_bias, x, p.logits, l->n_embd, l->n_expert, T,
-                                                                  p.groups.counts, l->n_expert, lblocks, p.xq, kind);
+    launch_k(ctx, route_front_kernel<TT, XT>, dim3(lblocks + qblocks), dim3(256), 0, st, l->router_w, l->router_bias, x, p.logits, l->n_embd,
+             l->n_expert, T, p.groups.counts, l->n_expert, lblocks, p.xq, kind);
     return check_launch(ctx, "route_front");
 }
 
@@ -441,7 +470,7 @@ int launch_select_group(b200moe_ctx * ctx, const b200moe_layer * l, int T, float
     Plan & p = ctx->plan;
     const int E = l->n_expert, K = l->n_expert_used;
     const size_t sh = (size_t) (2 * E + 1) * sizeof(int);
-#define SELG(EPL) route_select_group_kernel<EPL><<<1, 1024, sh, st>>>(p.logits, E, K, T, p.ids, p.wts, probs, p.groups, ctx->d_err)
+#define SELG(EPL) launch_k(ctx, route_select_group_kernel<EPL>, dim3(1), dim3(1024), sh, st, p.logits, E, K, T, p.ids, p.wts, probs, p.groups, ctx->d_err)
     if (E <= 32) SELG(1);
     else if (E <= 64) SELG(2);
     else if (E <= 128) SELG(4);
@@ -457,7 +486,7 @@ int launch_select(b200moe_ctx * ctx, const b200moe_layer * l, int T, int32_t * i
     const int blocks = (T * 32 + 255) / 256;
     const int E = l->n_expert, K = l->n_expert_used;
     int * counts = count ? p.groups.counts : nullptr;
-#define SEL(EPL) route_select_kernel<EPL><<<blocks, 256, 0, st>>>(p.logits, E, K, T, ids, wts, probs, counts, p.groups.pos)
+#define SEL(EPL) launch_k(ctx, route_select_kernel<EPL>, dim3(blocks), dim3(256), 0, st, p.logits, E, K, T, ids, wts, probs, counts, p.groups.pos)
     if (E <= 32) SEL(1);
     else if (E <= 64) SEL(2);
     else if (E <= 128) SEL(4);
@@ -471,7 +500,7 @@ int launch_select(b200moe_ctx * ctx, const b200moe_layer * l, int T, int32_t * i
 int launch_group(b200moe_ctx * ctx, const int32_t * ids, int E, int rows, cudaStream_t st) {
     Plan & p = ctx->plan;
     const size_t sh = (size_t) (2 * E + 1) * sizeof(int);
-    group_scan_kernel<<<1, 1024, sh, st>>>(p.groups, ids, E, rows, ctx->d_err);
+    launch_k(ctx, group_scan_kernel, dim3(1), dim3(1024), sh, st, p.groups, ids, E, rows, ctx->d_err);
     return check_launch(ctx, "group_scan");
 }
 
@@ -501,11 +530,17 @@ GemvParams gemv_params(b200moe_ctx * ctx, const void * w0, const void * w1, cons
 int tokens_per_pass(int rows, int n_as) { return rows <= n_as ? (rows <= 32 ? 1 : 4) : 4; }
 
 __global__ void scale_rows_kernel(float * v, const float * s, size_t n) {
+    pdl_wait();
+    pdl_launch_dependents();
+
     const size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) v[i] = __fmul_rn(v[i], s[0]);
 }
 
 __global__ void bf16_to_f32_kernel(const __nv_bfloat16 * src, float * dst, size_t n) {
+    pdl_wait();
+    pdl_launch_dependents();
+
     const size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) dst[i] = __bfloat162float(src[i]);
 }
@@ -534,6 +569,9 @@ int dense_matvec(b200moe_ctx * ctx, int wtype, const void * w, const float * sca
 
 __global__ void gather_rows_kernel(const float4 * __restrict__ src, const int * __restrict__ idx, float4 * __restrict__ dst, int n_rows,
                                    int w4, int src_rows) {
+    pdl_wait();
+    pdl_launch_dependents();
+
     const int r = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= n_rows || c >= w4) return;
@@ -566,6 +604,45 @@ int route_impl(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, 
     return B200MOE_OK;
 }
 
+// Exact re-quantisation behind the tensor-core gate/up GEMM (requant_fixup.cuh): list the values of `hidden` whose int8
+// rounding the GEMM's error could change, recompute them with the integer lane chains, patch `hidden`.
+// The list lives in the `down` output buffer, which is not in use yet.
+constexpr float FIX_STEP_MARGIN = 0.015f;  // quantisation steps; largest GEMM error measured: 3.7e-3 steps (p99.99: 1.8e-3)
+constexpr float FIX_REL_MARGIN = 1.2e-4f;  // of the block maximum; largest error measured: 2.9e-5 of it
+
+template <int K>
+int launch_fix_t(b200moe_ctx * ctx, const FixParams & fp, cudaStream_t st) {
+    launch_k(ctx, requant_fix_kernel<K>, dim3(ctx->sm_count * 8), dim3(256), 0, st, fp);
+    return check_launch(ctx, "requant_fix");
+}
+
+int launch_requant_fixup(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, int rows, int n_in, int n_ids, cudaStream_t st) {
+    Plan & p = ctx->plan;
+    FixList list;
+    list.items = reinterpret_cast<int2 *>(p.y);
+    list.count = p.groups.meta + 2;
+    const size_t room = (size_t) rows * n_in * sizeof(float) / sizeof(int2);
+    list.capacity = (int) std::min<size_t>(room, (size_t) rows * l->n_ff / 4);
+    CUDA_TRY(ctx, cudaMemsetAsync(list.count, 0, sizeof(int), st));
+    const int64_t warps = (int64_t) rows * (l->n_ff / 32);
+    launch_k(ctx, requant_mark_kernel, dim3((unsigned) ((warps * 32 + 255) / 256)), dim3(256), 0, st, (const float *) p.hid, rows, l->n_ff,
+             FIX_STEP_MARGIN, FIX_REL_MARGIN, list);
+    int rc = check_launch(ctx, "requant_mark");
+    if (rc) return rc;
+    FixParams fp{};
+    fp.w0 = static_cast<const uint8_t *>(l->gate); fp.w1 = static_cast<const uint8_t *>(l->up);
+    fp.scale0 = l->gate_scale; fp.scale1 = l->up_scale; fp.act = xq; fp.ids = p.ids; fp.n_ids = n_ids; fp.n_ff = l->n_ff;
+    fp.n_as = l->n_expert; fp.hid = p.hid; fp.list = list; fp.err = ctx->d_err;
+    switch (n_in) {
+        case 256: return launch_fix_t<256>(ctx, fp, st);
+        case 512: return launch_fix_t<512>(ctx, fp, st);
+        case 768: return launch_fix_t<768>(ctx, fp, st);
+        case 1024: return launch_fix_t<1024>(ctx, fp, st);
+        case 2048: return launch_fix_t<2048>(ctx, fp, st);
+    }
+    return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no re-quantisation fix-up for width %d", n_in);
+}
+
 // experts on activations xe [T][n_in] (fp32), routing already grouped in the plan
 int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const int32_t * ids, const float * wts, int T, float * out,
                  const b200moe_observe * ob, cudaStream_t st) {
@@ -590,9 +667,13 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
     // A latent layer re-quantises once more after `down` (the up-projection), which amplifies the GEMM's error a second time
     // (measured 1.7e-2 of RMS on the 512-expert latent configuration, 2.2e-3 with only `down` on tensor cores): by default
     // latent layers stay on the integer kernels.
-    const bool dflt = path == 0 && many_rows && l->n_latent == 0;
-    const bool mma_down = can_mma && (path == 2 || path == 3 || dflt);
-    const bool mma_gu = can_mma && (path == 2 || (dflt && rows <= 4096));
+    // Path 4 / large or latent default: tensor-core gate/up followed by the exact re-quantisation fix-up, which makes the
+    // int8 `hidden` the reference's own again.
+    const bool latent = l->n_latent > 0;
+    const bool dflt = path == 0 && many_rows;
+    const bool mma_down = can_mma && (path == 2 || path == 3 || path == 4 || (dflt && !latent));
+    const bool mma_gu = can_mma && (path == 2 || path == 4 || dflt);
+    const bool fixup = mma_gu && (path == 4 || (dflt && (rows > 4096 || latent)));
     const bool small_tiles = rows < 24 * l->n_expert;   // on average fewer than 24 rows per expert
     auto mp = [&](const void * w0, const void * w1, const float * s0, const float * s1, float * out, int n_out, int m_k) {
         MmaParams m{};
@@ -613,6 +694,7 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
         GemvParams gu = gemv_params(ctx, l->gate, l->up, l->gate_scale, l->up_scale, xq, p.hid, l->n_ff, k, 1, l->n_expert);
         if ((rc = launch_gemv<true>(ctx, l->wtype, n_in, gu, nt, st))) return rc;
     }
+    if (fixup && (rc = launch_requant_fixup(ctx, l, xq, rows, n_in, k, st))) return rc;
     if ((rc = launch_quantize<float>(ctx, p.hid, l->n_ff, p.hq, rows, l->n_ff, l->wtype, st))) return rc;
     if (mma_down) {
         if ((rc = launch_sorted_act(ctx, p.hq, rows, l->n_ff, k, k, tm_down, st))) return rc;
@@ -623,7 +705,7 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
         if ((rc = launch_gemv<false>(ctx, l->wtype, l->n_ff, dn, nt, st))) return rc;
     }
     dim3 grid((n_in / 4 + 255) / 256, T);
-    combine_kernel<<<grid, 256, 0, st>>>(p.y, wts, out, n_in, k, T);
+    launch_k(ctx, combine_kernel, grid, dim3(256), 0, st, p.y, wts, out, n_in, k, T);
     if ((rc = check_launch(ctx, "combine"))) return rc;
     if (ob && ob->ffn_moe_hidden)
         CUDA_TRY(ctx, cudaMemcpyAsync(ob->ffn_moe_hidden, p.hid, sizeof(float) * (size_t) rows * l->n_ff, cudaMemcpyDeviceToDevice, st));
@@ -768,8 +850,14 @@ int b200moe_get_counters(const b200moe_ctx * ctx, b200moe_counters * out) {
 }
 
 int b200moe_set_expert_path(b200moe_ctx * ctx, int path) {
-    if (!ctx || path < 0 || path > 3) return B200MOE_ERR_INVALID_ARG;
+    if (!ctx || path < 0 || path > 4) return B200MOE_ERR_INVALID_ARG;
     ctx->expert_path = path;
+    return B200MOE_OK;
+}
+
+int b200moe_set_launch_overlap(b200moe_ctx * ctx, int enable) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    ctx->overlap = enable != 0;
     return B200MOE_OK;
 }
 
@@ -1072,6 +1160,7 @@ int b200moe_route(b200moe_ctx * ctx, const b200moe_layer * l, const void * x, in
     if (x_type != TYPE_F32 && x_type != TYPE_BF16) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "activations must be F32 or BF16");
     if (T == 0) return B200MOE_OK;
     CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    layer_overlap(ctx, (int64_t) T * l->n_expert_used, l->n_expert);
     if ((rc = ensure_plan(ctx, l->n_embd, l->n_latent ? l->n_latent : l->n_embd, l->n_expert, l->n_expert_used, l->n_ff, l->wtype, T))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (x_type == TYPE_F32) return route_impl<float>(ctx, l, static_cast<const float *>(x), T, ids, weights, ob, false, st);
@@ -1080,6 +1169,7 @@ int b200moe_route(b200moe_ctx * ctx, const b200moe_layer * l, const void * x, in
 
 int b200moe_mul_mat_id(b200moe_ctx * ctx, int wtype, const void * as, int64_t ne00, int64_t ne01, int64_t n_as, const float * b, int64_t ne11,
                        const int32_t * ids, int64_t n_ids, int64_t ids_nb1, int64_t T, float * dst, void * stream) {
+    if (ctx) ctx->overlap_now = false;
     if (!ctx) return B200MOE_ERR_INVALID_ARG;
     if (T == 0) return B200MOE_OK;
     if (!as || !b || !ids || !dst) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer");
@@ -1111,6 +1201,7 @@ int b200moe_mul_mat_id(b200moe_ctx * ctx, int wtype, const void * as, int64_t ne
 
 int b200moe_mul_mat(b200moe_ctx * ctx, int wtype, const void * w, int64_t ne00, int64_t ne01, const float * x, int64_t T, const float * scale,
                     float * dst, void * stream) {
+    if (ctx) ctx->overlap_now = false;
     if (!ctx) return B200MOE_ERR_INVALID_ARG;
     if (T == 0) return B200MOE_OK;
     if (!w || !x || !dst || ne00 <= 0 || ne01 <= 0 || T < 0) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer or non-positive size");
@@ -1124,6 +1215,7 @@ int b200moe_mul_mat(b200moe_ctx * ctx, int wtype, const void * w, int64_t ne00, 
 }
 
 int b200moe_combine(b200moe_ctx * ctx, const float * y, const float * weights, float * out, int64_t n, int64_t k, int64_t T, void * stream) {
+    if (ctx) ctx->overlap_now = false;
     if (!ctx) return B200MOE_ERR_INVALID_ARG;
     if (T == 0) return B200MOE_OK;
     if (!y || !weights || !out || n <= 0 || k <= 0 || T < 0 || n % 4) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer, non-positive size or width not a multiple of 4");
@@ -1135,6 +1227,7 @@ int b200moe_combine(b200moe_ctx * ctx, const float * y, const float * weights, f
 
 int b200moe_gather_rows(b200moe_ctx * ctx, const float * src, int64_t src_rows, const int32_t * idx, float * dst, int64_t n_rows, int64_t width,
                         void * stream) {
+    if (ctx) ctx->overlap_now = false;
     if (!ctx) return B200MOE_ERR_INVALID_ARG;
     if (n_rows == 0) return B200MOE_OK;
     if (!src || !idx || !dst || n_rows < 0 || src_rows <= 0 || width <= 0 || width % 4) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer, bad size or width not a multiple of 4");
@@ -1154,6 +1247,7 @@ int b200moe_ffn(b200moe_ctx * ctx, const b200moe_layer * l, const void * x, int 
     if (x_type != TYPE_F32 && x_type != TYPE_BF16) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "activations must be F32 or BF16");
     if (T == 0) return B200MOE_OK;
     CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    layer_overlap(ctx, (int64_t) T * l->n_expert_used, l->n_expert);
     if ((rc = ensure_plan(ctx, l->n_embd, l->n_latent ? l->n_latent : l->n_embd, l->n_expert, l->n_expert_used, l->n_ff, l->wtype, T))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     Plan & p = ctx->plan;
@@ -1179,6 +1273,7 @@ int b200moe_layer_forward(b200moe_ctx * ctx, const b200moe_layer * l, const void
     if (x_type != TYPE_F32 && x_type != TYPE_BF16) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "activations must be F32 or BF16");
     if (T == 0) return B200MOE_OK;
     CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    layer_overlap(ctx, (int64_t) T * l->n_expert_used, l->n_expert);
     if ((rc = b200moe_reserve(ctx, l, T))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (x_type == TYPE_F32) return layer_impl<float>(ctx, l, static_cast<const float *>(x), T, out, ob, st);
@@ -1194,6 +1289,7 @@ int b200moe_layer_forward_host(b200moe_ctx * ctx, const b200moe_layer * l, const
     if (x_type != TYPE_F32 && x_type != TYPE_BF16) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "activations must be F32 or BF16");
     if (T == 0) return B200MOE_OK;
     CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    layer_overlap(ctx, (int64_t) T * l->n_expert_used, l->n_expert);
     if ((rc = b200moe_reserve(ctx, l, T))) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     Plan & p = ctx->plan;

@@ -160,6 +160,8 @@ expert_gemm_nvfp4_kernel(const MmaParams p, const __grid_constant__ CUtensorMap 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
+    pdl_wait();                 // programmatic dependent launch: everything before this ran alongside the previous kernel's tail
+    pdl_launch_dependents();
 
     const int n_active = p.meta[0];
     const int m_tiles = p.n_out / 128;

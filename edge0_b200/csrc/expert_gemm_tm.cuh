@@ -89,6 +89,8 @@ expert_gemm_tm_kernel(const MmaParams p, const __grid_constant__ CUtensorMap map
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
+    pdl_wait();                 // programmatic dependent launch: everything before this ran alongside the previous kernel's tail
+    pdl_launch_dependents();
 
     const int n_active = p.meta[0];
     const int f_tiles = p.n_out / FEAT;

@@ -177,6 +177,42 @@ __device__ __forceinline__ void lane_chain(const uint8_t * __restrict__ row, int
     }
 }
 
+// The NVFP4 chain of lane_chain for ONE activation row whose int8 values (q, K bytes) and block scales (d, K/32 floats)
+// lie in separate arrays, in any address space.  Same operations in the same order as lane_chain<TYPE_NVFP4, K, 1, 1>.
+template <int K>
+__device__ __forceinline__ void lane_chain_split(const uint8_t * __restrict__ row, int L, const uint8_t * __restrict__ q,
+                                                 const float * __restrict__ d, const float * __restrict__ ue_tab, float (&acc)[1]) {
+    const int sub_in_half = L >> 2, mp = L & 3;
+    const int word_off = 4 + 8 * sub_in_half + 4 * (mp & 1);
+    const int nib_shift = 4 * (mp >> 1);
+    float a = 0.0f;
+#pragma unroll 4
+    for (int b = 0; b < K / 64; ++b) {
+        const uint8_t * blk = row + b * NVFP4_BLOCK_BYTES;
+        const uint32_t dw = *reinterpret_cast<const uint32_t *>(blk);
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            const uint32_t w = *reinterpret_cast<const uint32_t *>(blk + 16 * hf + word_off);
+            const uint32_t t4 = (w >> nib_shift) & 0x0f0f0f0fu;
+            const uint32_t u = t4 | (t4 >> 4);
+            const uint32_t sel = (u & 0xffff00ffu) | ((u >> 8) & 0x0000ff00u);
+            const uint32_t pos = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel);
+            const uint32_t neg = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel ^ 0x8888u);
+            const uint32_t code = pos | ((0x80808080u - neg) ^ 0x80808080u);
+            const float sw = ue_tab[(dw >> (8 * (2 * hf + sub_in_half))) & 0xff];
+            const int unit = 2 * b + hf;
+            const uint32_t aw = reinterpret_cast<const uint32_t *>(q)[unit * 8 + L];
+            const float dy = d[unit];
+            const int p = dot4((int) code, (int) aw, 0);
+            a = __fmaf_rn(__fmul_rn(sw, dy), small_int_to_float(p), a);
+        }
+    }
+    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 4));
+    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 2));
+    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 1));
+    acc[0] = a;
+}
+
 // chunk walker shared by the producer thread and the consumers
 struct Chunk {
     int a;      // index into active[]
@@ -226,6 +262,8 @@ __global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_ke
     if (WT == TYPE_NVFP4)
         for (int i = tid; i < 256; i += NTHREADS) ue_tab[i] = ue4m3_half_to_f32(i);
     __syncthreads();
+    pdl_wait();                 // programmatic dependent launch: everything before this ran alongside the previous kernel's tail
+    pdl_launch_dependents();
 
     const int n_active = p.meta[0];
     const int upe = p.n_out / C::GRAN;                       // span units per expert
@@ -386,6 +424,9 @@ constexpr size_t gemv_smem_bytes() {
 // ---- weighted combine: out[t][i] = sum over slots in slot order of y[t*k+s][i] * w[t][s] (forward.cpp:308-310)
 __global__ void __launch_bounds__(256) combine_kernel(const float * __restrict__ y, const float * __restrict__ w, float * __restrict__ out,
                                                      int n, int k, int T) {
+    pdl_wait();
+    pdl_launch_dependents();
+
     const int i4 = blockIdx.x * blockDim.x + threadIdx.x;  // float4 index within a token row
     const int t = blockIdx.y;
     if (i4 * 4 >= n || t >= T) return;

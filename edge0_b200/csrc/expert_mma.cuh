@@ -85,6 +85,9 @@ __device__ __forceinline__ uint32_t sw128_offset(int r, int c) { return (uint32_
 __global__ void __launch_bounds__(256) sorted_act_fp16_kernel(ActQuant act, const int * __restrict__ perm, int rows, int K, int n_ids,
                                                              int ne11, __half * __restrict__ out_hi, __half * __restrict__ out_lo,
                                                              int row_stride) {
+    pdl_wait();
+    pdl_launch_dependents();
+
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     const int nb = K / 32;
     if (warp >= rows * nb) return;

@@ -28,6 +28,9 @@ template <int TT, typename XT>
 __global__ void __launch_bounds__(256) router_logits_kernel(const float * __restrict__ W, const float * __restrict__ bias,
                                                            const XT * __restrict__ x, float * __restrict__ logits, int H,
                                                            int E, int T, int * __restrict__ zero_buf, int zero_n) {
+    pdl_wait();
+    pdl_launch_dependents();
+
     // block 0 also clears the per-expert counters the selection kernel accumulates into
     if (blockIdx.x == 0)
         for (int i = threadIdx.x; i < zero_n; i += blockDim.x) zero_buf[i] = 0;
@@ -132,6 +135,9 @@ __device__ __forceinline__ void quantize_q8_K_block(const XT * __restrict__ src,
 template <typename XT>
 __global__ void __launch_bounds__(256) quantize_act_kernel(const XT * __restrict__ src, int64_t src_stride, ActQuant dst, int rows,
                                                           int K, int kind) {
+    pdl_wait();
+    pdl_launch_dependents();
+
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (kind == 0) {
@@ -155,6 +161,9 @@ __global__ void __launch_bounds__(256) route_front_kernel(const float * __restri
                                                          const XT * __restrict__ x, float * __restrict__ logits, int H, int E, int T,
                                                          int * __restrict__ zero_buf, int zero_n, int n_logit_blocks, ActQuant dst,
                                                          int kind) {
+    pdl_wait();
+    pdl_launch_dependents();
+
     if ((int) blockIdx.x < n_logit_blocks) {
         if (blockIdx.x == 0)
             for (int i = threadIdx.x; i < zero_n; i += blockDim.x) zero_buf[i] = 0;
@@ -314,6 +323,9 @@ __global__ void __launch_bounds__(256) route_select_kernel(const float * __restr
                                                           int32_t * __restrict__ ids, float * __restrict__ weights,
                                                           float * __restrict__ probs_out, int * __restrict__ counts,
                                                           int * __restrict__ pos) {
+    pdl_wait();
+    pdl_launch_dependents();
+
     const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (t >= T) return;
     route_select_token<EPL>(logits, E, K, t, threadIdx.x & 31, ids, weights, probs_out, counts, pos);
@@ -389,6 +401,9 @@ __device__ __forceinline__ void group_scan_body(Groups g, const int32_t * __rest
 
 // Single block.  counts must be final (selection kernel finished).
 __global__ void __launch_bounds__(1024) group_scan_kernel(Groups g, const int32_t * __restrict__ ids, int E, int rows, int * err) {
+    pdl_wait();
+    pdl_launch_dependents();
+
     extern __shared__ int sh[];  // [E+1] offsets, [E] active flags
     group_scan_body(g, ids, E, rows, err, sh);
 }
@@ -398,6 +413,9 @@ template <int EPL>
 __global__ void __launch_bounds__(1024) route_select_group_kernel(const float * __restrict__ logits, int E, int K, int T,
                                                                  int32_t * __restrict__ ids, float * __restrict__ weights,
                                                                  float * __restrict__ probs_out, Groups g, int * err) {
+    pdl_wait();
+    pdl_launch_dependents();
+
     extern __shared__ int sh[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     for (int t = warp; t < T; t += nw) route_select_token<EPL>(logits, E, K, t, lane, ids, weights, probs_out, g.counts, g.pos);
@@ -410,6 +428,9 @@ __global__ void __launch_bounds__(1024) route_select_group_kernel(const float * 
 __global__ void __launch_bounds__(256) count_ids_kernel(const int32_t * __restrict__ ids, int64_t ids_stride, int n_ids, int T, int E,
                                                        int32_t * __restrict__ ids_compact, int * __restrict__ counts,
                                                        int * __restrict__ pos, int * err) {
+    pdl_wait();
+    pdl_launch_dependents();
+
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= n_ids * T) return;
     const int t = r / n_ids, s = r % n_ids;

@@ -114,6 +114,10 @@ class Context:
         """0 automatic, 1 integer GEMV always, 2 tensor-core grouped GEMM whenever the shape allows."""
         self.check(self.lib.b200moe_set_expert_path(self.handle, path))
 
+    def set_launch_overlap(self, enable: bool) -> None:
+        """Programmatic dependent launches between the kernels of a layer (default off); see b200moe_set_launch_overlap."""
+        self.check(self.lib.b200moe_set_launch_overlap(self.handle, int(bool(enable))))
+
     def enable_kernel_timing(self, on: bool = True):
         self.check(self.lib.b200moe_enable_kernel_timing(self.handle, int(on)))
 

@@ -111,16 +111,26 @@ B200MOE_API int  b200moe_synchronize(b200moe_ctx * ctx, void * stream); /* ggml_
  * edge0-infer/docs/configuration.md:62-72; plain struct-style option, no environment variables):
  *   0  default: below two routed rows per expert everything runs on the integer kernels, which follow the reference's fp32
  *      summation order and are bit-identical to the CPU path.  Above that `down` runs on the tcgen05 grouped GEMM (its ~3e-5
- *      accumulation error is not re-quantised afterwards: ~1e-5 of RMS on the output) and, up to 4096 routed rows (512 tokens at
- *      top-8), so does gate/up
- *      (re-quantisation of `hidden` amplifies the GEMM's error: 2e-3 of RMS on the output at 64 tokens, 4e-3 at 256)
- *      Latent layers (n_latent > 0) re-quantise once more after `down` and stay on the integer kernels by default.
+ *      accumulation error is not re-quantised afterwards: ~1e-5 of RMS on the output) and so does gate/up.  The reference
+ *      re-quantises `hidden` to int8, which turns the GEMM's error into occasional flipped values (2e-3 of RMS on the output at
+ *      64 tokens, 4e-3 at 256, 1e-2 at 4096): up to 4096 routed rows (512 tokens at top-8) that is accepted; beyond, and for
+ *      latent layers (n_latent > 0, which re-quantise once more after `down` and keep `down` on the integer kernel), the values
+ *      of `hidden` whose rounding the error could change are recomputed exactly (see 4).
  *   1  integer kernels everywhere: the whole layer is bit-identical to the reference CPU path
- *   2  tcgen05 grouped GEMM wherever the type and widths allow (NVFP4, n_ff and n_in multiples of 128); fastest for prefill,
+ *   2  tcgen05 grouped GEMM wherever the type and widths allow (NVFP4, n_ff and n_in multiples of 128), no exact recomputation;
  *      output error growing to 1e-2 of RMS at 4096 tokens
+ *   4  as 2, plus the exact re-quantisation fix-up after gate/up: every value of `hidden` within a safe margin of an int8
+ *      rounding boundary or of its block's maximum (a few per cent) is recomputed with the integer kernels' arithmetic, so the
+ *      quantised `hidden` equals the reference's; what remains is the ~1e-5 of the `down` GEMM
  *   3  integer gate/up, tcgen05 down at any batch size */
 B200MOE_API int  b200moe_set_expert_path(b200moe_ctx * ctx, int path);
 
+/* Launch overlap (no counterpart in the reference; comparable to a backend's own stream options).  OFF by default.  When on, calls
+ * in the batched-decode regime (fewer than 24 routed rows per expert on average; larger calls always launch serially) launch the
+ * kernels of one layer as programmatic dependents of one another, so a kernel's launch and set-up (barriers, tables, tensor
+ * memory) run alongside the tail of its predecessor; every kernel waits for its predecessor to finish before it reads or writes
+ * global memory.  Helps eagerly launched steps (+7 % through b200moe_layer_forward_host), not CUDA-graph replay. */
+B200MOE_API int  b200moe_set_launch_overlap(b200moe_ctx * ctx, int enable);
 /* Per-kernel device timing (reference: DecodeTiming with an injectable clock, include/edge0/timing.h:4-9).
  * When enabled, every expert-matmul launch is bracketed by CUDA events on its stream; b200moe_kernel_times
  * waits for them and returns, for kind 0 (fused gate+up+SwiGLU) and kind 1 (single indexed matmul / down),
