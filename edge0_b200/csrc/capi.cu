@@ -672,8 +672,8 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
     const bool latent = l->n_latent > 0;
     const bool dflt = path == 0 && many_rows;
     const bool mma_down = can_mma && (path == 2 || path == 3 || path == 4 || (dflt && !latent));
-    const bool mma_gu = can_mma && (path == 2 || path == 4 || dflt);
-    const bool fixup = mma_gu && (path == 4 || (dflt && (rows > 4096 || latent)));
+    const bool mma_gu = can_mma && (path == 2 || path == 4 || path == 5 || dflt);
+    const bool fixup = mma_gu && (path == 4 || path == 5 || (dflt && (rows > 4096 || latent)));
     const bool small_tiles = rows < 24 * l->n_expert;   // on average fewer than 24 rows per expert
     auto mp = [&](const void * w0, const void * w1, const float * s0, const float * s1, float * out, int n_out, int m_k) {
         MmaParams m{};
@@ -850,7 +850,7 @@ int b200moe_get_counters(const b200moe_ctx * ctx, b200moe_counters * out) {
 }
 
 int b200moe_set_expert_path(b200moe_ctx * ctx, int path) {
-    if (!ctx || path < 0 || path > 4) return B200MOE_ERR_INVALID_ARG;
+    if (!ctx || path < 0 || path > 5) return B200MOE_ERR_INVALID_ARG;
     ctx->expert_path = path;
     return B200MOE_OK;
 }

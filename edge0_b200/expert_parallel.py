@@ -148,9 +148,9 @@ class CudaBackend:
         self.ctx, self.cfg = ctx, cfg
         if cfg.n_latent:
             # The owner of an expert sees a plain layer of the latent width and cannot know that its rows are re-quantised
-            # again by the up-projection on the token's rank: pin the bit-exact integer kernels, as the library does by
-            # default for a latent layer it sees whole.
-            ctx.set_expert_path(1)
+            # again by the up-projection on the token's rank: pin what the library does by default for a latent layer it sees
+            # whole (tensor-core gate/up with the exact re-quantisation fix-up, integer down: bit-identical results).
+            ctx.set_expert_path(5)
         E, per = cfg.n_expert, cfg.n_expert // world
         lo, hi = rank * per, (rank + 1) * per
         if host_layer.gate.shape[0] == per and world > 1:      # generated for this shard only (make_layer(expert_range=...))

@@ -122,6 +122,7 @@ B200MOE_API int  b200moe_synchronize(b200moe_ctx * ctx, void * stream); /* ggml_
  *   4  as 2, plus the exact re-quantisation fix-up after gate/up: every value of `hidden` within a safe margin of an int8
  *      rounding boundary or of its block's maximum (a few per cent) is recomputed with the integer kernels' arithmetic, so the
  *      quantised `hidden` equals the reference's; what remains is the ~1e-5 of the `down` GEMM
+ *   5  tcgen05 gate/up + exact fix-up, integer down: bit-identical whenever the fix-up's margin holds (what 0 does for latent layers)
  *   3  integer gate/up, tcgen05 down at any batch size */
 B200MOE_API int  b200moe_set_expert_path(b200moe_ctx * ctx, int path);
 

@@ -43,9 +43,9 @@ def expected_engines(cfg, T, path):
         all(k in (256, 512, 768, 1024, 2048) for k in (cfg.n_ff, cfg.n_in))
     many = rows >= 2 * cfg.n_expert
     latent = bool(cfg.n_latent)
-    gu = can and (path in (2, 4) or (path == 0 and many))
+    gu = can and (path in (2, 4, 5) or (path == 0 and many))
     down = can and (path in (2, 3, 4) or (path == 0 and many and not latent))
-    fix = gu and (path == 4 or (path == 0 and many and (rows > 4096 or latent)))
+    fix = gu and (path in (4, 5) or (path == 0 and many and (rows > 4096 or latent)))
     return gu, down, fix
 
 
