@@ -50,7 +50,7 @@ struct Plan {  // carved out of the scratch arena for one (layer shape, max_toke
     float * xf = nullptr;   // [T][n_embd] fp32 copy of bf16 input (only for host entry / conversions)
     void * xin = nullptr;   // [T][n_embd] staging for the host entry point (input dtype bytes, <= 4 B/elt)
     float * outb = nullptr; // [T][n_embd] staging for the host entry point
-    int * one_group_ids = nullptr;  // [T] zeros: dense matvec expressed as one expert
+    int * one_group_ids = nullptr;  // [T] group of every token when a dense matvec runs on the indexed-matmul kernel
     __half * afp16 = nullptr;       // [T*k][max(n_in, n_ff)] expert-sorted fp16 activations of the tensor-core path
     size_t total = 0;
 };
@@ -519,6 +519,7 @@ GemvParams gemv_params(b200moe_ctx * ctx, const void * w0, const void * w1, cons
     g.meta = p.groups.meta;
     g.cost = p.groups.cost;
     g.out = out;
+    g.w_stride = n_out;
     g.n_out = n_out;
     g.n_ids = n_ids;
     g.ne11 = ne11;
@@ -545,19 +546,35 @@ __global__ void bf16_to_f32_kernel(const __nv_bfloat16 * src, float * dst, size_
     if (i < n) dst[i] = __bfloat162float(src[i]);
 }
 
-// Dense quantised matvec y[T][n_out] = W[n_out][k] . x[T][k], as one "expert" that every row is routed to.
+// token t belongs to group t / group_size
+__global__ void fill_group_ids_kernel(int * ids, int T, int group_size) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < T) ids[t] = t / group_size;
+}
+
+// Dense quantised matvec y[T][n_out] = W[n_out][k] . x[T][k] on the indexed-matmul kernel: the tokens are cut into up to 32
+// groups that all point at the same matrix (expert stride 0), so a matrix with few rows and many tokens still fills the grid
+// (one group would leave a 1024-row matrix on a fifth of the SMs, walking all tokens in turn).  The matrix is re-read from L2.
 int dense_matvec(b200moe_ctx * ctx, int wtype, const void * w, const float * scale, const float * x, ActQuant xq, int k, int n_out, int T,
                  float * y, cudaStream_t st) {
     Plan & p = ctx->plan;
     int rc = launch_quantize<float>(ctx, x, k, xq, T, k, wtype, st);
     if (rc) return rc;
-    CUDA_TRY(ctx, cudaMemsetAsync(p.groups.counts, 0, sizeof(int) * 8, st));
-    count_ids_kernel<<<(T + 255) / 256, 256, 0, st>>>(p.one_group_ids, 1, 1, T, 1, p.groups.perm /*scratch: compact ids*/, p.groups.counts,
+    const int G = std::max(1, std::min({32, T / 8, p.n_expert}));
+    const int gsize = (T + G - 1) / G;
+    const int groups = (T + gsize - 1) / gsize;
+    fill_group_ids_kernel<<<(T + 255) / 256, 256, 0, st>>>(p.one_group_ids, T, gsize);
+    if ((rc = check_launch(ctx, "fill_group_ids"))) return rc;
+    CUDA_TRY(ctx, cudaMemsetAsync(p.groups.counts, 0, sizeof(int) * std::max(groups, 8), st));
+    count_ids_kernel<<<(T + 255) / 256, 256, 0, st>>>(p.one_group_ids, 1, 1, T, groups, p.groups.perm /*scratch: compact ids*/, p.groups.counts,
                                                       p.groups.pos, ctx->d_err);
     if ((rc = check_launch(ctx, "count_ids"))) return rc;
-    // perm is about to be overwritten by the scan; the compact ids are all zero, so read them from one_group_ids
-    if ((rc = launch_group(ctx, p.one_group_ids, 1, T, st))) return rc;
-    GemvParams g = gemv_params(ctx, w, nullptr, nullptr, nullptr, xq, y, n_out, 1, 1, 1);
+    // perm is about to be overwritten by the scan: read the ids from one_group_ids
+    if ((rc = launch_group(ctx, p.one_group_ids, groups, T, st))) return rc;
+    GemvParams g = gemv_params(ctx, w, nullptr, nullptr, nullptr, xq, y, n_out, 1, 1, groups);
+    g.w_stride = 0;
     if ((rc = launch_gemv<false>(ctx, wtype, k, g, 4, st))) return rc;
     if (scale) {
         const size_t n = (size_t) T * n_out;

@@ -43,6 +43,7 @@ struct GemvParams {
     int n_ids;
     int ne11;
     int n_as;
+    int w_stride;         // rows between consecutive experts' matrices: n_out, or 0 when every group uses the same matrix
     int * err;
 };
 
@@ -303,7 +304,7 @@ __global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_ke
         const uint32_t bytes = (uint32_t) c.n * C::ROW_BYTES;
         uint8_t * dst = ring + (size_t) stage * STAGE_BYTES;
         mbar_arrive_expect_tx(&full[stage], bytes * NTENS);
-        const size_t off = ((size_t) e * p.n_out + c.r0) * C::ROW_BYTES;
+        const size_t off = ((size_t) e * p.w_stride + c.r0) * C::ROW_BYTES;
         bulk_g2s(dst, p.w0 + off, bytes, &full[stage]);
         if (DUAL) bulk_g2s(dst + C::TENSOR_STAGE_BYTES, p.w1 + off, bytes, &full[stage]);
     };
