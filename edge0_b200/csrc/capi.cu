@@ -642,8 +642,8 @@ int launch_requant_fixup(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq
     list.capacity = (int) std::min<size_t>(room, (size_t) rows * l->n_ff / 4);
     CUDA_TRY(ctx, cudaMemsetAsync(list.count, 0, sizeof(int), st));
     const int64_t warps = (int64_t) rows * (l->n_ff / 32);
-    launch_k(ctx, requant_mark_kernel, dim3((unsigned) ((warps * 32 + 255) / 256)), dim3(256), 0, st, (const float *) p.hid, rows, l->n_ff,
-             FIX_STEP_MARGIN, FIX_REL_MARGIN, list);
+    launch_k(ctx, requant_mark_kernel, dim3((unsigned) ((warps * 32 + 255) / 256)), dim3(256), 0, st, (const float *) p.hid,
+             (const int *) p.groups.perm, rows, l->n_ff, FIX_STEP_MARGIN, FIX_REL_MARGIN, list);
     int rc = check_launch(ctx, "requant_mark");
     if (rc) return rc;
     FixParams fp{};

@@ -28,14 +28,17 @@ struct FixList {
 //   step_margin : distance from a rounding boundary, in quantisation steps, below which a value is recomputed
 //   rel_margin  : relative distance from the block maximum below which a value counts as a candidate for it; the same
 //                 relative uncertainty of the scale widens the step margin of large values
-__global__ void __launch_bounds__(256) requant_mark_kernel(const float * __restrict__ hid, int rows, int n_ff, float step_margin,
-                                                          float rel_margin, FixList list) {
+//   perm        : routed rows sorted by expert.  Warps walk (feature block, sorted row) with the row fastest, so values that need
+//                 the same weight rows (same expert, same 32 features) are listed next to each other and the recomputation
+//                 finds those rows in cache instead of fetching 2 x row_bytes from HBM per value.
+__global__ void __launch_bounds__(256) requant_mark_kernel(const float * __restrict__ hid, const int * __restrict__ perm, int rows, int n_ff,
+                                                          float step_margin, float rel_margin, FixList list) {
     pdl_wait();
     pdl_launch_dependents();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     const int nb = n_ff / 32;
     if (warp >= rows * nb) return;
-    const int r = warp / nb, b = warp % nb;
+    const int b = warp / rows, r = perm[warp % rows];
     const float v = hid[(size_t) r * n_ff + b * 32 + lane];
     const float a = fabsf(v);
     float amax = a;
