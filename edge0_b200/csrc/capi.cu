@@ -267,11 +267,41 @@ int launch_gemv_t(b200moe_ctx * ctx, const GemvParams & p, cudaStream_t st) {
     return check_launch(ctx, "expert_gemv");
 }
 
+// One or two tokens: the whole call is a few thousand weight rows.  Four-warp CTAs with a single 16-row stage, several per SM,
+// give every CTA one pass over one chunk instead of two or three passes of a half-empty eight-warp CTA.
+template <int WT, int K, bool DUAL>
+int launch_gemv_tiny(b200moe_ctx * ctx, const GemvParams & p, int rows, cudaStream_t st) {
+    constexpr int NW = 4;
+    constexpr size_t smem = gemv_smem_bytes<WT, K, DUAL, 1, 1, NW>();
+    auto kern = expert_gemv_kernel<WT, K, DUAL, 1, 1, NW>;
+    static bool configured = false;  // per instantiation
+    if (!configured) {
+        CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+        configured = true;
+    }
+    b200moe_ctx::Timed tm{};
+    if (ctx->timing) {
+        CUDA_TRY(ctx, cudaEventCreate(&tm.beg));
+        CUDA_TRY(ctx, cudaEventCreate(&tm.end));
+        tm.kind = DUAL ? 0 : 1;
+        CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
+    }
+    const int64_t chunks = ((int64_t) rows * p.n_out + GemvCfg<WT, K, NW>::ROWS_PER_STAGE - 1) / GemvCfg<WT, K, NW>::ROWS_PER_STAGE;
+    const int grid = (int) std::max<int64_t>(1, std::min<int64_t>(chunks, (int64_t) ctx->sm_count * 4));
+    launch_k(ctx, kern, dim3(grid), dim3(NW * 32), smem, st, p);
+    if (ctx->timing) {
+        CUDA_TRY(ctx, cudaEventRecord(tm.end, st));
+        ctx->timed.push_back(tm);
+    }
+    return check_launch(ctx, "expert_gemv");
+}
+
 template <int WT, int K, bool DUAL>
 int launch_gemv_k(b200moe_ctx * ctx, const GemvParams & p, int nt, cudaStream_t st) {
     if constexpr (DUAL && K > 2048) {
         return fail(ctx, B200MOE_ERR_UNSUPPORTED, "fused gate/up kernel is not built for K=%d", K);
     } else {
+        if (nt <= 0) return launch_gemv_tiny<WT, K, DUAL>(ctx, p, -nt, st);   // nt = -(routed rows): the one-or-two-token kernel
         if (nt <= 1) return launch_gemv_t<WT, K, DUAL, 1>(ctx, p, st);
         return launch_gemv_t<WT, K, DUAL, 4>(ctx, p, st);
     }
@@ -528,7 +558,9 @@ GemvParams gemv_params(b200moe_ctx * ctx, const void * w0, const void * w1, cons
     return g;
 }
 
-int tokens_per_pass(int rows, int n_as) { return rows <= n_as ? (rows <= 32 ? 1 : 4) : 4; }
+// activation rows per pass of the integer kernel: 4, 1 when experts see about one row each, -(rows) selects the
+// one-or-two-token kernel
+int tokens_per_pass(int rows, int n_as) { return rows <= 16 ? -rows : rows <= n_as ? (rows <= 32 ? 1 : 4) : 4; }
 
 __global__ void scale_rows_kernel(float * v, const float * s, size_t n) {
     pdl_wait();

@@ -47,13 +47,13 @@ struct GemvParams {
     int * err;
 };
 
-template <int WT, int K>
+template <int WT, int K, int NW = 8>
 struct GemvCfg {
     static constexpr int LPR = 8;            // lanes per row = the reference's 8 SIMD lanes
     static constexpr int RPP = 4;            // rows per warp pass
     static constexpr int ROW_BYTES = WT == TYPE_NVFP4 ? K / 64 * 36 : K / 256 * 110;
     static constexpr int GRAN = (ROW_BYTES % 16 == 0) ? 1 : 8;  // span granularity in rows (16-byte rule of bulk copies)
-    static constexpr int NWARPS = 8;
+    static constexpr int NWARPS = NW;        // 8; 4 for the one-or-two-token kernel (several small CTAs per SM)
     // passes per warp per stage chosen so a (single-tensor) stage is roughly 12-40 KB
     static constexpr int PASSES = (ROW_BYTES * RPP * NWARPS >= 12288) ? 1 : (ROW_BYTES * RPP * NWARPS >= 6144) ? 2 : 4;
     static constexpr int ROWS_PER_STAGE = NWARPS * RPP * PASSES;
@@ -236,9 +236,9 @@ struct ChunkWalker {
     }
 };
 
-template <int WT, int K, bool DUAL, int NT, int STAGES>
-__global__ void __launch_bounds__(GemvCfg<WT, K>::NWARPS * 32, 1) expert_gemv_kernel(const GemvParams p) {
-    using C = GemvCfg<WT, K>;
+template <int WT, int K, bool DUAL, int NT, int STAGES, int NW = 8>
+__global__ void __launch_bounds__(NW * 32, NW == 8 ? 1 : 4) expert_gemv_kernel(const GemvParams p) {
+    using C = GemvCfg<WT, K, NW>;
     constexpr int NTENS = DUAL ? 2 : 1;
     constexpr int STAGE_BYTES = C::TENSOR_STAGE_BYTES * NTENS;
     constexpr int NTHREADS = C::NWARPS * 32;
@@ -416,9 +416,9 @@ constexpr int gemv_stages() {
     return (4 * stage <= 190 * 1024) ? 4 : (3 * stage <= 190 * 1024) ? 3 : 2;
 }
 
-template <int WT, int K, bool DUAL, int NT, int STAGES>
+template <int WT, int K, bool DUAL, int NT, int STAGES, int NW = 8>
 constexpr size_t gemv_smem_bytes() {
-    return (size_t) STAGES * GemvCfg<WT, K>::TENSOR_STAGE_BYTES * (DUAL ? 2 : 1) + NT * GemvCfg<WT, K>::ACT_TOKEN_BYTES + STAGES * 8 +
+    return (size_t) STAGES * GemvCfg<WT, K, NW>::TENSOR_STAGE_BYTES * (DUAL ? 2 : 1) + NT * GemvCfg<WT, K, NW>::ACT_TOKEN_BYTES + STAGES * 8 +
            256 * 4 + 64;
 }
 
