@@ -744,13 +744,16 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
         if ((rc = launch_gemv<true>(ctx, l->wtype, n_in, gu, nt, st))) return rc;
     }
     if (fixup && (rc = launch_requant_fixup(ctx, l, xq, rows, n_in, k, st))) return rc;
-    if ((rc = launch_quantize<float>(ctx, p.hid, l->n_ff, p.hq, rows, l->n_ff, l->wtype, st))) return rc;
+    // the integer down kernel quantises `hidden` itself while staging it (NVFP4 / Q8_0); otherwise a separate pass
+    const bool fused_quant = !mma_down && l->wtype == TYPE_NVFP4;
+    if (!fused_quant && (rc = launch_quantize<float>(ctx, p.hid, l->n_ff, p.hq, rows, l->n_ff, l->wtype, st))) return rc;
     if (mma_down) {
         if ((rc = launch_sorted_act(ctx, p.hq, rows, l->n_ff, k, k, tm_down, st))) return rc;
         const MmaParams m = mp(l->down, nullptr, l->down_scale, nullptr, p.y, n_in, l->n_ff);
         if ((rc = tm_down ? launch_gemm_tm<false>(ctx, l->n_ff, m, rows, st) : launch_gemm<false>(ctx, l->n_ff, m, rows, small_tiles, st))) return rc;
     } else {
         GemvParams dn = gemv_params(ctx, l->down, nullptr, l->down_scale, nullptr, p.hq, p.y, n_in, k, k, l->n_expert);
+        if (fused_quant) dn.act_f32 = p.hid;
         if ((rc = launch_gemv<false>(ctx, l->wtype, l->n_ff, dn, nt, st))) return rc;
     }
     dim3 grid((n_in / 4 + 255) / 256, T);

@@ -33,6 +33,7 @@ struct GemvParams {
     const float * scale0; // per-expert fp32 scale applied to w0's result (or null)
     const float * scale1;
     ActQuant act;         // quantised activation planes, row index = (row / n_ids) * ne11 + (row % n_ids) % ne11
+    const float * act_f32; // or (NVFP4 only): the fp32 activations [rows][K], quantised to Q8_0 while they are staged (act unused)
     const int * offsets;  // [n_as + 1]
     const int * perm;     // [rows]
     const int * active;   // [n_as]
@@ -354,11 +355,34 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 1 : 4) expert_gemv_kernel(c
                     if (t >= ntc) break;
                     const int r = rows[t];
                     const int arow = r >= 0 ? (r / p.n_ids) * p.ne11 + (r % p.n_ids) % p.ne11 : 0;
-                    const uint32_t * srcq = reinterpret_cast<const uint32_t *>(p.act.q + (size_t) arow * K);
                     uint32_t * dq = reinterpret_cast<uint32_t *>(acts);
-                    for (int i = tid; i < K / 4; i += NTHREADS) dq[(size_t) i * NT + t] = r >= 0 ? __ldg(srcq + i) : 0u;
                     float * dd = reinterpret_cast<float *>(acts + (size_t) K * NT);
-                    for (int i = tid; i < C::ACT_D; i += NTHREADS) dd[(size_t) i * NT + t] = r >= 0 ? __ldg(p.act.d + (size_t) arow * C::ACT_D + i) : 0.0f;
+                    if (WT == TYPE_NVFP4 && p.act_f32) {
+                        // Q8_0 on the fly, the arithmetic of quantize_q8_0_block: 8 lanes hold one block of 32 (4 values each)
+                        const float4 * src = reinterpret_cast<const float4 *>(p.act_f32 + (size_t) arow * K);
+                        for (int i0 = 0; i0 < K / 4; i0 += NTHREADS) {
+                            const int i = i0 + tid;
+                            const bool in = i < K / 4;
+                            const float4 v = (in && r >= 0) ? __ldg(src + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                            float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+                            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                            const float id = amax != 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+                            const uint32_t q = ((uint32_t) __float2int_rn(__fmul_rn(v.x, id)) & 0xffu) |
+                                               (((uint32_t) __float2int_rn(__fmul_rn(v.y, id)) & 0xffu) << 8) |
+                                               (((uint32_t) __float2int_rn(__fmul_rn(v.z, id)) & 0xffu) << 16) |
+                                               (((uint32_t) __float2int_rn(__fmul_rn(v.w, id)) & 0xffu) << 24);
+                            if (in) {
+                                dq[(size_t) i * NT + t] = q;
+                                if ((i & 7) == 0) dd[(size_t) (i >> 3) * NT + t] = __half2float(__float2half_rn(__fdiv_rn(amax, 127.0f)));
+                            }
+                        }
+                    } else {
+                        const uint32_t * srcq = reinterpret_cast<const uint32_t *>(p.act.q + (size_t) arow * K);
+                        for (int i = tid; i < K / 4; i += NTHREADS) dq[(size_t) i * NT + t] = r >= 0 ? __ldg(srcq + i) : 0u;
+                        for (int i = tid; i < C::ACT_D; i += NTHREADS) dd[(size_t) i * NT + t] = r >= 0 ? __ldg(p.act.d + (size_t) arow * C::ACT_D + i) : 0.0f;
+                    }
                 }
                 __syncthreads();
                 loaded_e = e;
