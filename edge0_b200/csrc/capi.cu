@@ -286,8 +286,9 @@ int launch_gemv_tiny(b200moe_ctx * ctx, const GemvParams & p, int rows, cudaStre
         tm.kind = DUAL ? 0 : 1;
         CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
     }
+    // one CTA per stage-sized chunk; at most `rows` experts are active, CTAs past the end of the row list leave at once
     const int64_t chunks = ((int64_t) rows * p.n_out + GemvCfg<WT, K, NW>::ROWS_PER_STAGE - 1) / GemvCfg<WT, K, NW>::ROWS_PER_STAGE;
-    const int grid = (int) std::max<int64_t>(1, std::min<int64_t>(chunks, (int64_t) ctx->sm_count * 4));
+    const int grid = (int) std::max<int64_t>(1, chunks);
     launch_k(ctx, kern, dim3(grid), dim3(NW * 32), smem, st, p);
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventRecord(tm.end, st));

@@ -272,7 +272,13 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 1 : 4) expert_gemv_kernel(c
     const long long total = (long long) n_active * upe;
     // Span boundaries balance WORK, not rows: a weight row of an expert with n routed rows costs 3 per pass (decode) + 2 per routed row.
     // Boundary i sits at work i/grid of the total; both neighbours compute it the same way, so spans tile exactly.
-    if (tid < 2) {
+    if (NW != 8) {
+        // one-or-two-token kernel: CTA b owns stage-sized chunk b of the flat row list - no search, no dependent loads
+        if (tid < 2) {
+            const long long u = (long long) (blockIdx.x + tid) * (C::ROWS_PER_STAGE / C::GRAN);
+            s_span[tid] = (int) (u < total ? u : total);
+        }
+    } else if (tid < 2) {
         const int * cw = p.cost + (NT == 1 ? 0 : NT == 2 ? 1 : 2) * (p.n_as + 1);
         const long long total_work = (long long) cw[n_active] * upe;
         const long long c = total_work * (blockIdx.x + tid) / gridDim.x;
