@@ -734,7 +734,8 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
     };
     // Few rows per expert: `down` runs with tokens on the M side (256 weight rows per instruction, a quarter of the MMAs);
     // gate+up stays with weights on the M side, where the per-stage dequantisation work is the same and the kernel was
-    // measured faster (167 us against 200 us at 64 tokens of configuration 2).
+    // measured faster (167 us against 182 us at 64 tokens of configuration 2: there the tokens-on-M form is bound by
+    // shared-memory traffic, twice the operand tile per stage).
     const bool tm_gu = false, tm_down = small_tiles && n_in % 256 == 0;
     if (mma_gu) {
         if ((rc = launch_sorted_act(ctx, xq, rows, n_in, k, 1, tm_gu, st))) return rc;

@@ -12,8 +12,9 @@
 // Per stage of K = 64 this is 4 instructions instead of 16.
 //
 // Roles and rings are those of expert_gemm.cuh (raw-weight TMA producer, activation TMA producer, MMA issuer, TMEM owner,
-// 4 epilogue warps, 16 dequant warps; every wait bounded).  E2M1 pairs are decoded through a 256-entry half2 table
-// replicated per bank (no conflicts, keeps the 16-lane integer pipe free).
+// 4 epilogue warps, 16 dequant warps; every wait bounded).  The kernel is bound by shared-memory traffic (operand tile written
+// once and read once by the tensor core, raw rows, activation tiles): E2M1 values are therefore decoded with byte permutes in
+// registers rather than through a table in shared memory (measured: the table's loads cost more than the permutes).
 #pragma once
 #include "expert_gemm.cuh"
 
@@ -32,12 +33,11 @@ struct GemmTmCfg {
     static constexpr int A_TILE = 128 * 128;                        // 64 rows x (hi, lo) x 64 halfs
     static constexpr int STAGE = B_TILE + A_TILE;
     static constexpr int RAW_STAGE = 256 * GEMM_RAW_ROW;
-    static constexpr int TS = 2;
+    static constexpr int TS = 3;
     static constexpr int RS = 2;
-    static constexpr int LUT_BYTES = 256 * 32 * 4;
     static constexpr uint32_t TMEM_COLS = 512;                      // two accumulators of 256 columns
     static_assert(K % GEMM_RAW_K == 0, "K must be a multiple of 256");
-    static constexpr size_t SMEM = (size_t) TS * STAGE + (size_t) RS * RAW_STAGE + LUT_BYTES + 1024;
+    static constexpr size_t SMEM = (size_t) TS * STAGE + (size_t) RS * RAW_STAGE + 1024;
 };
 
 // DUAL: B rows 0..127 = gate rows, 128..255 = up rows of the same 128 features; epilogue = SwiGLU.
@@ -54,7 +54,6 @@ expert_gemm_tm_kernel(const MmaParams p, const __grid_constant__ CUtensorMap map
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t * tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
     uint8_t * raws = tiles + (size_t) TS * C::STAGE;
-    uint32_t * lut = reinterpret_cast<uint32_t *>(raws + (size_t) RS * C::RAW_STAGE);   // [256 byte values][32 banks] half2
     __shared__ uint64_t raw_full[RS], raw_empty[RS], tile_full[TS], tile_empty[TS], acc_full[2], acc_empty[2];
     __shared__ uint32_t s_tmem;
     __shared__ volatile int s_abort;
@@ -71,15 +70,6 @@ expert_gemm_tm_kernel(const MmaParams p, const __grid_constant__ CUtensorMap map
     if (tid < 256) {
         const __half2 h = __float2half2_rn(2.0f * ue4m3_half_to_f32(tid));   // the helper returns the value halved
         s_scale_lut[tid] = *reinterpret_cast<const uint32_t *>(&h);
-    }
-    for (int i = tid; i < 256 * 32; i += GEMM_TM_THREADS) {
-        // byte b = nibble of element j (low) | nibble of element j + 8 (high)  ->  half2(value j, value j + 8)
-        const int b = i >> 5;
-        const int m0 = b & 7, m1 = (b >> 4) & 7;
-        const float v0 = m0 < 4 ? 0.5f * m0 : (m0 == 4 ? 2.0f : m0 == 5 ? 3.0f : m0 == 6 ? 4.0f : 6.0f);
-        const float v1 = m1 < 4 ? 0.5f * m1 : (m1 == 4 ? 2.0f : m1 == 5 ? 3.0f : m1 == 6 ? 4.0f : 6.0f);
-        const __half2 h = __floats2half2_rn((b & 0x08) ? -v0 : v0, (b & 0x80) ? -v1 : v1);
-        lut[i] = *reinterpret_cast<const uint32_t *>(&h);
     }
     if (warp == 3) {
         tmem_alloc(&s_tmem, C::TMEM_COLS);
@@ -223,7 +213,6 @@ expert_gemm_tm_kernel(const MmaParams p, const __grid_constant__ CUtensorMap map
 #pragma unroll
         for (int i = 0; i < 4; ++i) b_off[i] = sw128_offset(drow, 4 * dhalf + i);
         const uint32_t raw_off = (uint32_t) drow * GEMM_RAW_ROW;
-        const uint32_t * lut_lane = lut + lane;
         Ring raw, tile;
         for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
             const int e = p.active[item / f_tiles];
@@ -259,13 +248,13 @@ expert_gemm_tm_kernel(const MmaParams p, const __grid_constant__ CUtensorMap map
                             const uint32_t s2u = s_scale_lut[(S[kb] >> (8 * i)) & 0xff];
                             const __half2 s2 = *reinterpret_cast<const __half2 *>(&s2u);
                             const uint32_t q0 = Q[4 * kb + 2 * i], q1 = Q[4 * kb + 2 * i + 1];
-                            uint32_t h[8];
+                            uint32_t h[8], h0[4], h1[4];
+                            fp4_word_to_half2x4(q0, h0);
+                            fp4_word_to_half2x4(q1, h1);
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
-                                const uint32_t e0 = lut_lane[((q0 >> (8 * j)) & 0xff) * 32];
-                                const uint32_t e1 = lut_lane[((q1 >> (8 * j)) & 0xff) * 32];
-                                const __half2 v0 = __hmul2(*reinterpret_cast<const __half2 *>(&e0), s2);
-                                const __half2 v1 = __hmul2(*reinterpret_cast<const __half2 *>(&e1), s2);
+                                const __half2 v0 = __hmul2(*reinterpret_cast<const __half2 *>(&h0[j]), s2);
+                                const __half2 v1 = __hmul2(*reinterpret_cast<const __half2 *>(&h1[j]), s2);
                                 h[j] = *reinterpret_cast<const uint32_t *>(&v0);
                                 h[4 + j] = *reinterpret_cast<const uint32_t *>(&v1);
                             }
