@@ -166,6 +166,20 @@ def test_exact_requantisation_fixup(T, gpu_ctx, checker):
     print("c2 T=%d fix-up errors" % T, errs)
 
 
+def test_hot_expert_spans_several_token_tiles(gpu_ctx, checker):
+    """Batched-decode regime (fewer than 24 routed rows per expert on average) with one expert that every token selects: its 80
+    rows exceed the 64-row tile of the tokens-on-M kernel and the 32-row tile of the weights-on-M kernel, so both walk several
+    token tiles of one expert, with a ragged last tile."""
+    cfg = W.small_config(TYPE_NVFP4, n_embd=512, n_expert=16, top_k=4, n_ff=256, seed=77, router_bias=True)
+    layer = W.make_layer(cfg)
+    layer.router_bias = layer.router_bias.copy()
+    layer.router_bias[3] += 12.0
+    x_np = W.make_tokens(cfg, 80, bf16=True)
+    for path in (2, 4, 0):
+        errs = run_and_compare(gpu_ctx, checker, layer, x_np, bf16=True, path=path)
+        print("hot expert path %d" % path, errs)
+
+
 def test_c5_latent_layer_full_shape(gpu_ctx, checker):
     from oracle import oracle as O
     cfg = W.CONFIGS["c5_latent"]
