@@ -12,7 +12,8 @@
 //   3. the ordinary quantiser then sees exact values wherever the outcome depends on them, so the int8 `hidden` - and with
 //      the integer down kernel the whole layer - is the reference's, bit for bit, as long as the GEMM's error stays
 //      inside the margin (a few per cent of the values are recomputed; the margin is ~10x the largest error measured).
-// If the list overflows, the caller falls back to the integer kernel for the whole matmul.
+// The list holds a quarter of all values (5-6 % are listed in practice); values that do not fit stay as the GEMM produced them,
+// i.e. such a call degrades to the plain tensor-core path for those values instead of failing.
 #pragma once
 #include "expert_gemv.cuh"
 
