@@ -57,7 +57,8 @@ def plan_dispatch(ids: torch.Tensor, n_expert: int, world: int, group=None) -> D
         dist.all_to_all_single(recv, send, group=group)
     else:
         recv.copy_(send)
-    return DispatchPlan(order=order, send_counts=[int(v) for v in send.cpu()], recv_counts=[int(v) for v in recv.cpu()])
+    both = torch.stack([send, recv]).cpu()      # one device-to-host read for both count vectors
+    return DispatchPlan(order=order, send_counts=[int(v) for v in both[0]], recv_counts=[int(v) for v in both[1]])
 
 
 def exchange_rows(rows: torch.Tensor, send_counts, recv_counts, world: int, group=None) -> torch.Tensor:
