@@ -291,11 +291,11 @@ def run_b200_arm(args):
     gu_kernel = ("expert_gemm_nvfp4_kernel<DUAL> (tcgen05 grouped GEMM: gate+up+SwiGLU)" if gu_tensor
                  else "expert_gemv_kernel<DUAL> (integer GEMV: gate+up+SwiGLU)")
     # DRAM traffic of one gate/up launch: dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture of this workload
-    # (profiles/expert_kernels_c2_nvfp4_T64.md: 227.29 MB + 5.22 MB with 126 experts touched), scaled by the experts touched here
+    # (summary committed under profiles/: 227.29 MB + 5.22 MB with 126 experts touched), scaled by the experts touched here
     traffic, traffic_src = None, None
     if cfg.name == "c2_nvfp4" and T == 64 and gu_tensor:
         traffic = (227.294208e6 + 5.220608e6) * U / 126.0
-        traffic_src = "ncu capture of the same workload (profiles/expert_kernels_c2_nvfp4_T64.md), scaled by experts touched"
+        traffic_src = "ncu capture of the same workload (summary committed under profiles/), scaled by experts touched"
     roofline = {"bound": "hbm", "kernel": gu_kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_src, "peak_source": peak_kind,
                 "algorithmic_bytes_per_launch": gu_bytes,

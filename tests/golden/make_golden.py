@@ -1,5 +1,5 @@
 """Generates tests/golden/*.npz from the COMPILED REFERENCE (oracle/_ref/libedge0_ref.so, built by
-`make -C oracle ref` from the reference's own ggml CPU sources).  Run where /root/reference exists:
+`make -C oracle ref` from the reference's own ggml CPU sources).  Run where the reference tree is present:
 
     python tests/golden/make_golden.py
 
