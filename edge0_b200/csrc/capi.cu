@@ -17,6 +17,7 @@
 
 #include "../../include/edge0_b200_moe.h"
 #include "expert_gemm.cuh"
+#include "expert_gemm_fp4.cuh"
 #include "expert_gemm_tm.cuh"
 #include "expert_gemv.cuh"
 #include "expert_mma.cuh"
@@ -51,7 +52,10 @@ struct Plan {  // carved out of the scratch arena for one (layer shape, max_toke
     void * xin = nullptr;   // [T][n_embd] staging for the host entry point (input dtype bytes, <= 4 B/elt)
     float * outb = nullptr; // [T][n_embd] staging for the host entry point
     int * one_group_ids = nullptr;  // [T] group of every token when a dense matvec runs on the indexed-matmul kernel
-    __half * afp16 = nullptr;       // [T*k][max(n_in, n_ff)] expert-sorted fp16 activations of the tensor-core path
+    __half * afp16 = nullptr;       // [T*k][max(n_in, n_ff)] expert-sorted fp16 activations of the tensor-core path (or the FP4 digit planes)
+    uint8_t * asf = nullptr;        // scale tiles of the FP4 digit planes: [token tiles][K / 256][2048]
+    size_t asf_bytes = 0;
+    float * arow_scale = nullptr;   // [T*k] power of two per expert-sorted routed row (FP4 digit planes)
     size_t total = 0;
 };
 
@@ -130,7 +134,7 @@ void carve(Plan & p, uint8_t * base) {
     p.groups.perm = c.take<int>(std::max(R, T));
     p.groups.active = c.take<int>(E);
     p.groups.meta = c.take<int>(4);
-    p.groups.cost = c.take<int>(3 * (E + 1));
+    p.groups.cost = c.take<int>(4 * (E + 1));
     p.xq = c.act(T, std::max(H, kin));
     p.xlq = c.act(T, kin);
     p.hq = c.act(R, I);
@@ -143,7 +147,10 @@ void carve(Plan & p, uint8_t * base) {
     p.xin = c.take<float>(T * H);
     p.outb = c.take<float>(T * H);
     p.one_group_ids = c.take<int>(T);
-    p.afp16 = c.take<__half>(2 * std::max(R, T) * std::max({kin, I, H}));   // hi plane, then lo plane
+    p.afp16 = c.take<__half>(2 * std::max<size_t>(std::max(R, T), 64) * std::max({kin, I, H}));   // hi plane, then lo plane
+    p.asf_bytes = (std::min(E, R) + R / FP4_RPT + 1) * ((std::max(kin, I) + 255) / 256) * FP4_SF_TILE;
+    p.asf = c.take<uint8_t>(p.asf_bytes);
+    p.arow_scale = c.take<float>(std::max(R, T));
     p.total = align_up(c.off, 256);
 }
 
@@ -204,7 +211,7 @@ int validate_layer(b200moe_ctx * ctx, const b200moe_layer * l, bool need_router 
     return B200MOE_OK;
 }
 
-int ensure_plan(b200moe_ctx * ctx, int n_embd, int n_in, int n_expert, int k, int n_ff, int wtype, int tokens, cudaStream_t st = nullptr) {
+int ensure_plan(b200moe_ctx * ctx, int n_embd, int n_in, int n_expert, int k, int n_ff, int wtype, int tokens) {
     Plan & p = ctx->plan;
     if (p.max_tokens >= tokens && p.n_embd == n_embd && p.n_in == n_in && p.n_expert == n_expert && p.k == k && p.n_ff == n_ff &&
         p.wtype == wtype && ctx->scratch.base)
@@ -227,9 +234,22 @@ int ensure_plan(b200moe_ctx * ctx, int n_embd, int n_in, int n_expert, int k, in
         ctx->scratch.base = static_cast<uint8_t *>(ptr);
         ctx->scratch.bytes = np.total;
     }
-    carve(np, ctx->scratch.base);
-    CUDA_TRY(ctx, cudaMemsetAsync(np.one_group_ids, 0, sizeof(int) * np.max_tokens, st));
+    carve(np, ctx->scratch.base);   // nothing needs clearing: every buffer is written by the call that reads it
     ctx->plan = np;
+    return B200MOE_OK;
+}
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to the (function, device) pair, and one process may hold contexts on
+// several devices: every kernel instantiation keeps one flag per device ordinal.
+constexpr int MAX_DEVICE_ORDINALS = 64;
+
+template <typename Kern>
+int raise_smem_limit(b200moe_ctx * ctx, Kern kern, size_t smem, bool (&done)[MAX_DEVICE_ORDINALS]) {
+    if (ctx->device < 0 || ctx->device >= MAX_DEVICE_ORDINALS) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "device ordinal %d out of range", ctx->device);
+    if (!done[ctx->device]) {
+        CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+        done[ctx->device] = true;
+    }
     return B200MOE_OK;
 }
 
@@ -247,11 +267,8 @@ int launch_gemv_t(b200moe_ctx * ctx, const GemvParams & p, cudaStream_t st) {
     constexpr size_t smem = gemv_smem_bytes<WT, K, DUAL, NT, GEMV_STAGES>();
     static_assert(smem <= 227 * 1024, "ring does not fit shared memory");
     auto kern = expert_gemv_kernel<WT, K, DUAL, NT, GEMV_STAGES>;
-    static bool configured = false;  // per instantiation
-    if (!configured) {
-        CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-        configured = true;
-    }
+    static bool configured[MAX_DEVICE_ORDINALS] = {};  // per instantiation and device
+    if (int rc = raise_smem_limit(ctx, kern, smem, configured)) return rc;
     b200moe_ctx::Timed tm{};
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventCreate(&tm.beg));
@@ -274,11 +291,8 @@ int launch_gemv_tiny(b200moe_ctx * ctx, const GemvParams & p, int rows, cudaStre
     constexpr int NW = 4;
     constexpr size_t smem = gemv_smem_bytes<WT, K, DUAL, 1, 1, NW>();
     auto kern = expert_gemv_kernel<WT, K, DUAL, 1, 1, NW>;
-    static bool configured = false;  // per instantiation
-    if (!configured) {
-        CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-        configured = true;
-    }
+    static bool configured[MAX_DEVICE_ORDINALS] = {};  // per instantiation and device
+    if (int rc = raise_smem_limit(ctx, kern, smem, configured)) return rc;
     b200moe_ctx::Timed tm{};
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventCreate(&tm.beg));
@@ -358,11 +372,8 @@ template <int K, bool DUAL, int NT>
 int launch_gemm_t(b200moe_ctx * ctx, const MmaParams & p, int rows, cudaStream_t st) {
     using C = GemmCfg<K, DUAL, NT>;
     auto kern = expert_gemm_nvfp4_kernel<K, DUAL, NT>;
-    static bool configured = false;
-    if (!configured) {
-        CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) C::SMEM));
-        configured = true;
-    }
+    static bool configured[MAX_DEVICE_ORDINALS] = {};  // per instantiation and device
+    if (int rc = raise_smem_limit(ctx, kern, C::SMEM, configured)) return rc;
     constexpr uint64_t ROW_BYTES = K / 64 * 36;
     CUtensorMap mw0, mw1, mhi, mlo;
     int rc;
@@ -395,11 +406,8 @@ template <int K, bool DUAL>
 int launch_gemm_tm_t(b200moe_ctx * ctx, const MmaParams & p, int rows, cudaStream_t st) {
     using C = GemmTmCfg<K>;
     auto kern = expert_gemm_tm_kernel<K, DUAL>;
-    static bool configured = false;
-    if (!configured) {
-        CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) C::SMEM));
-        configured = true;
-    }
+    static bool configured[MAX_DEVICE_ORDINALS] = {};  // per instantiation and device
+    if (int rc = raise_smem_limit(ctx, kern, C::SMEM, configured)) return rc;
     constexpr uint64_t ROW_BYTES = K / 64 * 36;
     CUtensorMap mw0, mw1, mact;
     int rc;
@@ -441,6 +449,62 @@ int launch_gemm(b200moe_ctx * ctx, int k, const MmaParams & p, int rows, bool sm
     switch (k) { GEMM_CASE(256) GEMM_CASE(512) GEMM_CASE(768) GEMM_CASE(1024) GEMM_CASE(2048) }
 #undef GEMM_CASE
     return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no tensor-core expert kernel for width %d", k);
+}
+
+// block-scaled FP4 grouped GEMM (expert_gemm_fp4.cuh): digit planes of the routed rows, then the GEMM
+template <int K, bool DUAL>
+int launch_gemm_fp4_t(b200moe_ctx * ctx, const Fp4Params & fp, const void * w0, const void * w1, const uint8_t * planes, int rows, cudaStream_t st) {
+    using C = Fp4Cfg<K>;
+    auto kern = expert_gemm_fp4_kernel<K, DUAL>;
+    static bool configured[MAX_DEVICE_ORDINALS] = {};  // per instantiation and device
+    if (int rc = raise_smem_limit(ctx, kern, C::SMEM, configured)) return rc;
+    constexpr uint64_t ROW_BYTES = K / 64 * 36;
+    CUtensorMap mw0, mw1, mpl;
+    int rc;
+    const uint64_t wrows = (uint64_t) fp.n_as * fp.n_out;
+    if ((rc = make_map_2d(ctx, &mw0, CU_TENSOR_MAP_DATA_TYPE_UINT8, w0, ROW_BYTES, wrows, ROW_BYTES, GEMM_RAW_ROW, 128, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+    if (DUAL) {
+        if ((rc = make_map_2d(ctx, &mw1, CU_TENSOR_MAP_DATA_TYPE_UINT8, w1, ROW_BYTES, wrows, ROW_BYTES, GEMM_RAW_ROW, 128, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+    } else {
+        mw1 = mw0;
+    }
+    const uint64_t prows = std::max<uint64_t>((uint64_t) rows * FP4_PLANES, FP4_NCOL);
+    if ((rc = make_map_2d(ctx, &mpl, CU_TENSOR_MAP_DATA_TYPE_UINT8, planes, K / 2, prows, K / 2, 128, FP4_NCOL, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    b200moe_ctx::Timed tm{};
+    if (ctx->timing) {
+        CUDA_TRY(ctx, cudaEventCreate(&tm.beg));
+        CUDA_TRY(ctx, cudaEventCreate(&tm.end));
+        tm.kind = DUAL ? 0 : 1;
+        CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
+    }
+    kern<<<ctx->sm_count, FP4_THREADS, C::SMEM, st>>>(fp, mw0, mw1, mpl);
+    if (ctx->timing) {
+        CUDA_TRY(ctx, cudaEventRecord(tm.end, st));
+        ctx->timed.push_back(tm);
+    }
+    return check_launch(ctx, "expert_gemm_fp4");
+}
+
+template <bool DUAL>
+int launch_gemm_fp4(b200moe_ctx * ctx, int k, const Fp4Params & fp, const void * w0, const void * w1, const uint8_t * planes, int rows, cudaStream_t st) {
+#define GEMM_CASE(KK) case KK: return launch_gemm_fp4_t<KK, DUAL>(ctx, fp, w0, w1, planes, rows, st);
+    switch (k) { GEMM_CASE(256) GEMM_CASE(512) GEMM_CASE(768) GEMM_CASE(1024) GEMM_CASE(2048) }
+#undef GEMM_CASE
+    return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no FP4 tensor-core expert kernel for width %d", k);
+}
+
+// gate/up: 128 features per item; down: 256 rows per item
+bool fp4_supported(int wtype, int n_in, int n_ff) {
+    auto kok = [](int k) { return k == 256 || k == 512 || k == 768 || k == 1024 || k == 2048; };
+    return wtype == TYPE_NVFP4 && kok(n_in) && kok(n_ff) && n_ff % 128 == 0 && n_in % 256 == 0;
+}
+
+// digit planes + scale tiles of the expert-sorted routed rows (input of the FP4 kernels)
+int launch_act_planes(b200moe_ctx * ctx, ActQuant act, int rows, int k, int n_ids, int ne11, int n_as, cudaStream_t st) {
+    Plan & p = ctx->plan;
+    PlaneOut po{ reinterpret_cast<uint8_t *>(p.afp16), p.asf, p.arow_scale };
+    act_planes_kernel<<<rows, 256, 0, st>>>(act, p.groups.perm, p.ids, p.groups.offsets, p.groups.cost + 3 * (n_as + 1), rows, k, n_ids, ne11, n_as, po);
+    return check_launch(ctx, "act_planes");
 }
 
 bool mma_supported(int wtype, int k, int n_out) {
@@ -721,9 +785,14 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
     // int8 `hidden` the reference's own again.
     const bool latent = l->n_latent > 0;
     const bool dflt = path == 0 && many_rows;
+    // Paths 6 and 7: the block-scaled FP4 tensor-core kernels (weights used as they lie in HBM, activations as exact digit planes).
+    //   6: gate/up and down;   7: gate/up + exact re-quantisation fix-up, integer down (layer bit-identical to the reference)
+    const bool can_fp4 = fp4_supported(l->wtype, n_in, l->n_ff);
+    const bool fp4_gu = can_fp4 && (path == 6 || path == 7), fp4_down = can_fp4 && path == 6;
+    if ((path == 6 || path == 7) && !can_fp4) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "the FP4 tensor-core path needs NVFP4 experts with widths that are multiples of 256");
     const bool mma_down = can_mma && (path == 2 || path == 3 || path == 4 || (dflt && !latent));
     const bool mma_gu = can_mma && (path == 2 || path == 4 || path == 5 || dflt);
-    const bool fixup = mma_gu && (path == 4 || path == 5 || (dflt && (rows > 4096 || latent)));
+    const bool fixup = path == 7 || (mma_gu && (path == 4 || path == 5 || (dflt && (rows > 4096 || latent))));
     const bool small_tiles = rows < 24 * l->n_expert;   // on average fewer than 24 rows per expert
     auto mp = [&](const void * w0, const void * w1, const float * s0, const float * s1, float * out, int n_out, int m_k) {
         MmaParams m{};
@@ -737,7 +806,17 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
     // measured faster (167 us against 182 us at 64 tokens of configuration 2: there the tokens-on-M form is bound by
     // shared-memory traffic, twice the operand tile per stage).
     const bool tm_gu = false, tm_down = small_tiles && n_in % 256 == 0;
-    if (mma_gu) {
+    auto fpp = [&](const float * s0, const float * s1, float * out, int n_out) {
+        Fp4Params f{};
+        f.scale0 = s0; f.scale1 = s1; f.sf = p.asf; f.row_scale = p.arow_scale; f.offsets = p.groups.offsets; f.perm = p.groups.perm;
+        f.active = p.groups.active; f.meta = p.groups.meta; f.tile_of_expert = p.groups.cost + 3 * (l->n_expert + 1); f.out = out; f.n_out = n_out;
+        f.n_as = l->n_expert; f.err = ctx->d_err;
+        return f;
+    };
+    if (fp4_gu) {
+        if ((rc = launch_act_planes(ctx, xq, rows, n_in, k, 1, l->n_expert, st))) return rc;
+        if ((rc = launch_gemm_fp4<true>(ctx, n_in, fpp(l->gate_scale, l->up_scale, p.hid, l->n_ff), l->gate, l->up, reinterpret_cast<const uint8_t *>(p.afp16), rows, st))) return rc;
+    } else if (mma_gu) {
         if ((rc = launch_sorted_act(ctx, xq, rows, n_in, k, 1, tm_gu, st))) return rc;
         const MmaParams m = mp(l->gate, l->up, l->gate_scale, l->up_scale, p.hid, l->n_ff, n_in);
         if ((rc = tm_gu ? launch_gemm_tm<true>(ctx, n_in, m, rows, st) : launch_gemm<true>(ctx, n_in, m, rows, small_tiles, st))) return rc;
@@ -747,9 +826,12 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
     }
     if (fixup && (rc = launch_requant_fixup(ctx, l, xq, rows, n_in, k, st))) return rc;
     // the integer down kernel quantises `hidden` itself while staging it (NVFP4 / Q8_0); otherwise a separate pass
-    const bool fused_quant = !mma_down && l->wtype == TYPE_NVFP4;
+    const bool fused_quant = !mma_down && !fp4_down && l->wtype == TYPE_NVFP4;
     if (!fused_quant && (rc = launch_quantize<float>(ctx, p.hid, l->n_ff, p.hq, rows, l->n_ff, l->wtype, st))) return rc;
-    if (mma_down) {
+    if (fp4_down) {
+        if ((rc = launch_act_planes(ctx, p.hq, rows, l->n_ff, k, k, l->n_expert, st))) return rc;
+        if ((rc = launch_gemm_fp4<false>(ctx, l->n_ff, fpp(l->down_scale, nullptr, p.y, n_in), l->down, nullptr, reinterpret_cast<const uint8_t *>(p.afp16), rows, st))) return rc;
+    } else if (mma_down) {
         if ((rc = launch_sorted_act(ctx, p.hq, rows, l->n_ff, k, k, tm_down, st))) return rc;
         const MmaParams m = mp(l->down, nullptr, l->down_scale, nullptr, p.y, n_in, l->n_ff);
         if ((rc = tm_down ? launch_gemm_tm<false>(ctx, l->n_ff, m, rows, st) : launch_gemm<false>(ctx, l->n_ff, m, rows, small_tiles, st))) return rc;
@@ -904,7 +986,7 @@ int b200moe_get_counters(const b200moe_ctx * ctx, b200moe_counters * out) {
 }
 
 int b200moe_set_expert_path(b200moe_ctx * ctx, int path) {
-    if (!ctx || path < 0 || path > 5) return B200MOE_ERR_INVALID_ARG;
+    if (!ctx || path < 0 || path > 7) return B200MOE_ERR_INVALID_ARG;
     ctx->expert_path = path;
     return B200MOE_OK;
 }
@@ -1263,7 +1345,7 @@ int b200moe_mul_mat(b200moe_ctx * ctx, int wtype, const void * w, int64_t ne00, 
     if (!gemv_supported(wtype, ne00) || ne01 % 8) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no kernel for type %d, K=%lld", wtype, (long long) ne00);
     CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    int rc = ensure_plan(ctx, (int) ne00, (int) ne00, 8, 1, (int) ne00, wtype, (int) T, st);
+    int rc = ensure_plan(ctx, (int) ne00, (int) ne00, 8, 1, (int) ne00, wtype, (int) T);
     if (rc) return rc;
     return dense_matvec(ctx, wtype, w, scale, x, ctx->plan.xq, (int) ne00, (int) ne01, (int) T, dst, st);
 }

@@ -1,0 +1,424 @@
+// Grouped expert GEMM on the block-scaled FP4 tensor-core instruction (tcgen05.mma kind::mxf4nvf4, one UE4M3 scale per 16
+// elements, fp32 accumulators in tensor memory) for NVFP4 experts in batched decode.
+//
+// Why it fits: ggml's block_nvfp4 IS the operand format of that instruction - E2M1 codes, one UE4M3 scale per 16 elements
+// (ggml-common.h:221-227; the doubled code table and the halved scale decode of ggml-impl.h:514-527 cancel).  A weight row
+// needs no arithmetic at all before the MMA: the 4 scale bytes in front of every 32 code bytes are stripped while the row moves
+// from the raw TMA stage into the 128B-swizzled K-major operand tile, and collected as the scale-factor tile that tcgen05.cp
+// copies into tensor memory.  Element order inside a 16-block does not matter as long as both operands agree on it, so the
+// activations are simply stored in ggml's nibble order (byte j = elements j and j+8 of the block).
+//
+// Activations stay on the reference's int8 grid (q * d with d an fp16 number per 32 elements, the Q8_0 rows the CPU path
+// multiplies with).  With d = M * 2^e (M an 11-bit integer) the product q * M is an 18-bit integer; its seven balanced
+// radix-8 digits (each in [-4, 4], all E2M1 values) are seven "planes" of one routed row, and 2^e - relative to the row's
+// largest block exponent - is a power of two that UE4M3 holds exactly.  So
+//     x_hat[k] = 2^(E_row - 8) * sum_p 8^p * digit_p[k] * sf[k / 16]
+// is exact (blocks more than 17 binades below the row's largest flush to zero: a relative 2^-17 of the row's unit), every
+// product inside the tensor core is exact, and the result differs from the integer path only by fp32 accumulation.
+//
+// Operand roles: D[feature, plane] = W[feature, k] * P[plane, k].  M = 128 weight rows, N = 7 planes x up to 16 routed rows
+// (N = 8 .. 112), K = 64 per instruction.  The seven plane columns of a routed row sit next to each other in one lane of tensor
+// memory, so the epilogue recombines them with a Horner chain in registers and stores 32 consecutive features per warp.
+// Two weight tiles are in flight per stage with an accumulator each (gate and up rows of the same 128 features, or two
+// consecutive 128-row tiles of `down`): dependent MMAs on one accumulator issue every ~190-230 cycles, MMAs that alternate
+// between two accumulators every ~116 (measured with the probe kernel in fp4_probe.cuh).
+//
+// Roles (every wait bounded, as in expert_gemm.cuh):
+//   warp 0      raw-weight producer: tiled TMA of [128 rows][144 bytes] boxes (K = 256 per row) of both tiles
+//   warp 1      activation producer: one tiled TMA box [112 plane rows][128 bytes] + one bulk copy of the 2 KB scale tile
+//   warp 2      MMA issuer: per K = 64 step three tcgen05.cp (scales of tile 0, tile 1, planes) and two tcgen05.mma
+//   warp 3      owns tensor memory
+//   warps 4-7   epilogue
+//   warps 8-15  repack: thread = one weight row of one tile; 9 x 16-byte loads, 8 x 16-byte stores, 4 scale words
+#pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+#include "expert_gemm.cuh"
+#include "expert_mma.cuh"
+#include "formats.cuh"
+
+namespace b200moe {
+
+constexpr int FP4_PLANES = 7;
+constexpr int FP4_RPT = 16;                       // routed rows per token tile
+constexpr int FP4_NCOL = FP4_PLANES * FP4_RPT;    // 112 accumulator columns per weight tile
+constexpr int FP4_SF_TILE = 4 * 512;              // scale factors of 128 rows for the four K = 64 steps of a stage
+constexpr int FP4_THREADS = 512;
+
+__device__ __forceinline__ void umma_fp4(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                         bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %7, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], da, db, %4, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(sfa), "r"(sfb), "r"((uint32_t) accumulate)
+        : "memory");
+}
+// shared memory -> tensor memory: 32 rows x 16 bytes, replicated to the four lane quarters (the layout the MMA reads scales from)
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint32_t smem_addr) {
+    // matrix descriptor without swizzle: 8-row groups of 16-byte rows, 128 bytes apart
+    const uint64_t desc = (uint64_t) ((smem_addr >> 4) & 0x3fff) | ((uint64_t) (128 >> 4) << 32) | ((uint64_t) 1 << 46);
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+// instruction descriptor: E2M1 x E2M1, UE4M3 scales, both operands K-major, M = 128, N = n (a multiple of 8)
+__host__ __device__ constexpr uint32_t umma_idesc_fp4(int n) { return (1u << 7) | (1u << 10) | ((uint32_t) (n >> 3) << 17) | ((128u >> 4) << 24); }
+// byte offset of the 4 scale bytes of row r (0..127) inside the 512-byte scale tile of one K = 64 step
+__host__ __device__ constexpr uint32_t sf_tile_offset(int r) { return (uint32_t) ((r & 31) * 16 + (r >> 5) * 4); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
+        "%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+          "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// ---- activation planes ---------------------------------------------------------------------------------------------------
+// Expert-sorted routed row i -> seven plane rows 7i .. 7i+6 of `planes` (K/2 bytes each, ggml nibble order inside every
+// 16-block), its scale bytes in the scale tiles of its token tile, and the power of two the epilogue multiplies with.
+//   tile_of_expert[e]: index of expert e's first token tile (prefix of ceil(rows_e / 16))
+//   sf tiles: [tile][K / 256][4 steps][512 bytes], byte for (plane row n of the tile, 16-block g of the step) at sf_tile_offset(n) + g
+struct PlaneOut {
+    uint8_t * planes;       // [rows * 7][K / 2]
+    uint8_t * sf;           // [tiles][K / 256][2048]
+    float *   row_scale;    // [rows] by sorted position
+};
+
+__global__ void __launch_bounds__(256) act_planes_kernel(ActQuant act, const int * __restrict__ perm, const int32_t * __restrict__ ids,
+                                                        const int * __restrict__ offsets, const int * __restrict__ tile_of_expert, int rows,
+                                                        int K, int n_ids, int ne11, int n_as, PlaneOut out) {
+    __shared__ int s_emax[8];
+    __shared__ int s_E;
+    const int i = blockIdx.x;                      // sorted position
+    if (i >= rows) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r = perm[i];
+    const int arow = (r / n_ids) * ne11 + (r % n_ids) % ne11;
+    int e = ids[r];
+    e = e < 0 ? 0 : (e >= n_as ? n_as - 1 : e);    // bad ids were reported by the grouping kernels; stay inside the tables
+    const int row_beg = offsets[e];
+    const int in_tile = (i - row_beg) % FP4_RPT;
+    const int tile = tile_of_expert[e] + (i - row_beg) / FP4_RPT;
+    const int nb32 = K / 32;
+    const float * drow = act.d + (size_t) arow * nb32;
+    // largest block exponent of the row: d = M * 2^(exp8 - 137) with M the top 11 bits of the fp32 significand
+    int emax = -1000;
+    for (int b = tid; b < nb32; b += 256) {
+        const uint32_t bits = __float_as_uint(drow[b]);
+        if (bits & 0x7fffffffu) emax = max(emax, (int) ((bits >> 23) & 0xff) - 137);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) emax = max(emax, __shfl_xor_sync(0xffffffffu, emax, o));
+    if (lane == 0) s_emax[warp] = emax;
+    __syncthreads();
+    if (tid == 0) {
+        int m = s_emax[0];
+        for (int w = 1; w < 8; ++w) m = max(m, s_emax[w]);
+        s_E = m;
+        out.row_scale[i] = m > -1000 ? __uint_as_float((uint32_t) (m - 8 + 127) << 23) : 0.0f;   // 2^(E_row - 8); exponents here are far from the fp32 limits
+    }
+    __syncthreads();
+    const int E_row = s_E;
+    const int8_t * qrow = act.q + (size_t) arow * K;
+    uint8_t * prow = out.planes + (size_t) i * FP4_PLANES * (K / 2);
+    uint8_t * sft = out.sf + (size_t) tile * (K / 256) * FP4_SF_TILE;
+    // item = (16-block g, byte j): elements 16g + j and 16g + j + 8
+    for (int it = tid; it < K / 2; it += 256) {
+        const int g = it >> 3, j = it & 7;
+        const uint32_t bits = __float_as_uint(drow[g >> 1]);
+        const bool nz = (bits & 0x7fffffffu) != 0;
+        const int M = nz ? (int) (((bits & 0x7fffffu) | 0x800000u) >> 13) : 0;
+        const int s = nz ? (int) ((bits >> 23) & 0xff) - 137 - E_row + 8 : -100;          // scale exponent, at most 8
+        const int Ms = s >= -9 ? M : 0;                                                   // flushed blocks contribute nothing
+        int p0 = (int) qrow[16 * g + j] * Ms, p1 = (int) qrow[16 * g + j + 8] * Ms;
+#pragma unroll
+        for (int p = 0; p < FP4_PLANES; ++p) {
+            const int d0 = p < FP4_PLANES - 1 ? ((p0 + 4) & 7) - 4 : p0, d1 = p < FP4_PLANES - 1 ? ((p1 + 4) & 7) - 4 : p1;
+            p0 = (p0 - d0) >> 3;
+            p1 = (p1 - d1) >> 3;
+            // E2M1 codes of 0,1,2,3,4: 0,2,4,5,6; sign in bit 3
+            const uint32_t c0 = ((0x65420u >> (4 * abs(d0))) & 0xfu) | (d0 < 0 ? 8u : 0u);
+            const uint32_t c1 = ((0x65420u >> (4 * abs(d1))) & 0xfu) | (d1 < 0 ? 8u : 0u);
+            prow[(size_t) p * (K / 2) + it] = (uint8_t) (c0 | (c1 << 4));
+        }
+        if (j == 0) {
+            // UE4M3 byte of 2^s: normal for s >= -6, the three power-of-two subnormals below, zero when flushed
+            const uint32_t sb = s >= -6 ? (uint32_t) (s + 7) << 3 : s == -7 ? 4u : s == -8 ? 2u : s == -9 ? 1u : 0u;
+            uint8_t * dst = sft + (size_t) (g >> 4) * FP4_SF_TILE + ((g >> 2) & 3) * 512 + (g & 3);
+#pragma unroll
+            for (int p = 0; p < FP4_PLANES; ++p) dst[sf_tile_offset(in_tile * FP4_PLANES + p)] = (uint8_t) sb;
+        }
+    }
+}
+
+struct Fp4Params {
+    const float * scale0;   // per-expert fp32 scale of tile 0's tensor (or null)
+    const float * scale1;
+    const uint8_t * sf;     // activation scale tiles
+    const float * row_scale;
+    const int * offsets;    // [n_as + 1]
+    const int * perm;       // [rows]
+    const int * active;     // [n_as]
+    const int * meta;
+    const int * tile_of_expert;
+    float * out;            // [rows][n_out] indexed by routed row
+    int n_out;
+    int n_as;
+    int * err;
+};
+
+template <int K>
+struct Fp4Cfg {
+    static constexpr int A_TILE = 128 * 128;                         // 128 weight rows x 256 K as fp4
+    static constexpr int B_TILE = FP4_NCOL * 128;                    // 112 plane rows
+    static constexpr int STAGE = 2 * A_TILE + 2 * FP4_SF_TILE + B_TILE + FP4_SF_TILE;
+    static constexpr int RAW_STAGE = 256 * GEMM_RAW_ROW;
+    static constexpr int RS = 3;
+    static constexpr int TS = 2;
+    static constexpr uint32_t TMEM_COLS = 512;                        // 2 buffers x 2 accumulators x 112 columns, then the scale factors
+    static constexpr uint32_t SF_COL = 4 * FP4_NCOL;                  // 448
+    static_assert(STAGE % 1024 == 0, "stages keep the 1024-byte alignment of swizzled tiles");
+    static_assert(K % GEMM_RAW_K == 0, "K must be a multiple of 256");
+    static constexpr size_t SMEM = (size_t) TS * STAGE + (size_t) RS * RAW_STAGE + 1024;
+};
+
+// DUAL: tile 0 = gate rows f .. f+127, tile 1 = up rows of the same features; epilogue = SwiGLU; 128 features per item.
+// single: tiles 0 and 1 = 256 consecutive rows of the one tensor; 256 features per item.
+template <int K, bool DUAL>
+__global__ void __launch_bounds__(FP4_THREADS, 1)
+expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1,
+                       const __grid_constant__ CUtensorMap map_planes) {
+    using C = Fp4Cfg<K>;
+    constexpr int TS = C::TS, RS = C::RS;
+    constexpr int KC = K / GEMM_RAW_K;
+    constexpr int FEAT = DUAL ? 128 : 256;
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t * tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
+    uint8_t * raws = tiles + (size_t) TS * C::STAGE;
+    __shared__ uint64_t raw_full[RS], raw_empty[RS], tile_full[TS], tile_empty[TS], acc_full[2], acc_empty[2];
+    __shared__ uint32_t s_tmem;
+    __shared__ volatile int s_abort;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 8); }
+        for (int i = 0; i < TS; ++i) { mbar_init(&tile_full[i], 256 + 1); mbar_init(&tile_empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+        mbar_fence_init();
+        s_abort = 0;
+    }
+    if (warp == 3) {
+        tmem_alloc(&s_tmem, C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+
+    const int n_active = p.meta[0];
+    const int f_tiles = p.n_out / FEAT;
+    const int n_items = n_active * f_tiles;
+    // stage layout: [A0][A1][SFA0][SFA1][B][SFB]
+    constexpr uint32_t OFF_A1 = C::A_TILE, OFF_SFA = 2 * C::A_TILE, OFF_B = OFF_SFA + 2 * FP4_SF_TILE, OFF_SFB = OFF_B + C::B_TILE;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- raw weight producer
+        if (lane == 0) {
+            Ring raw;
+            for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
+                const int a = item / f_tiles, ft = item % f_tiles;
+                const int e = p.active[a];
+                const int n_e = p.offsets[e + 1] - p.offsets[e];
+                const int row0 = e * p.n_out + ft * FEAT;
+                for (int t0 = 0; t0 < n_e && !s_abort; t0 += FP4_RPT) {
+                    for (int kc = 0; kc < KC; ++kc) {
+                        if (!wait_or_abort<200>(&raw_empty[raw.stage], raw.phase ^ 1u, &s_abort, p.err)) break;
+                        uint8_t * dst = raws + (size_t) raw.stage * C::RAW_STAGE;
+                        mbar_arrive_expect_tx(&raw_full[raw.stage], C::RAW_STAGE);
+                        tma_load_2d(dst, &map_w0, kc * GEMM_RAW_ROW, row0, &raw_full[raw.stage]);
+                        if (DUAL) tma_load_2d(dst + 128 * GEMM_RAW_ROW, &map_w1, kc * GEMM_RAW_ROW, row0, &raw_full[raw.stage]);
+                        else tma_load_2d(dst + 128 * GEMM_RAW_ROW, &map_w0, kc * GEMM_RAW_ROW, row0 + 128, &raw_full[raw.stage]);
+                        raw.template advance<RS>();
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- activation producer
+        if (lane == 0) {
+            Ring tile;
+            for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
+                const int e = p.active[item / f_tiles];
+                const int row_beg = p.offsets[e], n_e = p.offsets[e + 1] - row_beg;
+                const int tile0 = p.tile_of_expert[e];
+                for (int t0 = 0; t0 < n_e && !s_abort; t0 += FP4_RPT) {
+                    const uint8_t * sft = p.sf + (size_t) (tile0 + t0 / FP4_RPT) * KC * FP4_SF_TILE;
+                    for (int kc = 0; kc < KC; ++kc) {
+                        if (!wait_or_abort<100>(&tile_empty[tile.stage], tile.phase ^ 1u, &s_abort, p.err)) break;
+                        uint8_t * st = tiles + (size_t) tile.stage * C::STAGE;
+                        mbar_arrive_expect_tx(&tile_full[tile.stage], C::B_TILE + FP4_SF_TILE);
+                        tma_load_2d(st + OFF_B, &map_planes, kc * 128, FP4_PLANES * (row_beg + t0), &tile_full[tile.stage]);
+                        bulk_g2s(st + OFF_SFB, sft + (size_t) kc * FP4_SF_TILE, FP4_SF_TILE, &tile_full[tile.stage]);
+                        tile.template advance<TS>();
+                    }
+                }
+            }
+        }
+    } else if (warp == 2) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            Ring tile, acc;
+            for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
+                const int e = p.active[item / f_tiles];
+                const int n_e = p.offsets[e + 1] - p.offsets[e];
+                for (int t0 = 0; t0 < n_e && !s_abort; t0 += FP4_RPT) {
+                    const int nt = min(FP4_RPT, n_e - t0);
+                    const uint32_t idesc = umma_idesc_fp4((FP4_PLANES * nt + 7) & ~7);
+                    if (!wait_or_abort<40>(&acc_empty[acc.stage], acc.phase ^ 1u, &s_abort, p.err)) break;
+                    tc_fence_after();
+                    const uint32_t d0 = tmem + (uint32_t) acc.stage * (2 * FP4_NCOL), d1 = d0 + FP4_NCOL;
+                    for (int kc = 0; kc < KC; ++kc) {
+                        if (!wait_or_abort<40>(&tile_full[tile.stage], tile.phase, &s_abort, p.err)) break;
+                        tc_fence_after();
+                        const uint32_t sbase = smem_u32(tiles + (size_t) tile.stage * C::STAGE);
+                        const uint32_t da = DESC_LO | (sbase >> 4);
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {   // 4 x K64 = 256; 32 bytes (2 units) further along the 128-byte row each
+                            const uint32_t t_sfa0 = tmem + C::SF_COL + 12 * kk, t_sfa1 = t_sfa0 + 4, t_sfb = t_sfa0 + 8;
+                            tmem_cp_sf(t_sfa0, sbase + OFF_SFA + kk * 512);
+                            tmem_cp_sf(t_sfa1, sbase + OFF_SFA + FP4_SF_TILE + kk * 512);
+                            tmem_cp_sf(t_sfb, sbase + OFF_SFB + kk * 512);
+                            const bool accum = kc != 0 || kk != 0;
+                            umma_fp4(d0, da + 2 * kk, da + (OFF_B >> 4) + 2 * kk, DESC_HI, idesc, t_sfa0, t_sfb, accum);
+                            umma_fp4(d1, da + (OFF_A1 >> 4) + 2 * kk, da + (OFF_B >> 4) + 2 * kk, DESC_HI, idesc, t_sfa1, t_sfb, accum);
+                        }
+                        umma_commit(&tile_empty[tile.stage]);   // frees the operand stage when these MMAs have read it
+                        tile.template advance<TS>();
+                    }
+                    umma_commit(&acc_full[acc.stage]);
+                    acc.template advance<2>();
+                }
+            }
+        }
+    } else if (warp >= 4 && warp < 8) {
+        // ---------------------------------------------------------------- epilogue
+        Ring acc;
+        const int q = warp & 3;                 // TMEM lane quarter this warp may read
+        for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
+            const int a = item / f_tiles, ft = item % f_tiles;
+            const int e = p.active[a];
+            const int row_beg = p.offsets[e], n_e = p.offsets[e + 1] - row_beg;
+            const float sc0 = p.scale0 ? p.scale0[e] : 1.0f;
+            const float sc1 = DUAL ? (p.scale1 ? p.scale1[e] : 1.0f) : sc0;
+            const int feature = ft * FEAT + q * 32 + lane;
+            for (int t0 = 0; t0 < n_e && !s_abort; t0 += FP4_RPT) {
+                const int nt = min(FP4_RPT, n_e - t0);
+                // lanes leave the polling loop one by one: the vote reconverges the warp (tcgen05.ld below needs all of it)
+                if (!__all_sync(0xffffffffu, wait_or_abort<200>(&acc_full[acc.stage], acc.phase, &s_abort, p.err))) break;
+                tc_fence_after();
+                const uint32_t d0 = tmem + (uint32_t) acc.stage * (2 * FP4_NCOL) + ((uint32_t) (q * 32) << 16);
+                for (int g = 0; g < nt; g += 4) {          // four routed rows = 28 plane columns per load
+                    float v0[32], v1[32];
+                    tmem_ld32(d0 + FP4_PLANES * g, v0);
+                    tmem_ld32(d0 + FP4_NCOL + FP4_PLANES * g, v1);
+#pragma unroll
+                    for (int rr = 0; rr < 4; ++rr) {
+                        if (g + rr < nt) {
+                            const int i = row_beg + t0 + g + rr;
+                            const float rs = p.row_scale[i];
+                            // sum_p 8^p * plane_p, highest plane first
+                            float x0 = v0[7 * rr + 6], x1 = v1[7 * rr + 6];
+#pragma unroll
+                            for (int pl = 5; pl >= 0; --pl) {
+                                x0 = __fmaf_rn(x0, 8.0f, v0[7 * rr + pl]);
+                                x1 = __fmaf_rn(x1, 8.0f, v1[7 * rr + pl]);
+                            }
+                            x0 = __fmul_rn(__fmul_rn(x0, rs), sc0);
+                            x1 = __fmul_rn(__fmul_rn(x1, rs), sc1);
+                            float * orow = p.out + (size_t) p.perm[i] * p.n_out;
+                            if (DUAL) orow[feature] = __fmul_rn(ggml_silu(x0), x1);
+                            else { orow[feature] = x0; orow[feature + 128] = x1; }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[acc.stage]);
+                acc.template advance<2>();
+            }
+        }
+    } else if (warp >= 8) {
+        // ---------------------------------------------------------------- repack: strip the scale bytes, keep everything else
+        const int dq = tid - 256;
+        const int trow = dq & 127, tsel = dq >> 7;
+        uint32_t a_off[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) a_off[c] = tsel * C::A_TILE + sw128_offset(trow, c);
+        const uint32_t sf_off = OFF_SFA + tsel * FP4_SF_TILE + sf_tile_offset(trow);
+        const uint32_t raw_off = (uint32_t) dq * GEMM_RAW_ROW;
+        Ring raw, tile;
+        for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
+            const int e = p.active[item / f_tiles];
+            const int n_e = p.offsets[e + 1] - p.offsets[e];
+            for (int t0 = 0; t0 < n_e && !s_abort; t0 += FP4_RPT) {
+                for (int kc = 0; kc < KC && !s_abort; ++kc) {
+                    if (!__all_sync(0xffffffffu, wait_or_abort(&raw_full[raw.stage], raw.phase, &s_abort, p.err))) break;
+                    uint32_t R[36];                // 4 blocks of [scale word][8 code words]
+                    {
+                        const uint4 * src = reinterpret_cast<const uint4 *>(raws + (size_t) raw.stage * C::RAW_STAGE + raw_off);
+#pragma unroll
+                        for (int i = 0; i < 9; ++i) {
+                            const uint4 v = src[i];
+                            R[4 * i] = v.x; R[4 * i + 1] = v.y; R[4 * i + 2] = v.z; R[4 * i + 3] = v.w;
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&raw_empty[raw.stage]);
+                    raw.template advance<RS>();
+                    if (!__all_sync(0xffffffffu, wait_or_abort(&tile_empty[tile.stage], tile.phase ^ 1u, &s_abort, p.err))) break;
+                    uint8_t * st = tiles + (size_t) tile.stage * C::STAGE;
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) {
+                        *reinterpret_cast<uint4 *>(st + a_off[2 * kb]) = make_uint4(R[9 * kb + 1], R[9 * kb + 2], R[9 * kb + 3], R[9 * kb + 4]);
+                        *reinterpret_cast<uint4 *>(st + a_off[2 * kb + 1]) = make_uint4(R[9 * kb + 5], R[9 * kb + 6], R[9 * kb + 7], R[9 * kb + 8]);
+                        // The reference reads scale bytes through ggml_ue4m3_to_fp32: bit 7 ignored, 0x7f decodes to zero; to the tensor
+                        // core 0x7f is NaN.  Clear bit 7 and turn 0x7f into 0 (t <= 0x7f per byte, so t + 1 carries into bit 7 only
+                        // for 0x7f and never into the next byte).
+                        const uint32_t t = R[9 * kb] & 0x7f7f7f7fu;
+                        const uint32_t nan1 = ((t + 0x01010101u) >> 7) & 0x01010101u;
+                        *reinterpret_cast<uint32_t *>(st + sf_off + kb * 512) = t & ~((nan1 << 7) - nan1);
+                    }
+                    // every writer orders its own stores against the tensor core's (async proxy) reads and then arrives itself
+                    fence_async_smem();
+                    mbar_arrive(&tile_full[tile.stage]);
+                    tile.template advance<TS>();
+                }
+            }
+        }
+    }
+
+    // ---- teardown: everyone meets here (all waits above are bounded), then tensor memory goes back
+    if (s_abort) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 1000000ull) { }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 3) tmem_dealloc(tmem, C::TMEM_COLS);
+}
+
+}  // namespace b200moe

@@ -344,7 +344,8 @@ struct Groups {
     int * perm;     // [rows]
     int * active;   // [E]
     int * meta;     // [4]
-    int * cost;     // [3][E+1]: prefix over active experts of the work per weight row for the nt = 1, 2, 4 kernels
+    int * cost;     // [4][E+1]: rows 0-2: prefix over active experts of the work per weight row for the nt = 1, 2, 4 kernels;
+                    // row 3, indexed by EXPERT id: index of the expert's first 16-row token tile (prefix of ceil(rows / 16))
 };
 
 // Block-wide: counts must be final and visible to this block.
@@ -354,19 +355,21 @@ __device__ __forceinline__ void group_scan_body(Groups g, const int32_t * __rest
     const int tid = threadIdx.x;
     if (tid < 32) {
         // warp 0: exclusive scan of counts, compaction of active experts and the three work prefixes, 32 experts a step
-        int run = 0, na = 0, c1 = 0, c2 = 0, c4 = 0;
+        int run = 0, na = 0, c1 = 0, c2 = 0, c4 = 0, tl = 0;
         for (int base = 0; base < E; base += 32) {
             const int e = base + tid;
             const int n = e < E ? g.counts[e] : 0;
             // work per weight row: nt=1 kernels: one pass per routed row; nt=4 kernels: 3 per pass (decode) + 2 per routed row
             int incl = n, w2 = (n + 1) / 2, w4 = 3 * ((n + 3) / 4) + 2 * n;
-            int i2 = w2, i4 = w4;
+            int i2 = w2, i4 = w4, it = (n + 15) / 16;
+            const int wt = it;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const int a = __shfl_up_sync(0xffffffffu, incl, o), b = __shfl_up_sync(0xffffffffu, i2, o), c = __shfl_up_sync(0xffffffffu, i4, o);
-                if (tid >= o) { incl += a; i2 += b; i4 += c; }
+                const int d = __shfl_up_sync(0xffffffffu, it, o);
+                if (tid >= o) { incl += a; i2 += b; i4 += c; it += d; }
             }
-            if (e < E) off[e] = run + incl - n;
+            if (e < E) { off[e] = run + incl - n; g.cost[3 * (E + 1) + e] = tl + it - wt; }
             const unsigned m = __ballot_sync(0xffffffffu, n > 0);
             if (n > 0) {
                 const int a = na + __popc(m & ((1u << tid) - 1));
@@ -380,11 +383,12 @@ __device__ __forceinline__ void group_scan_body(Groups g, const int32_t * __rest
             c1 += __shfl_sync(0xffffffffu, incl, 31);
             c2 += __shfl_sync(0xffffffffu, i2, 31);
             c4 += __shfl_sync(0xffffffffu, i4, 31);
+            tl += __shfl_sync(0xffffffffu, it, 31);
             na += __popc(m);
         }
         if (tid == 0) {
             off[E] = run;
-            g.cost[na] = c1; g.cost[(E + 1) + na] = c2; g.cost[2 * (E + 1) + na] = c4;
+            g.cost[na] = c1; g.cost[(E + 1) + na] = c2; g.cost[2 * (E + 1) + na] = c4; g.cost[3 * (E + 1) + E] = tl;
             g.meta[0] = na;
             g.meta[1] = run;
             if (run != rows) report_error(err, DEV_ERR_BAD_SHAPE);
