@@ -35,6 +35,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
            "--shared", "-Xcompiler", "-fPIC,-fvisibility=hidden", "-o", LIB] + SRC
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
+    cmd[1:1] = os.environ.get("B200MOE_NVCC_FLAGS", "").split()   # development switches, e.g. -DB200MOE_FP4_PROF
     subprocess.check_call(cmd)
     return LIB
 

@@ -29,7 +29,7 @@ class Observe(C.Structure):
 
 
 class Counters(C.Structure):
-    _fields_ = [(n, C.c_int64) for n in ("tokens", "experts_touched", "weight_bytes", "kernel_launches")]
+    _fields_ = [(n, C.c_int64) for n in ("tokens", "experts_touched", "weight_bytes", "kernel_launches", "fixup_overflow")]
 
 
 # name -> (restype, argtypes); every symbol include/edge0_b200_moe.h declares
@@ -55,12 +55,22 @@ SIGNATURES = {
     "b200moe_mul_mat_id": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int64,
                                      C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
     "b200moe_mul_mat": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200moe_latent_down": (C.c_int, [C.c_void_p, C.POINTER(Layer), C.c_void_p, C.c_int, C.c_int32, C.c_void_p, C.c_void_p]),
+    "b200moe_latent_up": (C.c_int, [C.c_void_p, C.POINTER(Layer), C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "b200moe_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
     "b200moe_gather_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
+    "b200moe_ep_slot_bytes": (C.c_int64, [C.c_int64]),
+    "b200moe_ep_pack": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200moe_ep_expert_rows": (C.c_int, [C.c_void_p, C.POINTER(Layer), C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
+    "b200moe_ep_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                     C.c_void_p, C.c_void_p]),
     "b200moe_ffn": (C.c_int, [C.c_void_p, C.POINTER(Layer), C.c_void_p, C.c_int, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
                               C.POINTER(Observe), C.c_void_p]),
     "b200moe_layer_forward": (C.c_int, [C.c_void_p, C.POINTER(Layer), C.c_void_p, C.c_int, C.c_int32, C.c_void_p,
                                         C.POINTER(Observe), C.c_void_p]),
+    "b200moe_probe_fp4_tile": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200moe_probe_fp4_rate": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double)]),
     "b200moe_route_noalloc": (C.c_int, [C.c_int, C.POINTER(Layer), C.c_void_p, C.c_int, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
                                         C.c_char_p, C.c_size_t]),
     "b200moe_layer_forward_host": (C.c_int, [C.c_void_p, C.POINTER(Layer), C.c_void_p, C.c_int, C.c_int32, C.c_void_p,

@@ -18,9 +18,11 @@
 #include "../../include/edge0_b200_moe.h"
 #include "expert_gemm.cuh"
 #include "expert_gemm_fp4.cuh"
+#include "expert_exchange.cuh"
 #include "expert_gemm_tm.cuh"
 #include "expert_gemv.cuh"
 #include "expert_mma.cuh"
+#include "fp4_probe.cuh"
 #include "requant_fixup.cuh"
 #include "router.cuh"
 
@@ -66,8 +68,8 @@ struct b200moe_ctx {
     int sm_count = 0;
     Scratch scratch;
     Plan plan;
-    int * d_err = nullptr;
-    int * h_err = nullptr;  // pinned
+    int * d_err = nullptr;  // 16 bytes: [error code][pad][fix-up overflow counter, 64 bit]
+    int * h_err = nullptr;  // pinned copy of the same
     std::string last_error;
     b200moe_counters counters{};
     int64_t launches = 0;
@@ -75,6 +77,7 @@ struct b200moe_ctx {
     int expert_path = 0;  // 0 auto, 1 integer GEMV always, 2 tensor-core GEMM whenever the shape allows
     bool overlap = false; // launch the layer's kernels as programmatic dependents of one another (opt-in)
     bool overlap_now = false;  // set per call: only the small-batch regime uses it (see layer_overlap)
+    bool dense_now = false;    // the expert kernels are running a dense product (kernel-timing kind 2)
     struct Timed { cudaEvent_t beg, end; int kind; };
     std::vector<Timed> timed;
 };
@@ -148,7 +151,7 @@ void carve(Plan & p, uint8_t * base) {
     p.outb = c.take<float>(T * H);
     p.one_group_ids = c.take<int>(T);
     p.afp16 = c.take<__half>(2 * std::max<size_t>(std::max(R, T), 64) * std::max({kin, I, H}));   // hi plane, then lo plane
-    p.asf_bytes = (std::min(E, R) + R / FP4_RPT + 1) * ((std::max(kin, I) + 255) / 256) * FP4_SF_TILE;
+    p.asf_bytes = (std::min(E, std::max(R, T)) + std::max(R, T) / FP4_RPT + 1) * ((std::max({kin, I, H}) + 255) / 256) * FP4_SF_TILE;
     p.asf = c.take<uint8_t>(p.asf_bytes);
     p.arow_scale = c.take<float>(std::max(R, T));
     p.total = align_up(c.off, 256);
@@ -186,6 +189,16 @@ cudaError_t launch_k(const b200moe_ctx * ctx, void (*kern)(KArgs...), dim3 grid,
     return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
+// Exact re-quantisation behind the tensor-core gate/up GEMM (requant_fixup.cuh): list the values of `hidden` whose int8
+// rounding the GEMM's error could change, recompute them with the integer lane chains, patch `hidden`.
+// The list lives in the `down` output buffer, which is not in use yet.
+// after the kind::f16 GEMM (activations as fp16 hi + lo):
+constexpr float FIX_STEP_MARGIN = 0.015f;  // quantisation steps; largest GEMM error measured: 3.8e-3 steps (p99.99: 1.8e-3)
+constexpr float FIX_REL_MARGIN = 1.2e-4f;  // of the block maximum; largest error measured: 3.0e-5 of it
+// after the block-scaled FP4 GEMM (exact digit planes; only fp32 accumulation differs):
+constexpr float FIX_STEP_MARGIN_FP4 = 2.5e-3f;  // largest error measured: 2.3e-4 steps (p99.99: 1.0e-4)
+constexpr float FIX_REL_MARGIN_FP4 = 2.0e-5f;   // largest error measured: 1.8e-6 of the block maximum
+
 // need_router / need_experts: which weight pointers the entry point is going to read
 int validate_layer(b200moe_ctx * ctx, const b200moe_layer * l, bool need_router = true, bool need_experts = true) {
     if (!ctx) return B200MOE_ERR_INVALID_ARG;
@@ -194,7 +207,8 @@ int validate_layer(b200moe_ctx * ctx, const b200moe_layer * l, bool need_router 
         return fail(ctx, B200MOE_ERR_INVALID_ARG, "non-positive layer dimension");
     if (l->n_expert_used > l->n_expert) return fail(ctx, B200MOE_ERR_INVALID_ARG, "n_expert_used > n_expert");
     if (l->n_expert_used > 32) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "n_expert_used > 32");
-    if (l->n_expert > 1024 || l->n_expert % 8) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "n_expert must be a multiple of 8, at most 1024");
+    if (l->n_expert > 1024) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "at most 1024 experts");
+    if (need_router && l->n_expert % 8) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "routing needs n_expert to be a multiple of 8");
     if (l->n_embd % 32) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "n_embd must be a multiple of 32");
     if (l->wtype != TYPE_NVFP4 && l->wtype != TYPE_Q3_K) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "expert type %d has no kernel", l->wtype);
     const int n_in = l->n_latent ? l->n_latent : l->n_embd;
@@ -273,7 +287,7 @@ int launch_gemv_t(b200moe_ctx * ctx, const GemvParams & p, cudaStream_t st) {
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventCreate(&tm.beg));
         CUDA_TRY(ctx, cudaEventCreate(&tm.end));
-        tm.kind = DUAL ? 0 : 1;
+        tm.kind = DUAL ? 0 : ctx->dense_now ? 2 : 1;
         CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
     }
     launch_k(ctx, kern, dim3(ctx->sm_count), dim3(GemvCfg<WT, K>::NWARPS * 32), smem, st, p);
@@ -297,7 +311,7 @@ int launch_gemv_tiny(b200moe_ctx * ctx, const GemvParams & p, int rows, cudaStre
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventCreate(&tm.beg));
         CUDA_TRY(ctx, cudaEventCreate(&tm.end));
-        tm.kind = DUAL ? 0 : 1;
+        tm.kind = DUAL ? 0 : ctx->dense_now ? 2 : 1;
         CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
     }
     // one CTA per stage-sized chunk; at most `rows` experts are active, CTAs past the end of the row list leave at once
@@ -390,7 +404,7 @@ int launch_gemm_t(b200moe_ctx * ctx, const MmaParams & p, int rows, cudaStream_t
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventCreate(&tm.beg));
         CUDA_TRY(ctx, cudaEventCreate(&tm.end));
-        tm.kind = DUAL ? 0 : 1;
+        tm.kind = DUAL ? 0 : ctx->dense_now ? 2 : 1;
         CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
     }
     launch_k(ctx, kern, dim3(ctx->sm_count), dim3(GEMM_THREADS), C::SMEM, st, p, mw0, mw1, mhi, mlo);
@@ -423,7 +437,7 @@ int launch_gemm_tm_t(b200moe_ctx * ctx, const MmaParams & p, int rows, cudaStrea
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventCreate(&tm.beg));
         CUDA_TRY(ctx, cudaEventCreate(&tm.end));
-        tm.kind = DUAL ? 0 : 1;
+        tm.kind = DUAL ? 0 : ctx->dense_now ? 2 : 1;
         CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
     }
     launch_k(ctx, kern, dim3(ctx->sm_count), dim3(GEMM_TM_THREADS), C::SMEM, st, p, mw0, mw1, mact);
@@ -468,16 +482,38 @@ int launch_gemm_fp4_t(b200moe_ctx * ctx, const Fp4Params & fp, const void * w0, 
     } else {
         mw1 = mw0;
     }
-    const uint64_t prows = std::max<uint64_t>((uint64_t) rows * FP4_PLANES, FP4_NCOL);
-    if ((rc = make_map_2d(ctx, &mpl, CU_TENSOR_MAP_DATA_TYPE_UINT8, planes, K / 2, prows, K / 2, 128, FP4_NCOL, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    const uint64_t prows = std::max<uint64_t>((uint64_t) rows * FP4_PLANES, FP4_NROW);
+    if ((rc = make_map_2d(ctx, &mpl, CU_TENSOR_MAP_DATA_TYPE_UINT8, planes, K / 2, prows, K / 2, 128, FP4_NROW, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
     b200moe_ctx::Timed tm{};
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventCreate(&tm.beg));
         CUDA_TRY(ctx, cudaEventCreate(&tm.end));
-        tm.kind = DUAL ? 0 : 1;
+        tm.kind = DUAL ? 0 : ctx->dense_now ? 2 : 1;
         CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
     }
+#ifdef B200MOE_FP4_PROF
+    static long long * d_prof = nullptr;
+    if (!d_prof) cudaMalloc(&d_prof, sizeof(long long) * 24 * 256);
+    cudaMemsetAsync(d_prof, 0, sizeof(long long) * 24 * 256, st);
+    Fp4Params fpp2 = fp;
+    fpp2.prof = d_prof;
+    kern<<<ctx->sm_count, FP4_THREADS, C::SMEM, st>>>(fpp2, mw0, mw1, mpl);
+    if (getenv("B200MOE_FP4_PROF_PRINT")) {
+        std::vector<long long> h(24 * 256);
+        cudaStreamSynchronize(st);
+        cudaMemcpy(h.data(), d_prof, sizeof(long long) * 24 * 256, cudaMemcpyDeviceToHost);
+        const char * names[13] = {"raw: wait raw_empty", "raw: total", "act: wait act_empty", "act: total", "mma: wait acc_empty", "mma: wait act_full", "mma: wait tile_full", "mma: total",
+                                  "epi: wait acc_full", "epi: total", "repack: wait raw_full", "repack: wait tile_empty", "repack: total"};
+        printf("fp4 kernel K=%d DUAL=%d role cycles (mean over CTAs / max):\n", K, (int) DUAL);
+        for (int k = 0; k < 13; ++k) {
+            double sum = 0; long long mx = 0;
+            for (int b = 0; b < ctx->sm_count; ++b) { sum += h[b * 24 + k]; mx = std::max(mx, h[b * 24 + k]); }
+            printf("  %-26s %10.0f %10lld\n", names[k], sum / ctx->sm_count, mx);
+        }
+    }
+#else
     kern<<<ctx->sm_count, FP4_THREADS, C::SMEM, st>>>(fp, mw0, mw1, mpl);
+#endif
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventRecord(tm.end, st));
         ctx->timed.push_back(tm);
@@ -488,23 +524,35 @@ int launch_gemm_fp4_t(b200moe_ctx * ctx, const Fp4Params & fp, const void * w0, 
 template <bool DUAL>
 int launch_gemm_fp4(b200moe_ctx * ctx, int k, const Fp4Params & fp, const void * w0, const void * w1, const uint8_t * planes, int rows, cudaStream_t st) {
 #define GEMM_CASE(KK) case KK: return launch_gemm_fp4_t<KK, DUAL>(ctx, fp, w0, w1, planes, rows, st);
-    switch (k) { GEMM_CASE(256) GEMM_CASE(512) GEMM_CASE(768) GEMM_CASE(1024) GEMM_CASE(2048) }
+    switch (k) { GEMM_CASE(256) GEMM_CASE(512) GEMM_CASE(768) GEMM_CASE(1024) GEMM_CASE(2048) GEMM_CASE(4096) }
 #undef GEMM_CASE
     return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no FP4 tensor-core expert kernel for width %d", k);
 }
 
 // gate/up: 128 features per item; down: 256 rows per item
-bool fp4_supported(int wtype, int n_in, int n_ff) {
-    auto kok = [](int k) { return k == 256 || k == 512 || k == 768 || k == 1024 || k == 2048; };
-    return wtype == TYPE_NVFP4 && kok(n_in) && kok(n_ff) && n_ff % 128 == 0 && n_in % 256 == 0;
-}
+bool fp4_width(int k) { return k == 256 || k == 512 || k == 768 || k == 1024 || k == 2048 || k == 4096; }
+bool fp4_supported(int wtype, int n_in, int n_ff) { return wtype == TYPE_NVFP4 && fp4_width(n_in) && fp4_width(n_ff) && n_ff % 128 == 0 && n_in % 256 == 0; }
 
 // digit planes + scale tiles of the expert-sorted routed rows (input of the FP4 kernels)
-int launch_act_planes(b200moe_ctx * ctx, ActQuant act, int rows, int k, int n_ids, int ne11, int n_as, cudaStream_t st) {
+// act: rows already on the int8 grid; or src != null: fp32 rows (src_stride floats apart) that are quantised (Q8_0) on the way.
+// ids: expert of every routed row; n_as experts; the token-tile prefix lies behind the three work prefixes of the group tables.
+int launch_act_planes(b200moe_ctx * ctx, ActQuant act, const float * src, const int32_t * ids, int rows, int k, int n_ids, int ne11, int n_as,
+                      cudaStream_t st) {
     Plan & p = ctx->plan;
     PlaneOut po{ reinterpret_cast<uint8_t *>(p.afp16), p.asf, p.arow_scale };
-    act_planes_kernel<<<rows, 256, 0, st>>>(act, p.groups.perm, p.ids, p.groups.offsets, p.groups.cost + 3 * (n_as + 1), rows, k, n_ids, ne11, n_as, po);
+    const int * tiles = p.groups.cost + 3 * (n_as + 1);
+    if (src) act_planes_kernel<true><<<rows, 256, 0, st>>>(act, src, k, p.groups.perm, ids, p.groups.offsets, tiles, p.groups.meta, rows, k, n_ids, ne11, n_as, po);
+    else act_planes_kernel<false><<<rows, 256, 0, st>>>(act, nullptr, 0, p.groups.perm, ids, p.groups.offsets, tiles, p.groups.meta, rows, k, n_ids, ne11, n_as, po);
     return check_launch(ctx, "act_planes");
+}
+
+Fp4Params fp4_params(b200moe_ctx * ctx, const float * s0, const float * s1, float * out, int n_out, int n_as) {
+    Plan & p = ctx->plan;
+    Fp4Params f{};
+    f.scale0 = s0; f.scale1 = s1; f.sf = p.asf; f.row_scale = p.arow_scale; f.offsets = p.groups.offsets; f.perm = p.groups.perm;
+    f.active = p.groups.active; f.meta = p.groups.meta; f.tile_of_expert = p.groups.cost + 3 * (n_as + 1); f.out = out; f.n_out = n_out;
+    f.n_as = n_as; f.err = ctx->d_err; f.prof = nullptr;
+    return f;
 }
 
 bool mma_supported(int wtype, int k, int n_out) {
@@ -516,7 +564,7 @@ int launch_sorted_act(b200moe_ctx * ctx, ActQuant act, int rows, int k, int n_id
     Plan & p = ctx->plan;
     const int64_t warps = (int64_t) rows * (k / 32);
     __half * lo = interleaved ? p.afp16 + k : p.afp16 + (size_t) rows * k;
-    launch_k(ctx, sorted_act_fp16_kernel, dim3((unsigned) ((warps * 32 + 255) / 256)), dim3(256), 0, st, act, p.groups.perm, rows, k, n_ids, ne11,
+    launch_k(ctx, sorted_act_fp16_kernel, dim3((unsigned) ((warps * 32 + 255) / 256)), dim3(256), 0, st, act, p.groups.perm, p.groups.meta, rows, k, n_ids, ne11,
              p.afp16, lo, interleaved ? 2 * k : k);
     return check_launch(ctx, "sorted_act_fp16");
 }
@@ -592,10 +640,10 @@ int launch_select(b200moe_ctx * ctx, const b200moe_layer * l, int T, int32_t * i
     return check_launch(ctx, "route_select");
 }
 
-int launch_group(b200moe_ctx * ctx, const int32_t * ids, int E, int rows, cudaStream_t st) {
+int launch_group(b200moe_ctx * ctx, const int32_t * ids, int E, int rows, cudaStream_t st, bool allow_empty = false) {
     Plan & p = ctx->plan;
     const size_t sh = (size_t) (2 * E + 1) * sizeof(int);
-    launch_k(ctx, group_scan_kernel, dim3(1), dim3(1024), sh, st, p.groups, ids, E, rows, ctx->d_err);
+    launch_k(ctx, group_scan_kernel, dim3(1), dim3(1024), sh, st, p.groups, ids, E, rows, ctx->d_err, allow_empty ? 1 : 0);
     return check_launch(ctx, "group_scan");
 }
 
@@ -654,9 +702,23 @@ __global__ void fill_group_ids_kernel(int * ids, int T, int group_size) {
 // Dense quantised matvec y[T][n_out] = W[n_out][k] . x[T][k] on the indexed-matmul kernel: the tokens are cut into up to 32
 // groups that all point at the same matrix (expert stride 0), so a matrix with few rows and many tokens still fills the grid
 // (one group would leave a 1024-row matrix on a fifth of the SMs, walking all tokens in turn).  The matrix is re-read from L2.
+int dense_matmul_fp4(b200moe_ctx * ctx, const void * w, const float * scale, const float * x, int k, int n_out, int T, float * y, cudaStream_t st,
+                     bool exact_requant, ActQuant xq, void * list_room, size_t list_room_bytes);
+
+// The FP4 tensor-core kernel takes a dense product when the type and shape fit, several tokens share the matrix, and the caller
+// has not asked for bit-identical results (expert paths 1, 5 and 7 are the ones documented as bit-identical).
+bool dense_on_fp4(const b200moe_ctx * ctx, int wtype, int k, int n_out, int T) {
+    const int path = ctx->expert_path;
+    return wtype == TYPE_NVFP4 && fp4_width(k) && n_out % 256 == 0 && T >= 4 && path != 1 && path != 5 && path != 7;
+}
+
+// exact_requant: see dense_matmul_fp4; `hidden` scratch holds the list (free before the experts run)
 int dense_matvec(b200moe_ctx * ctx, int wtype, const void * w, const float * scale, const float * x, ActQuant xq, int k, int n_out, int T,
-                 float * y, cudaStream_t st) {
+                 float * y, cudaStream_t st, bool exact_requant = false) {
     Plan & p = ctx->plan;
+    struct DenseMark { b200moe_ctx * c; DenseMark(b200moe_ctx * c_) : c(c_) { c->dense_now = true; } ~DenseMark() { c->dense_now = false; } } mark(ctx);
+    if (dense_on_fp4(ctx, wtype, k, n_out, T) && (!exact_requant || n_out % 32 == 0))
+        return dense_matmul_fp4(ctx, w, scale, x, k, n_out, T, y, st, exact_requant, xq, p.hid, (size_t) p.max_tokens * p.k * p.n_ff * sizeof(float));
     int rc = launch_quantize<float>(ctx, x, k, xq, T, k, wtype, st);
     if (rc) return rc;
     const int G = std::max(1, std::min({32, T / 8, p.n_expert}));
@@ -681,6 +743,56 @@ int dense_matvec(b200moe_ctx * ctx, int wtype, const void * w, const float * sca
     return B200MOE_OK;
 }
 
+// The same product on the FP4 tensor-core kernel: the matrix is the single "expert" of a one-group routing, the tokens its routed
+// rows (digit planes made straight from the fp32 activations).  Not bit-identical to the integer kernel: fp32 accumulation order.
+template <int K>
+int launch_fix_single_t(b200moe_ctx * ctx, const FixSingleParams & fp, cudaStream_t st) {
+    requant_fix_single_kernel<K><<<ctx->sm_count * 8, 256, 0, st>>>(fp);
+    return check_launch(ctx, "requant_fix_single");
+}
+
+// exact_requant: the caller re-quantises y (the latent down-projection): the values of y whose Q8_0 rounding the GEMM's error
+// could change are recomputed with the integer kernel's arithmetic (requant_fixup.cuh), so the quantised y is the reference's.
+// The list lives in `list_room`, memory the caller does not need yet.
+int dense_matmul_fp4(b200moe_ctx * ctx, const void * w, const float * scale, const float * x, int k, int n_out, int T, float * y, cudaStream_t st,
+                     bool exact_requant, ActQuant xq, void * list_room, size_t list_room_bytes) {
+    Plan & p = ctx->plan;
+    int rc;
+    fill_group_ids_kernel<<<(T + 255) / 256, 256, 0, st>>>(p.one_group_ids, T, T);
+    if ((rc = check_launch(ctx, "fill_group_ids"))) return rc;
+    CUDA_TRY(ctx, cudaMemsetAsync(p.groups.counts, 0, sizeof(int) * 8, st));
+    count_ids_kernel<<<(T + 255) / 256, 256, 0, st>>>(p.one_group_ids, 1, 1, T, 1, p.groups.perm /*scratch: compact ids*/, p.groups.counts, p.groups.pos, ctx->d_err);
+    if ((rc = check_launch(ctx, "count_ids"))) return rc;
+    if ((rc = launch_group(ctx, p.one_group_ids, 1, T, st))) return rc;
+    if (exact_requant) {
+        if ((rc = launch_quantize<float>(ctx, x, k, xq, T, k, TYPE_NVFP4, st))) return rc;
+        if ((rc = launch_act_planes(ctx, xq, nullptr, p.one_group_ids, T, k, 1, 1, 1, st))) return rc;
+    } else {
+        if ((rc = launch_act_planes(ctx, ActQuant{}, x, p.one_group_ids, T, k, 1, 1, 1, st))) return rc;
+    }
+    if ((rc = launch_gemm_fp4<false>(ctx, k, fp4_params(ctx, scale, nullptr, y, n_out, 1), w, nullptr, reinterpret_cast<const uint8_t *>(p.afp16), T, st))) return rc;
+    if (!exact_requant) return B200MOE_OK;
+    FixList list;
+    list.items = static_cast<int2 *>(list_room);
+    list.count = p.groups.meta + 2;
+    list.capacity = (int) std::min<size_t>(list_room_bytes / sizeof(int2), (size_t) T * n_out / 4);
+    list.overflow = reinterpret_cast<unsigned long long *>(ctx->d_err + 2);
+    CUDA_TRY(ctx, cudaMemsetAsync(list.count, 0, sizeof(int), st));
+    const int64_t warps = (int64_t) T * (n_out / 32);
+    requant_mark_kernel<<<(unsigned) ((warps * 32 + 255) / 256), 256, 0, st>>>(y, p.groups.perm, p.groups.meta, T, n_out, FIX_STEP_MARGIN_FP4, FIX_REL_MARGIN_FP4, list);
+    if ((rc = check_launch(ctx, "requant_mark"))) return rc;
+    FixSingleParams fs{ static_cast<const uint8_t *>(w), scale, xq, n_out, y, list };
+    switch (k) {
+        case 256: return launch_fix_single_t<256>(ctx, fs, st);
+        case 512: return launch_fix_single_t<512>(ctx, fs, st);
+        case 768: return launch_fix_single_t<768>(ctx, fs, st);
+        case 1024: return launch_fix_single_t<1024>(ctx, fs, st);
+        case 2048: return launch_fix_single_t<2048>(ctx, fs, st);
+        case 4096: return launch_fix_single_t<4096>(ctx, fs, st);
+    }
+    return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no re-quantisation fix-up for width %d", k);
+}
+
 __global__ void gather_rows_kernel(const float4 * __restrict__ src, const int * __restrict__ idx, float4 * __restrict__ dst, int n_rows,
                                    int w4, int src_rows) {
     pdl_wait();
@@ -695,8 +807,9 @@ __global__ void gather_rows_kernel(const float4 * __restrict__ src, const int * 
 }
 
 int read_device_error(b200moe_ctx * ctx, cudaStream_t st) {
-    CUDA_TRY(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(ctx, cudaMemcpyAsync(ctx->h_err, ctx->d_err, 16, cudaMemcpyDeviceToHost, st));
     CUDA_TRY(ctx, cudaStreamSynchronize(st));
+    ctx->counters.fixup_overflow = (int64_t) *reinterpret_cast<const unsigned long long *>(ctx->h_err + 2);
     if (*ctx->h_err != 0) {
         const int code = *ctx->h_err;
         cudaMemsetAsync(ctx->d_err, 0, sizeof(int), st);
@@ -718,29 +831,24 @@ int route_impl(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, 
     return B200MOE_OK;
 }
 
-// Exact re-quantisation behind the tensor-core gate/up GEMM (requant_fixup.cuh): list the values of `hidden` whose int8
-// rounding the GEMM's error could change, recompute them with the integer lane chains, patch `hidden`.
-// The list lives in the `down` output buffer, which is not in use yet.
-constexpr float FIX_STEP_MARGIN = 0.015f;  // quantisation steps; largest GEMM error measured: 3.7e-3 steps (p99.99: 1.8e-3)
-constexpr float FIX_REL_MARGIN = 1.2e-4f;  // of the block maximum; largest error measured: 2.9e-5 of it
-
 template <int K>
 int launch_fix_t(b200moe_ctx * ctx, const FixParams & fp, cudaStream_t st) {
     launch_k(ctx, requant_fix_kernel<K>, dim3(ctx->sm_count * 8), dim3(256), 0, st, fp);
     return check_launch(ctx, "requant_fix");
 }
 
-int launch_requant_fixup(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, int rows, int n_in, int n_ids, cudaStream_t st) {
+int launch_requant_fixup(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, int rows, int n_in, int n_ids, bool after_fp4, cudaStream_t st) {
     Plan & p = ctx->plan;
     FixList list;
     list.items = reinterpret_cast<int2 *>(p.y);
     list.count = p.groups.meta + 2;
     const size_t room = (size_t) rows * n_in * sizeof(float) / sizeof(int2);
     list.capacity = (int) std::min<size_t>(room, (size_t) rows * l->n_ff / 4);
+    list.overflow = reinterpret_cast<unsigned long long *>(ctx->d_err + 2);
     CUDA_TRY(ctx, cudaMemsetAsync(list.count, 0, sizeof(int), st));
     const int64_t warps = (int64_t) rows * (l->n_ff / 32);
     launch_k(ctx, requant_mark_kernel, dim3((unsigned) ((warps * 32 + 255) / 256)), dim3(256), 0, st, (const float *) p.hid,
-             (const int *) p.groups.perm, rows, l->n_ff, FIX_STEP_MARGIN, FIX_REL_MARGIN, list);
+             (const int *) p.groups.perm, (const int *) p.groups.meta, rows, l->n_ff, after_fp4 ? FIX_STEP_MARGIN_FP4 : FIX_STEP_MARGIN, after_fp4 ? FIX_REL_MARGIN_FP4 : FIX_REL_MARGIN, list);
     int rc = check_launch(ctx, "requant_mark");
     if (rc) return rc;
     FixParams fp{};
@@ -758,42 +866,50 @@ int launch_requant_fixup(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq
 }
 
 // experts on activations xe [T][n_in] (fp32), routing already grouped in the plan
+// y_direct != null: the per-row results of `down` go there ([rows][n_in]) and the weighted combine is left to the caller
 int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const int32_t * ids, const float * wts, int T, float * out,
-                 const b200moe_observe * ob, cudaStream_t st) {
+                 const b200moe_observe * ob, cudaStream_t st, float * y_direct = nullptr) {
     Plan & p = ctx->plan;
+    float * const y = y_direct ? y_direct : p.y;
     const int n_in = l->n_latent ? l->n_latent : l->n_embd;
     const int k = l->n_expert_used, rows = T * k;
     const int nt = tokens_per_pass(rows, l->n_expert);
     int rc;
-    // Which engine runs which matmul.  The integer kernels reproduce the reference's fp32 summation order and are
-    // bit-identical to the CPU path; their cost grows with the rows an expert receives.  The tensor-core grouped GEMM
-    // (tcgen05, kind::f16; cost per expert independent of its rows up to the tile size) adds ~3e-5 of RMS of its own
-    // accumulation error: after `down` nothing is re-quantised, so there it only costs ~1e-5 on the output; on gate/up it
-    // moves a few values of `hidden` across int8 rounding boundaries of the re-quantisation (output error 2e-3 of RMS at
-    // 64 tokens, 4e-3 at 256, 1.05e-2 at 4096 against the bar of 1e-2), so by default gate/up goes to the tensor
-    // cores only up to 4096 routed rows (512 tokens at top-8).
-    //   path 0 (default): tensor cores for down, and for gate/up up to 4096 routed rows, once experts see several rows each
-    //   path 1: integer everywhere (whole layer bit-identical to the reference)
-    //   path 2: tensor cores wherever the shape allows;  path 3: integer gate/up, tensor-core down at any batch size
+    // Which engine runs which matmul (b200moe_set_expert_path documents the paths).
+    //   integer kernels   reproduce the reference's fp32 summation order: bit-identical to the CPU path; cost grows with the rows an
+    //                     expert receives
+    //   FP4 tensor cores  (tcgen05 kind::mxf4nvf4, expert_gemm_fp4.cuh): NVFP4 rows as they lie in HBM, activations as exact digit
+    //                     planes, 14 routed rows per pass over an expert; error = fp32 accumulation only (~5e-6 of RMS on `hidden`)
+    //   f16 tensor cores  (tcgen05 kind::f16, expert_gemm.cuh): weights dequantised to fp16, activations as fp16 hi + lo, up to 128
+    //                     routed rows per pass (~1.4e-4 of RMS on `hidden`): the prefill engine
+    // After `down` nothing is re-quantised, so a tensor-core `down` only adds its own ~1e-5 to the output.  A tensor-core gate/up
+    // moves a few values of `hidden` across int8 rounding boundaries of the reference's re-quantisation; the exact fix-up
+    // (requant_fixup.cuh) removes those flips where the bar needs it: beyond 4096 routed rows on the f16 engine, and on latent
+    // layers, which re-quantise once more after `down`.
     const bool can_mma = mma_supported(l->wtype, n_in, l->n_ff) && mma_supported(l->wtype, l->n_ff, n_in);
-    const bool many_rows = rows >= 2 * l->n_expert;
-    const int path = ctx->expert_path;
-    // A latent layer re-quantises once more after `down` (the up-projection), which amplifies the GEMM's error a second time
-    // (measured 1.7e-2 of RMS on the 512-expert latent configuration, 2.2e-3 with only `down` on tensor cores): by default
-    // latent layers stay on the integer kernels.
-    // Path 4 / large or latent default: tensor-core gate/up followed by the exact re-quantisation fix-up, which makes the
-    // int8 `hidden` the reference's own again.
-    const bool latent = l->n_latent > 0;
-    const bool dflt = path == 0 && many_rows;
-    // Paths 6 and 7: the block-scaled FP4 tensor-core kernels (weights used as they lie in HBM, activations as exact digit planes).
-    //   6: gate/up and down;   7: gate/up + exact re-quantisation fix-up, integer down (layer bit-identical to the reference)
     const bool can_fp4 = fp4_supported(l->wtype, n_in, l->n_ff);
-    const bool fp4_gu = can_fp4 && (path == 6 || path == 7), fp4_down = can_fp4 && path == 6;
-    if ((path == 6 || path == 7) && !can_fp4) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "the FP4 tensor-core path needs NVFP4 experts with widths that are multiples of 256");
-    const bool mma_down = can_mma && (path == 2 || path == 3 || path == 4 || (dflt && !latent));
-    const bool mma_gu = can_mma && (path == 2 || path == 4 || path == 5 || dflt);
-    const bool fixup = path == 7 || (mma_gu && (path == 4 || path == 5 || (dflt && (rows > 4096 || latent))));
-    const bool small_tiles = rows < 24 * l->n_expert;   // on average fewer than 24 rows per expert
+    const int path = ctx->expert_path;
+    const bool latent = l->n_latent > 0;
+    const bool few_rows = rows < 24 * l->n_expert;          // batched decode: on average fewer than 24 rows per expert
+    bool fp4_gu = false, fp4_down = false, mma_gu = false, mma_down = false, fixup = false;
+    switch (path) {
+        case 0:
+            if (rows <= 16) break;                           // one or two tokens: the small integer kernel, bit-identical
+            if (can_fp4 && few_rows) { fp4_gu = fp4_down = true; fixup = latent; }
+            else if (can_mma && rows >= 2 * l->n_expert) { mma_gu = true; mma_down = !latent; fixup = rows > 4096 || latent; }
+            break;
+        case 1: break;
+        case 2: mma_gu = mma_down = can_mma; break;
+        case 3: mma_down = can_mma; break;
+        case 4: mma_gu = mma_down = fixup = can_mma; break;
+        case 5: mma_gu = fixup = can_mma; break;
+        case 6: fp4_gu = fp4_down = true; break;
+        case 7: fp4_gu = fixup = true; break;
+        case 8: fp4_gu = fp4_down = fixup = true; break;
+    }
+    if ((fp4_gu || fp4_down) && !can_fp4)
+        return fail(ctx, B200MOE_ERR_UNSUPPORTED, "the FP4 tensor-core path needs NVFP4 experts, n_ff a multiple of 128 and n_in a multiple of 256");
+    const bool small_tiles = few_rows;
     auto mp = [&](const void * w0, const void * w1, const float * s0, const float * s1, float * out, int n_out, int m_k) {
         MmaParams m{};
         m.w0 = static_cast<const uint8_t *>(w0); m.w1 = static_cast<const uint8_t *>(w1); m.scale0 = s0; m.scale1 = s1;
@@ -806,16 +922,9 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
     // measured faster (167 us against 182 us at 64 tokens of configuration 2: there the tokens-on-M form is bound by
     // shared-memory traffic, twice the operand tile per stage).
     const bool tm_gu = false, tm_down = small_tiles && n_in % 256 == 0;
-    auto fpp = [&](const float * s0, const float * s1, float * out, int n_out) {
-        Fp4Params f{};
-        f.scale0 = s0; f.scale1 = s1; f.sf = p.asf; f.row_scale = p.arow_scale; f.offsets = p.groups.offsets; f.perm = p.groups.perm;
-        f.active = p.groups.active; f.meta = p.groups.meta; f.tile_of_expert = p.groups.cost + 3 * (l->n_expert + 1); f.out = out; f.n_out = n_out;
-        f.n_as = l->n_expert; f.err = ctx->d_err;
-        return f;
-    };
     if (fp4_gu) {
-        if ((rc = launch_act_planes(ctx, xq, rows, n_in, k, 1, l->n_expert, st))) return rc;
-        if ((rc = launch_gemm_fp4<true>(ctx, n_in, fpp(l->gate_scale, l->up_scale, p.hid, l->n_ff), l->gate, l->up, reinterpret_cast<const uint8_t *>(p.afp16), rows, st))) return rc;
+        if ((rc = launch_act_planes(ctx, xq, nullptr, p.ids, rows, n_in, k, 1, l->n_expert, st))) return rc;
+        if ((rc = launch_gemm_fp4<true>(ctx, n_in, fp4_params(ctx, l->gate_scale, l->up_scale, p.hid, l->n_ff, l->n_expert), l->gate, l->up, reinterpret_cast<const uint8_t *>(p.afp16), rows, st))) return rc;
     } else if (mma_gu) {
         if ((rc = launch_sorted_act(ctx, xq, rows, n_in, k, 1, tm_gu, st))) return rc;
         const MmaParams m = mp(l->gate, l->up, l->gate_scale, l->up_scale, p.hid, l->n_ff, n_in);
@@ -824,29 +933,31 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
         GemvParams gu = gemv_params(ctx, l->gate, l->up, l->gate_scale, l->up_scale, xq, p.hid, l->n_ff, k, 1, l->n_expert);
         if ((rc = launch_gemv<true>(ctx, l->wtype, n_in, gu, nt, st))) return rc;
     }
-    if (fixup && (rc = launch_requant_fixup(ctx, l, xq, rows, n_in, k, st))) return rc;
+    if (fixup && (rc = launch_requant_fixup(ctx, l, xq, rows, n_in, k, fp4_gu, st))) return rc;
     // the integer down kernel quantises `hidden` itself while staging it (NVFP4 / Q8_0); otherwise a separate pass
     const bool fused_quant = !mma_down && !fp4_down && l->wtype == TYPE_NVFP4;
-    if (!fused_quant && (rc = launch_quantize<float>(ctx, p.hid, l->n_ff, p.hq, rows, l->n_ff, l->wtype, st))) return rc;
+    if (!fused_quant && !fp4_down && (rc = launch_quantize<float>(ctx, p.hid, l->n_ff, p.hq, rows, l->n_ff, l->wtype, st))) return rc;
     if (fp4_down) {
-        if ((rc = launch_act_planes(ctx, p.hq, rows, l->n_ff, k, k, l->n_expert, st))) return rc;
-        if ((rc = launch_gemm_fp4<false>(ctx, l->n_ff, fpp(l->down_scale, nullptr, p.y, n_in), l->down, nullptr, reinterpret_cast<const uint8_t *>(p.afp16), rows, st))) return rc;
+        if ((rc = launch_act_planes(ctx, p.hq, p.hid, p.ids, rows, l->n_ff, k, k, l->n_expert, st))) return rc;   // quantises `hidden` itself
+        if ((rc = launch_gemm_fp4<false>(ctx, l->n_ff, fp4_params(ctx, l->down_scale, nullptr, y, n_in, l->n_expert), l->down, nullptr, reinterpret_cast<const uint8_t *>(p.afp16), rows, st))) return rc;
     } else if (mma_down) {
         if ((rc = launch_sorted_act(ctx, p.hq, rows, l->n_ff, k, k, tm_down, st))) return rc;
-        const MmaParams m = mp(l->down, nullptr, l->down_scale, nullptr, p.y, n_in, l->n_ff);
+        const MmaParams m = mp(l->down, nullptr, l->down_scale, nullptr, y, n_in, l->n_ff);
         if ((rc = tm_down ? launch_gemm_tm<false>(ctx, l->n_ff, m, rows, st) : launch_gemm<false>(ctx, l->n_ff, m, rows, small_tiles, st))) return rc;
     } else {
-        GemvParams dn = gemv_params(ctx, l->down, nullptr, l->down_scale, nullptr, p.hq, p.y, n_in, k, k, l->n_expert);
+        GemvParams dn = gemv_params(ctx, l->down, nullptr, l->down_scale, nullptr, p.hq, y, n_in, k, k, l->n_expert);
         if (fused_quant) dn.act_f32 = p.hid;
         if ((rc = launch_gemv<false>(ctx, l->wtype, l->n_ff, dn, nt, st))) return rc;
     }
-    dim3 grid((n_in / 4 + 255) / 256, T);
-    launch_k(ctx, combine_kernel, grid, dim3(256), 0, st, p.y, wts, out, n_in, k, T);
-    if ((rc = check_launch(ctx, "combine"))) return rc;
+    if (!y_direct) {
+        dim3 grid((n_in / 4 + 255) / 256, T);
+        launch_k(ctx, combine_kernel, grid, dim3(256), 0, st, y, wts, out, n_in, k, T);
+        if ((rc = check_launch(ctx, "combine"))) return rc;
+    }
     if (ob && ob->ffn_moe_hidden)
         CUDA_TRY(ctx, cudaMemcpyAsync(ob->ffn_moe_hidden, p.hid, sizeof(float) * (size_t) rows * l->n_ff, cudaMemcpyDeviceToDevice, st));
     if (ob && ob->ffn_moe_down)
-        CUDA_TRY(ctx, cudaMemcpyAsync(ob->ffn_moe_down, p.y, sizeof(float) * (size_t) rows * n_in, cudaMemcpyDeviceToDevice, st));
+        CUDA_TRY(ctx, cudaMemcpyAsync(ob->ffn_moe_down, y, sizeof(float) * (size_t) rows * n_in, cudaMemcpyDeviceToDevice, st));
     (void) ids;
     return B200MOE_OK;
 }
@@ -898,7 +1009,8 @@ int layer_impl(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, 
         if ((rc = check_launch(ctx, "bf16_to_f32"))) return rc;
         xf32 = p.xf;
     }
-    if ((rc = dense_matvec(ctx, l->wtype, l->lat_down, l->lat_down_scale, xf32, p.xq, l->n_embd, l->n_latent, T, p.xl, st))) return rc;
+    // the latent row is re-quantised for the experts: keep its quantised form the reference's (exact fix-up behind the FP4 engine)
+    if ((rc = dense_matvec(ctx, l->wtype, l->lat_down, l->lat_down_scale, xf32, p.xq, l->n_embd, l->n_latent, T, p.xl, st, true))) return rc;
     // regroup the expert routing
     CUDA_TRY(ctx, cudaMemsetAsync(p.groups.counts, 0, sizeof(int) * l->n_expert, st));
     count_ids_kernel<<<(T * k + 255) / 256, 256, 0, st>>>(p.ids, k, k, T, l->n_expert, p.groups.perm, p.groups.counts, p.groups.pos, ctx->d_err);
@@ -943,13 +1055,13 @@ int b200moe_create(int device, b200moe_ctx ** out) {
     auto * ctx = new b200moe_ctx();
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;
-    if (cudaMalloc(&ctx->d_err, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_err, 0, sizeof(int)) != cudaSuccess ||
-        cudaMallocHost(&ctx->h_err, sizeof(int)) != cudaSuccess) {
+    if (cudaMalloc(&ctx->d_err, 16) != cudaSuccess || cudaMemset(ctx->d_err, 0, 16) != cudaSuccess ||
+        cudaMallocHost(&ctx->h_err, 16) != cudaSuccess) {
         cudaGetLastError();
         delete ctx;
         return B200MOE_ERR_ALLOC;
     }
-    *ctx->h_err = 0;
+    memset(ctx->h_err, 0, 16);
     *out = ctx;
     return B200MOE_OK;
 }
@@ -986,7 +1098,7 @@ int b200moe_get_counters(const b200moe_ctx * ctx, b200moe_counters * out) {
 }
 
 int b200moe_set_expert_path(b200moe_ctx * ctx, int path) {
-    if (!ctx || path < 0 || path > 7) return B200MOE_ERR_INVALID_ARG;
+    if (!ctx || path < 0 || path > 8) return B200MOE_ERR_INVALID_ARG;
     ctx->expert_path = path;
     return B200MOE_OK;
 }
@@ -1003,10 +1115,10 @@ int b200moe_enable_kernel_timing(b200moe_ctx * ctx, int enable) {
     return B200MOE_OK;
 }
 
-int b200moe_kernel_times(b200moe_ctx * ctx, int64_t launches[2], double total_ms[2]) {
+int b200moe_kernel_times(b200moe_ctx * ctx, int64_t launches[3], double total_ms[3]) {
     if (!ctx || !launches || !total_ms) return B200MOE_ERR_INVALID_ARG;
-    launches[0] = launches[1] = 0;
-    total_ms[0] = total_ms[1] = 0.0;
+    launches[0] = launches[1] = launches[2] = 0;
+    total_ms[0] = total_ms[1] = total_ms[2] = 0.0;
     for (auto & t : ctx->timed) {
         float ms = 0.0f;
         CUDA_TRY(ctx, cudaEventSynchronize(t.end));
@@ -1095,145 +1207,6 @@ int b200moe_quantize_nvfp4_host(const float * src, void * dst, int64_t nrows, in
         th.emplace_back([=] {
             for (int64_t r = nrows * t / nthreads; r < nrows * (t + 1) / nthreads; ++r)
                 quantize_row_nvfp4(src + r * n_per_row, static_cast<uint8_t *>(dst) + r * rs, n_per_row);
-        });
-    for (auto & t : th) t.join();
-    return B200MOE_OK;
-}
-
-// ---- Q3_K weight quantiser: the algorithm of quantize_row_q3_K_ref (ggml-quants.c:1229-1303) with its helper
-// make_q3_quants (ggml-quants.c:697-754).  Per 16 values: a scale from an iterative weighted least-squares fit of codes in
-// [-4,3]; the 16 scales of a super-block are then quantised to 6 bits against the largest one and the codes re-derived.
-static inline int q3_nearest_int(float f) {
-    float v = f + 12582912.f;
-    int i;
-    memcpy(&i, &v, 4);
-    return (i & 0x007fffff) - 0x00400000;
-}
-
-static float q3_fit_scale16(const float * x, int8_t * L) {
-    const int n = 16, nmax = 4;
-    float max = 0, amax = 0;
-    for (int i = 0; i < n; ++i) { const float ax = std::fabs(x[i]); if (ax > amax) { amax = ax; max = x[i]; } }
-    if (amax < 1e-15f) { for (int i = 0; i < n; ++i) L[i] = 0; return 0.f; }
-    const float iscale = -nmax / max;
-    float sumlx = 0, suml2 = 0;
-    for (int i = 0; i < n; ++i) {
-        int l = q3_nearest_int(iscale * x[i]);
-        l = std::max(-nmax, std::min(nmax - 1, l));
-        L[i] = (int8_t) l;
-        const float w = x[i] * x[i];
-        sumlx += w * x[i] * l;
-        suml2 += w * l * l;
-    }
-    for (int itry = 0; itry < 5; ++itry) {
-        int changed = 0;
-        for (int i = 0; i < n; ++i) {
-            const float w = x[i] * x[i];
-            float slx = sumlx - w * x[i] * L[i];
-            if (slx > 0) {
-                float sl2 = suml2 - w * L[i] * L[i];
-                int nl = q3_nearest_int(x[i] * sl2 / slx);
-                nl = std::max(-nmax, std::min(nmax - 1, nl));
-                if (nl != L[i]) {
-                    slx += w * x[i] * nl;
-                    sl2 += w * nl * nl;
-                    if (sl2 > 0 && slx * slx * suml2 > sumlx * sumlx * sl2) { L[i] = (int8_t) nl; sumlx = slx; suml2 = sl2; ++changed; }
-                }
-            }
-        }
-        if (!changed) break;
-    }
-    for (int i = 0; i < n; ++i) L[i] += nmax;
-    return suml2 > 0.0f ? sumlx / suml2 : 0.0f;
-}
-
-static uint16_t f32_to_f16_rne(float f) {
-    uint32_t u;
-    memcpy(&u, &f, 4);
-    const uint16_t sign = (uint16_t) ((u >> 16) & 0x8000u);
-    const uint32_t a = u & 0x7fffffffu;
-    if (a >= 0x7f800000u) return (uint16_t) (sign | 0x7c00u | (a > 0x7f800000u ? 0x200u : 0));
-    if (a >= 0x477ff000u) return (uint16_t) (sign | 0x7c00u);
-    if (a < 0x33000001u) return sign;
-    const int exp = (int) (a >> 23) - 127;
-    uint32_t man = (a & 0x7fffffu) | 0x800000u, base;
-    int shift;
-    if (exp < -14) { shift = 13 + (-14 - exp); base = 0; } else { shift = 13; base = (uint32_t) (exp + 15) << 10; man &= 0x7fffffu; }
-    uint32_t q = man >> shift;
-    const uint32_t rem = man & ((1u << shift) - 1), half = 1u << (shift - 1);
-    if (rem > half || (rem == half && (q & 1))) q++;
-    return (uint16_t) (sign | (base + q));
-}
-
-static float f16_to_f32(uint16_t hb) {
-    const uint32_t sign = (uint32_t) (hb & 0x8000) << 16, ex = (hb >> 10) & 31, mn = hb & 1023;
-    float d;
-    if (ex == 0) d = std::ldexp((float) mn, -24);
-    else if (ex == 31) d = INFINITY;
-    else { uint32_t u = ((ex + 112) << 23) | (mn << 13); memcpy(&d, &u, 4); }
-    return sign ? -d : d;
-}
-
-static void quantize_row_q3_K(const float * x, uint8_t * y, int64_t k) {
-    int8_t L[256];
-    float scales[16];
-    for (int64_t b = 0; b < k / 256; ++b, x += 256) {
-        uint8_t * blk = y + b * 110;
-        uint8_t * hmask = blk, * qs = blk + 32, * sc12 = blk + 96;
-        float max_scale = 0, amax = 0;
-        for (int j = 0; j < 16; ++j) {
-            scales[j] = q3_fit_scale16(x + 16 * j, L + 16 * j);
-            const float sc = std::fabs(scales[j]);
-            if (sc > amax) { amax = sc; max_scale = scales[j]; }
-        }
-        memset(sc12, 0, 12);
-        uint16_t dh = 0;
-        if (max_scale) {
-            const float iscale = -32.f / max_scale;
-            for (int j = 0; j < 16; ++j) {
-                int8_t l = (int8_t) q3_nearest_int(iscale * scales[j]);
-                l = (int8_t) (std::max(-32, std::min(31, (int) l)) + 32);
-                if (j < 8) sc12[j] = l & 0xF; else sc12[j - 8] |= ((l & 0xF) << 4);
-                l >>= 4;
-                sc12[j % 4 + 8] |= (l << (2 * (j / 4)));
-            }
-            dh = f32_to_f16_rne(1 / iscale);
-        }
-        memcpy(blk + 108, &dh, 2);
-        const float dd = f16_to_f32(dh);
-        for (int j = 0; j < 16; ++j) {
-            int sc = j < 8 ? sc12[j] & 0xF : sc12[j - 8] >> 4;
-            sc = (sc | (((sc12[8 + j % 4] >> (2 * (j / 4))) & 3) << 4)) - 32;
-            const float d = dd * sc;
-            if (!d) continue;
-            for (int ii = 0; ii < 16; ++ii) {
-                int l = q3_nearest_int(x[16 * j + ii] / d);
-                l = std::max(-4, std::min(3, l));
-                L[16 * j + ii] = (int8_t) (l + 4);
-            }
-        }
-        memset(hmask, 0, 32);
-        int m = 0;
-        uint8_t hm = 1;
-        for (int j = 0; j < 256; ++j) {
-            if (L[j] > 3) { hmask[m] |= hm; L[j] -= 4; }
-            if (++m == 32) { m = 0; hm <<= 1; }
-        }
-        for (int j = 0; j < 256; j += 128)
-            for (int l = 0; l < 32; ++l) qs[j / 4 + l] = (uint8_t) (L[j + l] | (L[j + l + 32] << 2) | (L[j + l + 64] << 4) | (L[j + l + 96] << 6));
-    }
-}
-
-int b200moe_quantize_q3_K_host(const float * src, void * dst, int64_t nrows, int64_t n_per_row) {
-    if (!src || !dst || nrows < 0 || n_per_row <= 0 || n_per_row % 256) return B200MOE_ERR_INVALID_ARG;
-    const int64_t rs = n_per_row / 256 * 110;
-    const unsigned hw = std::max(1u, std::thread::hardware_concurrency());
-    const int nthreads = (int) std::min<int64_t>(hw, std::max<int64_t>(1, nrows / 16));
-    std::vector<std::thread> th;
-    for (int t = 0; t < nthreads; ++t)
-        th.emplace_back([=] {
-            for (int64_t r = nrows * t / nthreads; r < nrows * (t + 1) / nthreads; ++r)
-                quantize_row_q3_K(src + r * n_per_row, static_cast<uint8_t *>(dst) + r * rs, n_per_row);
         });
     for (auto & t : th) t.join();
     return B200MOE_OK;
@@ -1350,6 +1323,44 @@ int b200moe_mul_mat(b200moe_ctx * ctx, int wtype, const void * w, int64_t ne00, 
     return dense_matvec(ctx, wtype, w, scale, x, ctx->plan.xq, (int) ne00, (int) ne01, (int) T, dst, st);
 }
 
+// The two shared projections of a latent layer as calls of their own (the expert-parallel layer runs them on the token's rank).
+int b200moe_latent_down(b200moe_ctx * ctx, const b200moe_layer * l, const void * x, int x_type, int32_t T, float * xl, void * stream) {
+    int rc = validate_layer(ctx, l, false, false);
+    if (rc) return rc;
+    if (!l->n_latent || !l->lat_down) return fail(ctx, B200MOE_ERR_INVALID_ARG, "layer has no latent down-projection");
+    if (T == 0) return B200MOE_OK;
+    if (!x || !xl || T < 0) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer or negative token count");
+    if (x_type != TYPE_F32 && x_type != TYPE_BF16) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "activations must be F32 or BF16");
+    if ((uintptr_t) l->lat_down & 15) return fail(ctx, B200MOE_ERR_INVALID_ARG, "quantised tensors must be 16-byte aligned");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    ctx->overlap_now = false;
+    if ((rc = ensure_plan(ctx, l->n_embd, l->n_latent, l->n_expert, l->n_expert_used, l->n_ff, l->wtype, T))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    Plan & p = ctx->plan;
+    const float * xf32 = static_cast<const float *>(x);
+    if (x_type == TYPE_BF16) {
+        const size_t n = (size_t) T * l->n_embd;
+        bf16_to_f32_kernel<<<(unsigned) ((n + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), p.xf, n);
+        if ((rc = check_launch(ctx, "bf16_to_f32"))) return rc;
+        xf32 = p.xf;
+    }
+    // the caller re-quantises the latent rows for the experts: their quantised form stays the reference's
+    return dense_matvec(ctx, l->wtype, l->lat_down, l->lat_down_scale, xf32, p.xq, l->n_embd, l->n_latent, T, xl, st, true);
+}
+
+int b200moe_latent_up(b200moe_ctx * ctx, const b200moe_layer * l, const float * m, int32_t T, float * out, void * stream) {
+    int rc = validate_layer(ctx, l, false, false);
+    if (rc) return rc;
+    if (!l->n_latent || !l->lat_up) return fail(ctx, B200MOE_ERR_INVALID_ARG, "layer has no latent up-projection");
+    if (T == 0) return B200MOE_OK;
+    if (!m || !out || T < 0) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer or negative token count");
+    if ((uintptr_t) l->lat_up & 15) return fail(ctx, B200MOE_ERR_INVALID_ARG, "quantised tensors must be 16-byte aligned");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    ctx->overlap_now = false;
+    if ((rc = ensure_plan(ctx, l->n_embd, l->n_latent, l->n_expert, l->n_expert_used, l->n_ff, l->wtype, T))) return rc;
+    return dense_matvec(ctx, l->wtype, l->lat_up, l->lat_up_scale, m, ctx->plan.moq, l->n_latent, l->n_embd, T, out, static_cast<cudaStream_t>(stream));
+}
+
 int b200moe_combine(b200moe_ctx * ctx, const float * y, const float * weights, float * out, int64_t n, int64_t k, int64_t T, void * stream) {
     if (ctx) ctx->overlap_now = false;
     if (!ctx) return B200MOE_ERR_INVALID_ARG;
@@ -1438,6 +1449,134 @@ int b200moe_layer_forward_host(b200moe_ctx * ctx, const b200moe_layer * l, const
     if (ids_host) CUDA_TRY(ctx, cudaMemcpyAsync(ids_host, p.ids, sizeof(int32_t) * (size_t) T * l->n_expert_used, cudaMemcpyDeviceToHost, st));
     if (weights_host) CUDA_TRY(ctx, cudaMemcpyAsync(weights_host, p.wts, sizeof(float) * (size_t) T * l->n_expert_used, cudaMemcpyDeviceToHost, st));
     return read_device_error(ctx, st);
+}
+
+// ---- expert-parallel exchange (expert_exchange.cuh) ---------------------------------------------------------------------
+
+int64_t b200moe_ep_slot_bytes(int64_t width) { return width > 0 && width % 4 == 0 ? (width + EP_SLOT_EXTRA) * 4 : -1; }
+
+int b200moe_ep_pack(b200moe_ctx * ctx, const float * rows, const int32_t * ids, int64_t T, int64_t k, int64_t width, int64_t n_ranks,
+                    int64_t experts_per_rank, int64_t capacity, void * slots, int32_t * slot_of, int32_t * fill, void * stream) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    if (!slots || !fill || T < 0 || k <= 0 || width <= 0 || width % 4 || n_ranks <= 0 || experts_per_rank <= 0 || capacity <= 0)
+        return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer or bad size");
+    if (T > 0 && (!rows || !ids || !slot_of)) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer");
+    if (T * k > capacity * n_ranks || n_ranks * capacity > (1 << 30)) return fail(ctx, B200MOE_ERR_INVALID_ARG, "capacity below the routed rows of this rank");
+    if ((uintptr_t) rows & 15 || (uintptr_t) slots & 15) return fail(ctx, B200MOE_ERR_INVALID_ARG, "rows and slots must be 16-byte aligned");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int n_slots = (int) (n_ranks * capacity);
+    ep_clear_kernel<<<(std::max<int>(n_slots, (int) n_ranks) + 255) / 256, 256, 0, st>>>(static_cast<float *>(slots), n_slots, (int) width + EP_SLOT_EXTRA,
+                                                                                       (int) width, fill, (int) n_ranks);
+    int rc = check_launch(ctx, "ep_clear");
+    if (rc || T == 0) return rc;
+    ep_pack_kernel<<<(unsigned) (T * k), 256, 0, st>>>(rows, ids, (int) (T * k), (int) k, (int) width, (int) n_ranks, (int) experts_per_rank, (int) capacity,
+                                                      static_cast<float *>(slots), slot_of, fill, ctx->d_err);
+    return check_launch(ctx, "ep_pack");
+}
+
+int b200moe_ep_expert_rows(b200moe_ctx * ctx, const b200moe_layer * l, const void * slots, int64_t n_slots, float * y, void * stream) {
+    int rc = validate_layer(ctx, l, false, true);
+    if (rc) return rc;
+    if (l->n_latent) return fail(ctx, B200MOE_ERR_INVALID_ARG, "the owner's layer is the plain expert layer of the exchanged width");
+    if (n_slots == 0) return B200MOE_OK;
+    if (!slots || !y || n_slots < 0 || n_slots > (1 << 30)) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer or bad slot count");
+    if ((uintptr_t) slots & 15) return fail(ctx, B200MOE_ERR_INVALID_ARG, "slots must be 16-byte aligned");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    ctx->overlap_now = false;
+    const int n_in = l->n_embd, R = (int) n_slots, slot_words = n_in + EP_SLOT_EXTRA;
+    // one slot = one routed row of a one-slot layer
+    if ((rc = ensure_plan(ctx, l->n_embd, n_in, l->n_expert, 1, l->n_ff, l->wtype, R))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    Plan & p = ctx->plan;
+    const float * rows = static_cast<const float *>(slots);
+    const int32_t * ids = reinterpret_cast<const int32_t *>(rows + n_in);
+    CUDA_TRY(ctx, cudaMemsetAsync(p.groups.counts, 0, sizeof(int) * l->n_expert, st));
+    count_ids_kernel<<<(R + 255) / 256, 256, 0, st>>>(ids, slot_words, 1, R, l->n_expert, p.ids, p.groups.counts, p.groups.pos, ctx->d_err, 1);
+    if ((rc = check_launch(ctx, "count_ids"))) return rc;
+    if ((rc = launch_group(ctx, p.ids, l->n_expert, R, st, true))) return rc;
+    if ((rc = launch_quantize<float>(ctx, rows, slot_words, p.xq, R, n_in, l->wtype, st))) return rc;   // empty slots hold garbage nobody reads
+    rc = experts_impl(ctx, l, p.xq, p.ids, nullptr, R, nullptr, nullptr, st, y);
+    account(ctx, l, 0);
+    return rc;
+}
+
+int b200moe_ep_combine(b200moe_ctx * ctx, const float * back, int64_t n_slots, const int32_t * slot_of, const float * weights, int64_t T, int64_t k,
+                       int64_t width, float * out, void * stream) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    if (T == 0) return B200MOE_OK;
+    if (!back || !slot_of || !weights || !out || T < 0 || k <= 0 || width <= 0 || width % 4 || n_slots <= 0)
+        return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer, bad size or width not a multiple of 4");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    dim3 grid((unsigned) ((width / 4 + 255) / 256), (unsigned) T);
+    ep_combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(back, slot_of, weights, out, (int) width, (int) k, (int) T, (int) n_slots);
+    return check_launch(ctx, "ep_combine");
+}
+
+// ---- probe of the block-scaled FP4 instruction (fp4_probe.cuh) -----------------------------------------------------------
+
+int b200moe_probe_fp4_tile(int device, const uint8_t * a_codes, const uint8_t * b_codes, const uint8_t * sfa, const uint8_t * sfb, float * d_host) {
+    if (!a_codes || !b_codes || !sfa || !sfb || !d_host) return B200MOE_ERR_INVALID_ARG;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) { cudaGetLastError(); return B200MOE_ERR_NO_DEVICE; }
+    if (device < 0 || device >= n || cudaSetDevice(device) != cudaSuccess) { cudaGetLastError(); return B200MOE_ERR_INVALID_ARG; }
+    std::vector<uint8_t> tiles(PROBE_TILE_BYTES);
+    fp4_probe_pack(a_codes, b_codes, sfa, sfb, tiles.data());
+    uint8_t * d_tiles = nullptr;
+    float * d_out = nullptr;
+    int * d_err = nullptr;
+    int rc = B200MOE_OK, herr = 0;
+    if (cudaMalloc(&d_tiles, PROBE_TILE_BYTES) != cudaSuccess || cudaMalloc(&d_out, sizeof(float) * 128 * PROBE_NB) != cudaSuccess ||
+        cudaMalloc(&d_err, sizeof(int)) != cudaSuccess) rc = B200MOE_ERR_ALLOC;
+    if (!rc && (cudaMemcpy(d_tiles, tiles.data(), PROBE_TILE_BYTES, cudaMemcpyHostToDevice) != cudaSuccess || cudaMemset(d_err, 0, sizeof(int)) != cudaSuccess ||
+                cudaFuncSetAttribute(fp4_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PROBE_SMEM) != cudaSuccess)) rc = B200MOE_ERR_CUDA;
+    if (!rc) {
+        fp4_probe_kernel<<<1, 128, PROBE_SMEM>>>(d_tiles, d_out, 0, PROBE_NB, 1, d_err);
+        if (cudaDeviceSynchronize() != cudaSuccess || cudaMemcpy(d_host, d_out, sizeof(float) * 128 * PROBE_NB, cudaMemcpyDeviceToHost) != cudaSuccess ||
+            cudaMemcpy(&herr, d_err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) rc = B200MOE_ERR_CUDA;
+        else if (herr) rc = B200MOE_ERR_DEVICE_CHECK;
+    }
+    cudaGetLastError();
+    cudaFree(d_tiles); cudaFree(d_out); cudaFree(d_err);
+    return rc;
+}
+
+int b200moe_probe_fp4_rate(int device, int n_mma, int n_acc, int rounds, double * tflops) {
+    if (!tflops || n_mma < 8 || n_mma > 256 || n_mma % 8 || n_acc < 1 || n_acc * n_mma + 48 > 512 || rounds < 1 || rounds > (1 << 22)) return B200MOE_ERR_INVALID_ARG;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) { cudaGetLastError(); return B200MOE_ERR_NO_DEVICE; }
+    if (device < 0 || device >= n || cudaSetDevice(device) != cudaSuccess) { cudaGetLastError(); return B200MOE_ERR_INVALID_ARG; }
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { cudaGetLastError(); return B200MOE_ERR_CUDA; }
+    if (prop.major != 10) return B200MOE_ERR_UNSUPPORTED;
+    // arbitrary operands: ones with unit scales (the rate does not depend on the values)
+    std::vector<uint8_t> a(128 * 256, 2), b(PROBE_NB * 256, 2), sfa(128 * 16, 0x38), sfb(PROBE_NB * 16, 0x38), tiles(PROBE_TILE_BYTES);
+    fp4_probe_pack(a.data(), b.data(), sfa.data(), sfb.data(), tiles.data());
+    uint8_t * d_tiles = nullptr;
+    int * d_err = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    int rc = B200MOE_OK, herr = 0;
+    if (cudaMalloc(&d_tiles, PROBE_TILE_BYTES) != cudaSuccess || cudaMalloc(&d_err, sizeof(int)) != cudaSuccess) rc = B200MOE_ERR_ALLOC;
+    if (!rc && (cudaMemcpy(d_tiles, tiles.data(), PROBE_TILE_BYTES, cudaMemcpyHostToDevice) != cudaSuccess || cudaMemset(d_err, 0, sizeof(int)) != cudaSuccess ||
+                cudaFuncSetAttribute(fp4_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PROBE_SMEM) != cudaSuccess ||
+                cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess)) rc = B200MOE_ERR_CUDA;
+    if (!rc) {
+        const int sms = prop.multiProcessorCount;
+        fp4_probe_kernel<<<sms, 128, PROBE_SMEM>>>(d_tiles, nullptr, std::max(1, rounds / 50), n_mma, n_acc, d_err);   // warm-up
+        cudaEventRecord(e0);
+        fp4_probe_kernel<<<sms, 128, PROBE_SMEM>>>(d_tiles, nullptr, rounds, n_mma, n_acc, d_err);
+        cudaEventRecord(e1);
+        float ms = 0.0f;
+        if (cudaDeviceSynchronize() != cudaSuccess || cudaEventElapsedTime(&ms, e0, e1) != cudaSuccess ||
+            cudaMemcpy(&herr, d_err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) rc = B200MOE_ERR_CUDA;
+        else if (herr) rc = B200MOE_ERR_DEVICE_CHECK;
+        else *tflops = 2.0 * 128 * n_mma * 64 * 4.0 * n_acc * (double) rounds * sms / (ms * 1e-3) / 1e12;
+    }
+    cudaGetLastError();
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    cudaFree(d_tiles); cudaFree(d_err);
+    return rc;
 }
 
 // ---- routing with no allocation at all -----------------------------------------------------------------

@@ -16,8 +16,8 @@
 // is exact (blocks more than 17 binades below the row's largest flush to zero: a relative 2^-17 of the row's unit), every
 // product inside the tensor core is exact, and the result differs from the integer path only by fp32 accumulation.
 //
-// Operand roles: D[feature, plane] = W[feature, k] * P[plane, k].  M = 128 weight rows, N = 7 planes x up to 16 routed rows
-// (N = 8 .. 112), K = 64 per instruction.  The seven plane columns of a routed row sit next to each other in one lane of tensor
+// Operand roles: D[feature, plane] = W[feature, k] * P[plane, k].  M = 128 weight rows, N = 7 planes x up to 14 routed rows
+// (N = 8 .. 104), K = 64 per instruction.  The seven plane columns of a routed row sit next to each other in one lane of tensor
 // memory, so the epilogue recombines them with a Horner chain in registers and stores 32 consecutive features per warp.
 // Two weight tiles are in flight per stage with an accumulator each (gate and up rows of the same 128 features, or two
 // consecutive 128-row tiles of `down`): dependent MMAs on one accumulator issue every ~190-230 cycles, MMAs that alternate
@@ -25,7 +25,8 @@
 //
 // Roles (every wait bounded, as in expert_gemm.cuh):
 //   warp 0      raw-weight producer: tiled TMA of [128 rows][144 bytes] boxes (K = 256 per row) of both tiles
-//   warp 1      activation producer: one tiled TMA box [112 plane rows][128 bytes] + one bulk copy of the 2 KB scale tile
+//   warp 1      activation producer: one tiled TMA box [98 plane rows][128 bytes] + one bulk copy of the 2 KB scale tile, into a
+//               ring of its own that runs three stages ahead (the planes come from L2 with about a microsecond of latency)
 //   warp 2      MMA issuer: per K = 64 step three tcgen05.cp (scales of tile 0, tile 1, planes) and two tcgen05.mma
 //   warp 3      owns tensor memory
 //   warps 4-7   epilogue
@@ -41,8 +42,9 @@
 namespace b200moe {
 
 constexpr int FP4_PLANES = 7;
-constexpr int FP4_RPT = 16;                       // routed rows per token tile
-constexpr int FP4_NCOL = FP4_PLANES * FP4_RPT;    // 112 accumulator columns per weight tile
+constexpr int FP4_RPT = TOKEN_TILE_ROWS;          // 14 routed rows per token tile
+constexpr int FP4_NROW = FP4_PLANES * FP4_RPT;    // 98 plane rows per token tile
+constexpr int FP4_NCOL = 104;                     // accumulator columns per weight tile: N of the instruction is a multiple of 8
 constexpr int FP4_SF_TILE = 4 * 512;              // scale factors of 128 rows for the four K = 64 steps of a stage
 constexpr int FP4_THREADS = 512;
 
@@ -87,7 +89,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 // ---- activation planes ---------------------------------------------------------------------------------------------------
 // Expert-sorted routed row i -> seven plane rows 7i .. 7i+6 of `planes` (K/2 bytes each, ggml nibble order inside every
 // 16-block), its scale bytes in the scale tiles of its token tile, and the power of two the epilogue multiplies with.
-//   tile_of_expert[e]: index of expert e's first token tile (prefix of ceil(rows_e / 16))
+//   tile_of_expert[e]: index of expert e's first token tile (prefix of ceil(rows_e / 14))
 //   sf tiles: [tile][K / 256][4 steps][512 bytes], byte for (plane row n of the tile, 16-block g of the step) at sf_tile_offset(n) + g
 struct PlaneOut {
     uint8_t * planes;       // [rows * 7][K / 2]
@@ -95,13 +97,49 @@ struct PlaneOut {
     float *   row_scale;    // [rows] by sorted position
 };
 
-__global__ void __launch_bounds__(256) act_planes_kernel(ActQuant act, const int * __restrict__ perm, const int32_t * __restrict__ ids,
-                                                        const int * __restrict__ offsets, const int * __restrict__ tile_of_expert, int rows,
-                                                        int K, int n_ids, int ne11, int n_as, PlaneOut out) {
+// digits, codes and scale bytes of one item: 16-block g, byte j (elements 16g + j and 16g + j + 8) with int8 values q0, q1 and
+// the fp32 bits of the block scale d (an fp16 number: d = M * 2^(exp8 - 137) with M the top 11 bits of the significand)
+__device__ __forceinline__ void plane_item(int q0, int q1, uint32_t dbits, int E_row, int it, int K, int in_tile, uint8_t * __restrict__ prow,
+                                           uint8_t * __restrict__ sft) {
+    const int g = it >> 3, j = it & 7;
+    const bool nz = (dbits & 0x7fffffffu) != 0;
+    const int M = nz ? (int) (((dbits & 0x7fffffu) | 0x800000u) >> 13) : 0;
+    const int s = nz ? (int) ((dbits >> 23) & 0xff) - 137 - E_row + 8 : -100;           // scale exponent, at most 8
+    const int Ms = s >= -9 ? M : 0;                                                     // flushed blocks contribute nothing
+    int p0 = q0 * Ms, p1 = q1 * Ms;
+#pragma unroll
+    for (int p = 0; p < FP4_PLANES; ++p) {
+        const int d0 = p < FP4_PLANES - 1 ? ((p0 + 4) & 7) - 4 : p0, d1 = p < FP4_PLANES - 1 ? ((p1 + 4) & 7) - 4 : p1;
+        p0 = (p0 - d0) >> 3;
+        p1 = (p1 - d1) >> 3;
+        // E2M1 codes of 0,1,2,3,4: 0,2,4,5,6; sign in bit 3
+        const uint32_t c0 = ((0x65420u >> (4 * abs(d0))) & 0xfu) | (d0 < 0 ? 8u : 0u);
+        const uint32_t c1 = ((0x65420u >> (4 * abs(d1))) & 0xfu) | (d1 < 0 ? 8u : 0u);
+        prow[(size_t) p * (K / 2) + it] = (uint8_t) (c0 | (c1 << 4));
+    }
+    if (j == 0) {
+        // UE4M3 byte of 2^s: normal for s >= -6, the three power-of-two subnormals below, zero when flushed
+        const uint32_t sb = s >= -6 ? (uint32_t) (s + 7) << 3 : s == -7 ? 4u : s == -8 ? 2u : s == -9 ? 1u : 0u;
+        uint8_t * dst = sft + (size_t) (g >> 4) * FP4_SF_TILE + ((g >> 2) & 3) * 512 + (g & 3);
+#pragma unroll
+        for (int p = 0; p < FP4_PLANES; ++p) dst[sf_tile_offset(in_tile * FP4_PLANES + p)] = (uint8_t) sb;
+    }
+}
+
+// One CTA per expert-sorted routed row.  SRC_F32 = false: the row's activations are already quantised (ActQuant planes, Q8_0).
+// SRC_F32 = true: they are fp32 (`src`, rows `src_stride` floats apart) and are quantised here exactly as quantize_q8_0_block
+// does it (d = half(amax / 127), q = rint(v * (127 / amax))), which saves the separate quantisation pass over `hidden`.
+template <bool SRC_F32>
+__global__ void __launch_bounds__(256) act_planes_kernel(ActQuant act, const float * __restrict__ src, int64_t src_stride,
+                                                        const int * __restrict__ perm, const int32_t * __restrict__ ids,
+                                                        const int * __restrict__ offsets, const int * __restrict__ tile_of_expert,
+                                                        const int * __restrict__ meta, int rows, int K, int n_ids, int ne11, int n_as,
+                                                        PlaneOut out) {
+    constexpr int MAX_ITEMS = 8;                   // K / 2 items over 256 threads, K <= 4096
     __shared__ int s_emax[8];
     __shared__ int s_E;
     const int i = blockIdx.x;                      // sorted position
-    if (i >= rows) return;
+    if (i >= rows || i >= meta[1]) return;         // meta[1]: rows that are in a group (fewer than `rows` when slots are empty)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r = perm[i];
     const int arow = (r / n_ids) * ne11 + (r % n_ids) % ne11;
@@ -111,12 +149,42 @@ __global__ void __launch_bounds__(256) act_planes_kernel(ActQuant act, const int
     const int in_tile = (i - row_beg) % FP4_RPT;
     const int tile = tile_of_expert[e] + (i - row_beg) / FP4_RPT;
     const int nb32 = K / 32;
-    const float * drow = act.d + (size_t) arow * nb32;
-    // largest block exponent of the row: d = M * 2^(exp8 - 137) with M the top 11 bits of the fp32 significand
+    uint8_t * prow = out.planes + (size_t) i * FP4_PLANES * (K / 2);
+    uint8_t * sft = out.sf + (size_t) tile * (K / 256) * FP4_SF_TILE;
+    int q0[MAX_ITEMS], q1[MAX_ITEMS];
+    uint32_t db[MAX_ITEMS];
     int emax = -1000;
-    for (int b = tid; b < nb32; b += 256) {
-        const uint32_t bits = __float_as_uint(drow[b]);
-        if (bits & 0x7fffffffu) emax = max(emax, (int) ((bits >> 23) & 0xff) - 137);
+    if (SRC_F32) {
+        const float * xrow = src + (size_t) arow * src_stride;
+#pragma unroll
+        for (int u = 0; u < MAX_ITEMS; ++u) {
+            const int it = tid + 256 * u;            // the 16 items of a 32-block sit in 16 consecutive lanes
+            const bool in = it < K / 2;
+            const int g = it >> 3, j = it & 7;
+            const float v0 = in ? xrow[16 * g + j] : 0.0f, v1 = in ? xrow[16 * g + j + 8] : 0.0f;
+            float amax = fmaxf(fabsf(v0), fabsf(v1));
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            const float d = __half2float(__float2half_rn(__fdiv_rn(amax, 127.0f)));
+            const float id = amax != 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+            q0[u] = __float2int_rn(__fmul_rn(v0, id));
+            q1[u] = __float2int_rn(__fmul_rn(v1, id));
+            db[u] = in ? __float_as_uint(d) : 0u;
+            if (db[u] & 0x7fffffffu) emax = max(emax, (int) ((db[u] >> 23) & 0xff) - 137);
+        }
+    } else {
+        const float * drow = act.d + (size_t) arow * nb32;
+        const int8_t * qrow = act.q + (size_t) arow * K;
+#pragma unroll
+        for (int u = 0; u < MAX_ITEMS; ++u) {
+            const int it = tid + 256 * u;
+            const bool in = it < K / 2;
+            const int g = it >> 3, j = it & 7;
+            q0[u] = in ? (int) qrow[16 * g + j] : 0;
+            q1[u] = in ? (int) qrow[16 * g + j + 8] : 0;
+            db[u] = in ? __float_as_uint(drow[g >> 1]) : 0u;
+            if (db[u] & 0x7fffffffu) emax = max(emax, (int) ((db[u] >> 23) & 0xff) - 137);
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) emax = max(emax, __shfl_xor_sync(0xffffffffu, emax, o));
@@ -126,41 +194,29 @@ __global__ void __launch_bounds__(256) act_planes_kernel(ActQuant act, const int
         int m = s_emax[0];
         for (int w = 1; w < 8; ++w) m = max(m, s_emax[w]);
         s_E = m;
-        out.row_scale[i] = m > -1000 ? __uint_as_float((uint32_t) (m - 8 + 127) << 23) : 0.0f;   // 2^(E_row - 8); exponents here are far from the fp32 limits
+        out.row_scale[i] = m > -1000 ? __uint_as_float((uint32_t) (m - 8 + 127) << 23) : 0.0f;   // 2^(E_row - 8): far from the fp32 limits
     }
     __syncthreads();
     const int E_row = s_E;
-    const int8_t * qrow = act.q + (size_t) arow * K;
-    uint8_t * prow = out.planes + (size_t) i * FP4_PLANES * (K / 2);
-    uint8_t * sft = out.sf + (size_t) tile * (K / 256) * FP4_SF_TILE;
-    // item = (16-block g, byte j): elements 16g + j and 16g + j + 8
-    for (int it = tid; it < K / 2; it += 256) {
-        const int g = it >> 3, j = it & 7;
-        const uint32_t bits = __float_as_uint(drow[g >> 1]);
-        const bool nz = (bits & 0x7fffffffu) != 0;
-        const int M = nz ? (int) (((bits & 0x7fffffu) | 0x800000u) >> 13) : 0;
-        const int s = nz ? (int) ((bits >> 23) & 0xff) - 137 - E_row + 8 : -100;          // scale exponent, at most 8
-        const int Ms = s >= -9 ? M : 0;                                                   // flushed blocks contribute nothing
-        int p0 = (int) qrow[16 * g + j] * Ms, p1 = (int) qrow[16 * g + j + 8] * Ms;
 #pragma unroll
-        for (int p = 0; p < FP4_PLANES; ++p) {
-            const int d0 = p < FP4_PLANES - 1 ? ((p0 + 4) & 7) - 4 : p0, d1 = p < FP4_PLANES - 1 ? ((p1 + 4) & 7) - 4 : p1;
-            p0 = (p0 - d0) >> 3;
-            p1 = (p1 - d1) >> 3;
-            // E2M1 codes of 0,1,2,3,4: 0,2,4,5,6; sign in bit 3
-            const uint32_t c0 = ((0x65420u >> (4 * abs(d0))) & 0xfu) | (d0 < 0 ? 8u : 0u);
-            const uint32_t c1 = ((0x65420u >> (4 * abs(d1))) & 0xfu) | (d1 < 0 ? 8u : 0u);
-            prow[(size_t) p * (K / 2) + it] = (uint8_t) (c0 | (c1 << 4));
-        }
-        if (j == 0) {
-            // UE4M3 byte of 2^s: normal for s >= -6, the three power-of-two subnormals below, zero when flushed
-            const uint32_t sb = s >= -6 ? (uint32_t) (s + 7) << 3 : s == -7 ? 4u : s == -8 ? 2u : s == -9 ? 1u : 0u;
-            uint8_t * dst = sft + (size_t) (g >> 4) * FP4_SF_TILE + ((g >> 2) & 3) * 512 + (g & 3);
-#pragma unroll
-            for (int p = 0; p < FP4_PLANES; ++p) dst[sf_tile_offset(in_tile * FP4_PLANES + p)] = (uint8_t) sb;
-        }
+    for (int u = 0; u < MAX_ITEMS; ++u) {
+        const int it = tid + 256 * u;
+        if (it < K / 2) plane_item(q0[u], q1[u], db[u], E_row, it, K, in_tile, prow, sft);
     }
 }
+
+// Development builds (-DB200MOE_FP4_PROF) record, per CTA, the cycles each role spends waiting on each of its barriers.
+#ifdef B200MOE_FP4_PROF
+#define FP4_PROF_T0() const long long prof_t0_ = clock64()
+#define FP4_PROF_ADD(slot) prof_[slot] += clock64() - prof_t0_
+#define FP4_PROF_DECL() long long prof_[4] = {0, 0, 0, 0}; const long long prof_beg_ = clock64()
+#define FP4_PROF_STORE(base, n) do { if (p.prof) { for (int i_ = 0; i_ < n; ++i_) p.prof[blockIdx.x * 24 + base + i_] = prof_[i_]; p.prof[blockIdx.x * 24 + base + n] = clock64() - prof_beg_; } } while (0)
+#else
+#define FP4_PROF_T0()
+#define FP4_PROF_ADD(slot)
+#define FP4_PROF_DECL()
+#define FP4_PROF_STORE(base, n)
+#endif
 
 struct Fp4Params {
     const float * scale0;   // per-expert fp32 scale of tile 0's tensor (or null)
@@ -176,21 +232,26 @@ struct Fp4Params {
     int n_out;
     int n_as;
     int * err;
+    long long * prof;       // development builds only
 };
 
 template <int K>
 struct Fp4Cfg {
     static constexpr int A_TILE = 128 * 128;                         // 128 weight rows x 256 K as fp4
-    static constexpr int B_TILE = FP4_NCOL * 128;                    // 112 plane rows
-    static constexpr int STAGE = 2 * A_TILE + 2 * FP4_SF_TILE + B_TILE + FP4_SF_TILE;
+    static constexpr int B_BYTES = FP4_NROW * 128;                   // 98 plane rows arrive per stage
+    static constexpr int B_TILE = 13 * 1024;                         // their room (rows 98..103 of an N = 104 instruction read what lies there: columns nobody uses)
+    static constexpr int STAGE = 2 * A_TILE + 2 * FP4_SF_TILE;      // repacked weights of both tiles, then their scale tiles
+    static constexpr int ACT_STAGE = B_TILE + FP4_SF_TILE;           // digit planes, then their scale tile
     static constexpr int RAW_STAGE = 256 * GEMM_RAW_ROW;
     static constexpr int RS = 3;
     static constexpr int TS = 2;
-    static constexpr uint32_t TMEM_COLS = 512;                        // 2 buffers x 2 accumulators x 112 columns, then the scale factors
-    static constexpr uint32_t SF_COL = 4 * FP4_NCOL;                  // 448
-    static_assert(STAGE % 1024 == 0, "stages keep the 1024-byte alignment of swizzled tiles");
+    static constexpr int AS = 3;                                      // plane tiles come from L2 with ~1 us latency: fetched three stages ahead
+    static constexpr uint32_t TMEM_COLS = 512;                        // 2 buffers x 2 accumulators x 104 columns, then two sets of scale factors
+    static constexpr uint32_t SF_COL = 4 * FP4_NCOL;                  // 416; 48 columns per set
+    static_assert(TS == 2 && B_TILE >= B_BYTES + 6 * 128, "one scale-factor set per operand stage");
+    static_assert(STAGE % 1024 == 0 && ACT_STAGE % 1024 == 0, "stages keep the 1024-byte alignment of swizzled tiles");
     static_assert(K % GEMM_RAW_K == 0, "K must be a multiple of 256");
-    static constexpr size_t SMEM = (size_t) TS * STAGE + (size_t) RS * RAW_STAGE + 1024;
+    static constexpr size_t SMEM = (size_t) TS * STAGE + (size_t) AS * ACT_STAGE + (size_t) RS * RAW_STAGE + 1024;
 };
 
 // DUAL: tile 0 = gate rows f .. f+127, tile 1 = up rows of the same features; epilogue = SwiGLU; 128 features per item.
@@ -200,21 +261,23 @@ __global__ void __launch_bounds__(FP4_THREADS, 1)
 expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1,
                        const __grid_constant__ CUtensorMap map_planes) {
     using C = Fp4Cfg<K>;
-    constexpr int TS = C::TS, RS = C::RS;
+    constexpr int TS = C::TS, RS = C::RS, AS = C::AS;
     constexpr int KC = K / GEMM_RAW_K;
     constexpr int FEAT = DUAL ? 128 : 256;
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t * tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
-    uint8_t * raws = tiles + (size_t) TS * C::STAGE;
-    __shared__ uint64_t raw_full[RS], raw_empty[RS], tile_full[TS], tile_empty[TS], acc_full[2], acc_empty[2];
+    uint8_t * acts = tiles + (size_t) TS * C::STAGE;
+    uint8_t * raws = acts + (size_t) AS * C::ACT_STAGE;
+    __shared__ uint64_t raw_full[RS], raw_empty[RS], tile_full[TS], tile_empty[TS], act_full[AS], act_empty[AS], acc_full[2], acc_empty[2];
     __shared__ uint32_t s_tmem;
     __shared__ volatile int s_abort;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 8); }
-        for (int i = 0; i < TS; ++i) { mbar_init(&tile_full[i], 256 + 1); mbar_init(&tile_empty[i], 1); }
+        for (int i = 0; i < TS; ++i) { mbar_init(&tile_full[i], 256); mbar_init(&tile_empty[i], 1); }
+        for (int i = 0; i < AS; ++i) { mbar_init(&act_full[i], 1); mbar_init(&act_empty[i], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
         mbar_fence_init();
         s_abort = 0;
@@ -222,6 +285,11 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
     if (warp == 3) {
         tmem_alloc(&s_tmem, C::TMEM_COLS);
         tmem_relinquish();
+    }
+    if (tid == 32) {   // the first use of a tensor map otherwise pays for its fetch
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w0) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w1) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_planes) : "memory");
     }
     tc_fence_before();
     __syncthreads();
@@ -231,13 +299,14 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
     const int n_active = p.meta[0];
     const int f_tiles = p.n_out / FEAT;
     const int n_items = n_active * f_tiles;
-    // stage layout: [A0][A1][SFA0][SFA1][B][SFB]
-    constexpr uint32_t OFF_A1 = C::A_TILE, OFF_SFA = 2 * C::A_TILE, OFF_B = OFF_SFA + 2 * FP4_SF_TILE, OFF_SFB = OFF_B + C::B_TILE;
+    // weight stage: [A0][A1][SFA0][SFA1]; activation stage: [B][SFB]
+    constexpr uint32_t OFF_A1 = C::A_TILE, OFF_SFA = 2 * C::A_TILE, OFF_SFB = C::B_TILE;
 
     if (warp == 0) {
         // ---------------------------------------------------------------- raw weight producer
         if (lane == 0) {
             Ring raw;
+            FP4_PROF_DECL();
             for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
                 const int a = item / f_tiles, ft = item % f_tiles;
                 const int e = p.active[a];
@@ -245,7 +314,9 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
                 const int row0 = e * p.n_out + ft * FEAT;
                 for (int t0 = 0; t0 < n_e && !s_abort; t0 += FP4_RPT) {
                     for (int kc = 0; kc < KC; ++kc) {
+                        FP4_PROF_T0();
                         if (!wait_or_abort<200>(&raw_empty[raw.stage], raw.phase ^ 1u, &s_abort, p.err)) break;
+                        FP4_PROF_ADD(0);
                         uint8_t * dst = raws + (size_t) raw.stage * C::RAW_STAGE;
                         mbar_arrive_expect_tx(&raw_full[raw.stage], C::RAW_STAGE);
                         tma_load_2d(dst, &map_w0, kc * GEMM_RAW_ROW, row0, &raw_full[raw.stage]);
@@ -255,11 +326,13 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
                     }
                 }
             }
+            FP4_PROF_STORE(0, 1);
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- activation producer
         if (lane == 0) {
-            Ring tile;
+            Ring act;
+            FP4_PROF_DECL();
             for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
                 const int e = p.active[item / f_tiles];
                 const int row_beg = p.offsets[e], n_e = p.offsets[e + 1] - row_beg;
@@ -267,55 +340,83 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
                 for (int t0 = 0; t0 < n_e && !s_abort; t0 += FP4_RPT) {
                     const uint8_t * sft = p.sf + (size_t) (tile0 + t0 / FP4_RPT) * KC * FP4_SF_TILE;
                     for (int kc = 0; kc < KC; ++kc) {
-                        if (!wait_or_abort<100>(&tile_empty[tile.stage], tile.phase ^ 1u, &s_abort, p.err)) break;
-                        uint8_t * st = tiles + (size_t) tile.stage * C::STAGE;
-                        mbar_arrive_expect_tx(&tile_full[tile.stage], C::B_TILE + FP4_SF_TILE);
-                        tma_load_2d(st + OFF_B, &map_planes, kc * 128, FP4_PLANES * (row_beg + t0), &tile_full[tile.stage]);
-                        bulk_g2s(st + OFF_SFB, sft + (size_t) kc * FP4_SF_TILE, FP4_SF_TILE, &tile_full[tile.stage]);
-                        tile.template advance<TS>();
+                        FP4_PROF_T0();
+                        if (!wait_or_abort<100>(&act_empty[act.stage], act.phase ^ 1u, &s_abort, p.err)) break;
+                        FP4_PROF_ADD(0);
+                        uint8_t * st = acts + (size_t) act.stage * C::ACT_STAGE;
+                        mbar_arrive_expect_tx(&act_full[act.stage], C::B_BYTES + FP4_SF_TILE);
+                        tma_load_2d(st, &map_planes, kc * 128, FP4_PLANES * (row_beg + t0), &act_full[act.stage]);
+                        bulk_g2s(st + OFF_SFB, sft + (size_t) kc * FP4_SF_TILE, FP4_SF_TILE, &act_full[act.stage]);
+                        act.template advance<AS>();
                     }
                 }
             }
+            FP4_PROF_STORE(2, 1);
         }
     } else if (warp == 2) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            Ring tile, acc;
+            Ring tile, act, acc;
+            FP4_PROF_DECL();
             for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
                 const int e = p.active[item / f_tiles];
                 const int n_e = p.offsets[e + 1] - p.offsets[e];
                 for (int t0 = 0; t0 < n_e && !s_abort; t0 += FP4_RPT) {
                     const int nt = min(FP4_RPT, n_e - t0);
                     const uint32_t idesc = umma_idesc_fp4((FP4_PLANES * nt + 7) & ~7);
-                    if (!wait_or_abort<40>(&acc_empty[acc.stage], acc.phase ^ 1u, &s_abort, p.err)) break;
+                    {
+                        FP4_PROF_T0();
+                        if (!wait_or_abort<40>(&acc_empty[acc.stage], acc.phase ^ 1u, &s_abort, p.err)) break;
+                        FP4_PROF_ADD(0);
+                    }
                     tc_fence_after();
                     const uint32_t d0 = tmem + (uint32_t) acc.stage * (2 * FP4_NCOL), d1 = d0 + FP4_NCOL;
                     for (int kc = 0; kc < KC; ++kc) {
-                        if (!wait_or_abort<40>(&tile_full[tile.stage], tile.phase, &s_abort, p.err)) break;
+                        {
+                            FP4_PROF_T0();
+                            if (!wait_or_abort<20>(&act_full[act.stage], act.phase, &s_abort, p.err)) break;
+                            FP4_PROF_ADD(1);
+                        }
+                        {
+                            FP4_PROF_T0();
+                            if (!wait_or_abort<20>(&tile_full[tile.stage], tile.phase, &s_abort, p.err)) break;
+                            FP4_PROF_ADD(2);
+                        }
                         tc_fence_after();
                         const uint32_t sbase = smem_u32(tiles + (size_t) tile.stage * C::STAGE);
-                        const uint32_t da = DESC_LO | (sbase >> 4);
+                        const uint32_t abase = smem_u32(acts + (size_t) act.stage * C::ACT_STAGE);
+                        const uint32_t da = DESC_LO | (sbase >> 4), db = DESC_LO | (abase >> 4);
+                        // Scale factors go to the set of tensor-memory columns that belongs to this operand stage.  The set was last
+                        // read by the MMAs of the stage two back, and those have completed: their commit released the operand stage,
+                        // the repack threads waited for that before refilling it, and only then could tile_full be seen above.  (Two
+                        // accumulators are in flight, and a scale copy is not ordered behind an earlier MMA on another accumulator:
+                        // with one set of columns a copy was measured to overtake MMAs of the previous stage.)
+                        const uint32_t sf_set = tmem + C::SF_COL + 48 * (uint32_t) tile.stage;
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {   // 4 x K64 = 256; 32 bytes (2 units) further along the 128-byte row each
-                            const uint32_t t_sfa0 = tmem + C::SF_COL + 12 * kk, t_sfa1 = t_sfa0 + 4, t_sfb = t_sfa0 + 8;
+                            const uint32_t t_sfa0 = sf_set + 12 * kk, t_sfa1 = t_sfa0 + 4, t_sfb = t_sfa0 + 8;
                             tmem_cp_sf(t_sfa0, sbase + OFF_SFA + kk * 512);
                             tmem_cp_sf(t_sfa1, sbase + OFF_SFA + FP4_SF_TILE + kk * 512);
-                            tmem_cp_sf(t_sfb, sbase + OFF_SFB + kk * 512);
+                            tmem_cp_sf(t_sfb, abase + OFF_SFB + kk * 512);
                             const bool accum = kc != 0 || kk != 0;
-                            umma_fp4(d0, da + 2 * kk, da + (OFF_B >> 4) + 2 * kk, DESC_HI, idesc, t_sfa0, t_sfb, accum);
-                            umma_fp4(d1, da + (OFF_A1 >> 4) + 2 * kk, da + (OFF_B >> 4) + 2 * kk, DESC_HI, idesc, t_sfa1, t_sfb, accum);
+                            umma_fp4(d0, da + 2 * kk, db + 2 * kk, DESC_HI, idesc, t_sfa0, t_sfb, accum);
+                            umma_fp4(d1, da + (OFF_A1 >> 4) + 2 * kk, db + 2 * kk, DESC_HI, idesc, t_sfa1, t_sfb, accum);
                         }
-                        umma_commit(&tile_empty[tile.stage]);   // frees the operand stage when these MMAs have read it
+                        umma_commit(&tile_empty[tile.stage]);   // frees both operand stages when these MMAs have read them
+                        umma_commit(&act_empty[act.stage]);
                         tile.template advance<TS>();
+                        act.template advance<AS>();
                     }
                     umma_commit(&acc_full[acc.stage]);
                     acc.template advance<2>();
                 }
             }
+            FP4_PROF_STORE(4, 3);
         }
     } else if (warp >= 4 && warp < 8) {
         // ---------------------------------------------------------------- epilogue
         Ring acc;
+        FP4_PROF_DECL();
         const int q = warp & 3;                 // TMEM lane quarter this warp may read
         for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
             const int a = item / f_tiles, ft = item % f_tiles;
@@ -327,10 +428,14 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
             for (int t0 = 0; t0 < n_e && !s_abort; t0 += FP4_RPT) {
                 const int nt = min(FP4_RPT, n_e - t0);
                 // lanes leave the polling loop one by one: the vote reconverges the warp (tcgen05.ld below needs all of it)
-                if (!__all_sync(0xffffffffu, wait_or_abort<200>(&acc_full[acc.stage], acc.phase, &s_abort, p.err))) break;
+                {
+                    FP4_PROF_T0();
+                    if (!__all_sync(0xffffffffu, wait_or_abort<200>(&acc_full[acc.stage], acc.phase, &s_abort, p.err))) break;
+                    FP4_PROF_ADD(0);
+                }
                 tc_fence_after();
                 const uint32_t d0 = tmem + (uint32_t) acc.stage * (2 * FP4_NCOL) + ((uint32_t) (q * 32) << 16);
-                for (int g = 0; g < nt; g += 4) {          // four routed rows = 28 plane columns per load
+                for (int g = 0; g < nt; g += 4) {          // four routed rows = 28 plane columns per load (the last load of a full tile reads past its 98)
                     float v0[32], v1[32];
                     tmem_ld32(d0 + FP4_PLANES * g, v0);
                     tmem_ld32(d0 + FP4_NCOL + FP4_PLANES * g, v1);
@@ -360,6 +465,7 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
                 acc.template advance<2>();
             }
         }
+        if (warp == 4 && lane == 0) FP4_PROF_STORE(8, 1);
     } else if (warp >= 8) {
         // ---------------------------------------------------------------- repack: strip the scale bytes, keep everything else
         const int dq = tid - 256;
@@ -370,12 +476,17 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
         const uint32_t sf_off = OFF_SFA + tsel * FP4_SF_TILE + sf_tile_offset(trow);
         const uint32_t raw_off = (uint32_t) dq * GEMM_RAW_ROW;
         Ring raw, tile;
+        FP4_PROF_DECL();
         for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
             const int e = p.active[item / f_tiles];
             const int n_e = p.offsets[e + 1] - p.offsets[e];
             for (int t0 = 0; t0 < n_e && !s_abort; t0 += FP4_RPT) {
                 for (int kc = 0; kc < KC && !s_abort; ++kc) {
-                    if (!__all_sync(0xffffffffu, wait_or_abort(&raw_full[raw.stage], raw.phase, &s_abort, p.err))) break;
+                    {
+                        FP4_PROF_T0();
+                        if (!__all_sync(0xffffffffu, wait_or_abort(&raw_full[raw.stage], raw.phase, &s_abort, p.err))) break;
+                        FP4_PROF_ADD(0);
+                    }
                     uint32_t R[36];                // 4 blocks of [scale word][8 code words]
                     {
                         const uint4 * src = reinterpret_cast<const uint4 *>(raws + (size_t) raw.stage * C::RAW_STAGE + raw_off);
@@ -388,7 +499,11 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&raw_empty[raw.stage]);
                     raw.template advance<RS>();
-                    if (!__all_sync(0xffffffffu, wait_or_abort(&tile_empty[tile.stage], tile.phase ^ 1u, &s_abort, p.err))) break;
+                    {
+                        FP4_PROF_T0();
+                        if (!__all_sync(0xffffffffu, wait_or_abort(&tile_empty[tile.stage], tile.phase ^ 1u, &s_abort, p.err))) break;
+                        FP4_PROF_ADD(1);
+                    }
                     uint8_t * st = tiles + (size_t) tile.stage * C::STAGE;
 #pragma unroll
                     for (int kb = 0; kb < 4; ++kb) {
@@ -408,6 +523,7 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
                 }
             }
         }
+        if (tid == 256) FP4_PROF_STORE(10, 2);
     }
 
     // ---- teardown: everyone meets here (all waits above are bounded), then tensor memory goes back

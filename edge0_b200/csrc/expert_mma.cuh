@@ -82,9 +82,9 @@ __device__ __forceinline__ uint32_t sw128_offset(int r, int c) { return (uint32_
 // [0,8,1,9,2,10,3,11,4,12,5,13,6,14,7,15], the order in which the NVFP4 nibbles of a sub-block unpack.
 // One warp per (sorted row, 32-element activation block).  Rows are row_stride halfs apart in both planes: K with the lo
 // plane stored after the hi plane, 2K with out_lo = out_hi + K when hi and lo rows alternate.
-__global__ void __launch_bounds__(256) sorted_act_fp16_kernel(ActQuant act, const int * __restrict__ perm, int rows, int K, int n_ids,
-                                                             int ne11, __half * __restrict__ out_hi, __half * __restrict__ out_lo,
-                                                             int row_stride) {
+__global__ void __launch_bounds__(256) sorted_act_fp16_kernel(ActQuant act, const int * __restrict__ perm, const int * __restrict__ meta, int rows,
+                                                             int K, int n_ids, int ne11, __half * __restrict__ out_hi,
+                                                             __half * __restrict__ out_lo, int row_stride) {
     pdl_wait();
     pdl_launch_dependents();
 
@@ -92,6 +92,7 @@ __global__ void __launch_bounds__(256) sorted_act_fp16_kernel(ActQuant act, cons
     const int nb = K / 32;
     if (warp >= rows * nb) return;
     const int i = warp / nb, b = warp % nb;
+    if (i >= meta[1]) return;   // rows that are in no group (empty exchange slots) have no sorted position
     const int r = perm[i];
     const int arow = (r / n_ids) * ne11 + (r % n_ids) % ne11;
     const float d = act.d[(size_t) arow * nb + b];

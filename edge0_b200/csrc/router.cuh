@@ -337,6 +337,8 @@ __global__ void __launch_bounds__(256) route_select_kernel(const float * __restr
 //   offsets[e]   first slot of expert e in perm, offsets[E] = total rows
 //   perm[i]      routed row index (token*K + slot) placed i-th
 //   active[a]    a-th expert that has at least one row; n_active in meta[0], total rows in meta[1]
+constexpr int TOKEN_TILE_ROWS = 14;   // routed rows per token tile of the FP4 tensor-core kernels (7 digit planes each)
+
 struct Groups {
     int * counts;   // [E]
     int * offsets;  // [E+1]
@@ -345,11 +347,12 @@ struct Groups {
     int * active;   // [E]
     int * meta;     // [4]
     int * cost;     // [4][E+1]: rows 0-2: prefix over active experts of the work per weight row for the nt = 1, 2, 4 kernels;
-                    // row 3, indexed by EXPERT id: index of the expert's first 16-row token tile (prefix of ceil(rows / 16))
+                    // row 3, indexed by EXPERT id: index of the expert's first token tile (prefix of ceil(rows / TOKEN_TILE_ROWS))
 };
 
 // Block-wide: counts must be final and visible to this block.
-__device__ __forceinline__ void group_scan_body(Groups g, const int32_t * __restrict__ ids, int E, int rows, int * err, int * sh) {
+// allow_empty: ids equal to -1 mark routed rows that do not exist (empty slots of an expert-parallel exchange): they are in no group.
+__device__ __forceinline__ void group_scan_body(Groups g, const int32_t * __restrict__ ids, int E, int rows, int * err, int * sh, bool allow_empty = false) {
     int * off = sh;
     int * act = sh + (E + 1);  // act[a] = a-th active expert (also written to g.active)
     const int tid = threadIdx.x;
@@ -361,7 +364,7 @@ __device__ __forceinline__ void group_scan_body(Groups g, const int32_t * __rest
             const int n = e < E ? g.counts[e] : 0;
             // work per weight row: nt=1 kernels: one pass per routed row; nt=4 kernels: 3 per pass (decode) + 2 per routed row
             int incl = n, w2 = (n + 1) / 2, w4 = 3 * ((n + 3) / 4) + 2 * n;
-            int i2 = w2, i4 = w4, it = (n + 15) / 16;
+            int i2 = w2, i4 = w4, it = (n + TOKEN_TILE_ROWS - 1) / TOKEN_TILE_ROWS;
             const int wt = it;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -391,25 +394,26 @@ __device__ __forceinline__ void group_scan_body(Groups g, const int32_t * __rest
             g.cost[na] = c1; g.cost[(E + 1) + na] = c2; g.cost[2 * (E + 1) + na] = c4; g.cost[3 * (E + 1) + E] = tl;
             g.meta[0] = na;
             g.meta[1] = run;
-            if (run != rows) report_error(err, DEV_ERR_BAD_SHAPE);
+            if (allow_empty ? run > rows : run != rows) report_error(err, DEV_ERR_BAD_SHAPE);
         }
     }
     __syncthreads();
     for (int e = tid; e <= E; e += blockDim.x) g.offsets[e] = off[e];
     for (int r = tid; r < rows; r += blockDim.x) {
         const int e = ids[r];
+        if (allow_empty && e == -1) continue;
         if (e < 0 || e >= E) { report_error(err, DEV_ERR_BAD_EXPERT_ID); continue; }
         g.perm[off[e] + g.pos[r]] = r;
     }
 }
 
 // Single block.  counts must be final (selection kernel finished).
-__global__ void __launch_bounds__(1024) group_scan_kernel(Groups g, const int32_t * __restrict__ ids, int E, int rows, int * err) {
+__global__ void __launch_bounds__(1024) group_scan_kernel(Groups g, const int32_t * __restrict__ ids, int E, int rows, int * err, int allow_empty) {
     pdl_wait();
     pdl_launch_dependents();
 
     extern __shared__ int sh[];  // [E+1] offsets, [E] active flags
-    group_scan_body(g, ids, E, rows, err, sh);
+    group_scan_body(g, ids, E, rows, err, sh, allow_empty != 0);
 }
 
 // Small batches: selection for every token and the grouping in ONE single-block launch (one warp per token, looping).
@@ -431,7 +435,7 @@ __global__ void __launch_bounds__(1024) route_select_group_kernel(const float * 
 // possibly as a strided view: row t starts at ids + t*ids_stride).  Writes compact ids as well.
 __global__ void __launch_bounds__(256) count_ids_kernel(const int32_t * __restrict__ ids, int64_t ids_stride, int n_ids, int T, int E,
                                                        int32_t * __restrict__ ids_compact, int * __restrict__ counts,
-                                                       int * __restrict__ pos, int * err) {
+                                                       int * __restrict__ pos, int * err, int allow_empty = 0) {
     pdl_wait();
     pdl_launch_dependents();
 
@@ -440,6 +444,7 @@ __global__ void __launch_bounds__(256) count_ids_kernel(const int32_t * __restri
     const int t = r / n_ids, s = r % n_ids;
     const int e = ids[(size_t) t * ids_stride + s];
     ids_compact[r] = e;
+    if (allow_empty && e == -1) { pos[r] = 0; return; }
     if (e < 0 || e >= E) { report_error(err, DEV_ERR_BAD_EXPERT_ID); pos[r] = 0; return; }
     pos[r] = atomicAdd(&counts[e], 1);
 }

@@ -5,21 +5,29 @@ Semantics follow edge0-strata's latent layer with one label group (src/latent/la
 The reference has no multi-GPU form of it; the partition here is:
   * tokens are split evenly over ranks for routing, D, the combine and U;
   * expert e lives on rank e // (E / N) (contiguous blocks), so expert weights are never moved;
-  * one exchange each way (all-to-all): routed latent rows travel to their expert's owner, result rows travel back.
-Every routed row is computed by exactly the arithmetic of the single-GPU layer (an ffn call with one slot and weight 1.0),
-and the slot-order sum happens on the token's own rank, so results do not depend on N.
+  * one exchange each way: routed latent rows travel to their expert's owner, result rows travel back.
 
-`backend` supplies the arithmetic.  CudaBackend calls the C ABI; tests on CPU plug in a backend made of the checker's
-functions to exercise this file's bookkeeping over gloo.
+The exchange is planned on the DEVICE.  Every rank sends every peer the same number of SLOTS (`capacity` = the routed rows a rank
+can have, T_local_max * k), so both all-to-alls have equal split sizes that are known before the step starts: no count is read
+on the host between routing and the collective, nothing is allocated, and the whole step (route, D, pack, all-to-all, experts,
+all-to-all, combine, U) is plain stream work that a CUDA graph can capture.  A slot is the fp32 row followed by the expert id
+local to the destination rank; id -1 marks an empty slot, which the owner's kernels skip.
+
+Every routed row is computed by exactly the arithmetic of the single-GPU layer (one slot of weight 1.0 on the owner's pinned
+kernel path), and the slot-order sum happens on the token's own rank, so results do not depend on N.
+
+`backend` supplies the arithmetic.  CudaBackend calls the C ABI; tests on CPU plug in a backend made of the checker's functions
+(with pack_slots / combine_slots below as the host statement of the slot format) to exercise this file over gloo.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
 from typing import Optional
 
 import numpy as np
 import torch
 import torch.distributed as dist
+
+SLOT_EXTRA_WORDS = 4   # behind the row: expert id + padding to 16 bytes (b200moe_ep_slot_bytes)
 
 
 def expert_owner(n_expert: int, world: int, e):
@@ -33,95 +41,103 @@ def token_range(n_tokens: int, world: int, rank: int) -> tuple[int, int]:
     return lo, lo + base + (1 if rank < rem else 0)
 
 
-@dataclass
-class DispatchPlan:
-    """Bookkeeping of one exchange, all index tensors on the compute device.
-    order        [R]  routed rows (t*k + s) of this rank sorted by destination rank (stable)
-    send_counts  [N]  rows going to each rank            (python ints: they size the collective)
-    recv_counts  [N]  rows arriving from each rank
-    """
-    order: torch.Tensor
-    send_counts: list
-    recv_counts: list
+def slot_capacity(n_tokens_total: int, world: int, top_k: int) -> int:
+    """Slots every rank sends to every peer: the routed rows of the rank with the most tokens, rounded up to a multiple of 4."""
+    t_max = -(-n_tokens_total // world)
+    return max(4, (t_max * top_k + 3) // 4 * 4)
 
 
-def plan_dispatch(ids: torch.Tensor, n_expert: int, world: int, group=None) -> DispatchPlan:
-    """ids int32 [T_local, k].  One small all-to-all of counts; the counts come to the host because they size the
-    payload collectives."""
-    flat = ids.reshape(-1).to(torch.int64)
-    dest = torch.div(flat, n_expert // world, rounding_mode="floor")
-    order = torch.sort(dest, stable=True).indices.to(torch.int32)
-    send = torch.bincount(dest, minlength=world).to(torch.int64)
-    recv = torch.empty_like(send)
-    if world > 1:
-        dist.all_to_all_single(recv, send, group=group)
-    else:
-        recv.copy_(send)
-    both = torch.stack([send, recv]).cpu()      # one device-to-host read for both count vectors
-    return DispatchPlan(order=order, send_counts=[int(v) for v in both[0]], recv_counts=[int(v) for v in both[1]])
+def pack_slots(rows: np.ndarray, ids: np.ndarray, world: int, experts_per_rank: int, capacity: int):
+    """Host statement of b200moe_ep_pack: rows float32 [T, w], ids int32 [T, k] -> (slots float32 [world, capacity, w + 4] with the
+    expert id stored bitwise in word w, slot_of int32 [T, k]).  Rows are placed per destination in routed-row order (the device
+    kernel places them in arrival order: any order is valid, slot_of records it)."""
+    T, w = rows.shape
+    k = ids.shape[1]
+    slots = np.zeros((world, capacity, w + SLOT_EXTRA_WORDS), np.float32)
+    slots.view(np.int32)[:, :, w] = -1
+    fill = [0] * world
+    slot_of = np.empty((T, k), np.int32)
+    for t in range(T):
+        for s in range(k):
+            dest = int(ids[t, s]) // experts_per_rank
+            pos = fill[dest]
+            fill[dest] += 1
+            slots[dest, pos, :w] = rows[t]
+            slots.view(np.int32)[dest, pos, w] = int(ids[t, s]) - dest * experts_per_rank
+            slot_of[t, s] = dest * capacity + pos
+    return slots, slot_of
 
 
-def exchange_rows(rows: torch.Tensor, send_counts, recv_counts, world: int, group=None) -> torch.Tensor:
-    """rows [sum(send_counts), w], already ordered by destination -> [sum(recv_counts), w] ordered by source."""
-    out = torch.empty((sum(recv_counts),) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
-    if world > 1:
-        dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=list(recv_counts), input_split_sizes=list(send_counts), group=group)
-    else:
-        out.copy_(rows)
-    return out
+def combine_slots(back: np.ndarray, slot_of: np.ndarray, weights: np.ndarray) -> np.ndarray:
+    """Host statement of b200moe_ep_combine: slots added in order, each product rounded to fp32 first."""
+    if slot_of.shape[0] == 0:
+        return np.zeros((0, back.shape[1]), np.float32)
+    acc = back[slot_of[:, 0]] * weights[:, 0:1]
+    for s in range(1, slot_of.shape[1]):
+        acc = acc + back[slot_of[:, s]] * weights[:, s:s + 1]
+    return acc.astype(np.float32)
 
 
 class ExpertParallelLayer:
     """One rank's share of the layer.
 
-    backend.route(x)                    -> ids int32 [T,k], weights float32 [T,k]      (full router, replicated)
-    backend.project_down(x) / project_up(m)                                            (shared D / U, replicated)
-    backend.expert_rows(xl_rows, local_expert_ids) -> float32 [R, L]                   (this rank's experts only)
-    backend.gather_rows(src, idx), backend.combine(y [T,k,L], w [T,k])
+    backend.route(x)                            -> ids int32 [T,k], weights float32 [T,k]      (full router, replicated)
+    backend.project_down(x) / project_up(m)                                                    (shared D / U, replicated)
+    backend.pack(xl, ids, world, per, capacity) -> slots [world, capacity, slot], slot_of int32 [T,k]
+    backend.expert_rows(slots [n_slots, slot])  -> float32 [n_slots, L]                        (this rank's experts only)
+    backend.combine(back [n_slots, L], slot_of, w) -> float32 [T, L]
+    backend.exchange_buffer(t)                  -> tensor like t that receives the all-to-all
     """
 
-    def __init__(self, backend, n_expert: int, top_k: int, rank: int = 0, world: int = 1, group=None):
+    def __init__(self, backend, n_expert: int, top_k: int, rank: int = 0, world: int = 1, group=None, capacity: Optional[int] = None):
         if n_expert % world:
             raise ValueError("n_expert must divide evenly over the ranks")
         self.b, self.E, self.k, self.rank, self.world, self.group = backend, n_expert, top_k, rank, world, group
+        if world > 1 and capacity is None:
+            raise ValueError("capacity (slot_capacity(total tokens, world, top_k)) must be the same on every rank")
+        self.capacity = capacity       # None (single rank): derived from the first batch
+        self._events = None
 
     def forward(self, x_local: torch.Tensor, return_routing: bool = False):
         """x_local: this rank's tokens [T_local, H] -> out [T_local, H]."""
-        b, k = self.b, self.k
+        b, k, N = self.b, self.k, self.world
         T = x_local.shape[0]
+        if self.capacity is None:
+            self.capacity = max(4, (T * k + 3) // 4 * 4)
+        cap = self.capacity
+        if T * k > cap:
+            raise ValueError(f"{T} tokens x top-{k} exceed the slot capacity {cap} this layer was built for")
         mark = self._mark
         mark("start")
         ids, w = b.route(x_local)                                    # [T,k]
         xl = b.project_down(x_local)                                 # [T,L] float32
         mark("route+D")
-        plan = plan_dispatch(ids, self.E, self.world, self.group)
-        # pack: routed row r = t*k+s carries token t's latent row and its expert id
-        tok = torch.div(plan.order, k, rounding_mode="floor").to(torch.int32)
-        send_rows = b.gather_rows(xl, tok)                           # [R, L] ordered by destination
-        send_eid = ids.reshape(-1)[plan.order.long()].to(torch.int32).reshape(-1, 1)
-        recv_rows = exchange_rows(send_rows, plan.send_counts, plan.recv_counts, self.world, self.group)
-        recv_eid = exchange_rows(send_eid, plan.send_counts, plan.recv_counts, self.world, self.group)
-        local_eid = (recv_eid.reshape(-1) - self.rank * (self.E // self.world)).to(torch.int32)
+        slots, slot_of = b.pack(xl, ids, N, self.E // N, cap)         # [N, cap, slot]
+        recv = self._exchange(slots)
         mark("dispatch")
-        y_rows = b.expert_rows(recv_rows, local_eid)                 # [R', L]
+        y = b.expert_rows(recv.reshape(N * cap, -1))                  # [N*cap, L]; row (p, s) answers slot s of peer p
         mark("experts")
-        back = exchange_rows(y_rows, plan.recv_counts, plan.send_counts, self.world, self.group)   # ordered like send_rows
-        # unpack: back[i] is routed row plan.order[i]; bring rows into (t, s) order
-        inv = torch.empty_like(plan.order)
-        inv[plan.order.long()] = torch.arange(plan.order.numel(), dtype=torch.int32, device=plan.order.device)
-        y = b.gather_rows(back, inv).reshape(T, k, -1)
+        back = self._exchange(y.reshape(N, cap, -1)).reshape(N * cap, -1)
         mark("return")
-        moe = b.combine(y, w)                                        # slot-order weighted sum on the token's rank
+        moe = b.combine(back, slot_of, w)                             # slot-order weighted sum on the token's rank
         out = b.project_up(moe)
         mark("combine+U")
         return (out, ids, w) if return_routing else out
+
+    def _exchange(self, t: torch.Tensor) -> torch.Tensor:
+        """[N, ...] -> [N, ...]: chunk p goes to rank p, chunk p of the result came from rank p.  Equal splits."""
+        if self.world == 1:
+            return t
+        out = self.b.exchange_buffer(t)
+        dist.all_to_all_single(out, t, group=self.group)
+        return out
 
     # ---- per-phase device timing (off by default): CUDA events on the current stream at the phase boundaries
     def enable_phase_timing(self, on: bool = True):
         self._events = [] if on else None
 
     def _mark(self, name: str):
-        ev = getattr(self, "_events", None)
+        ev = self._events
         if ev is None or not torch.cuda.is_available():
             return
         e = torch.cuda.Event(enable_timing=True)
@@ -130,7 +146,7 @@ class ExpertParallelLayer:
 
     def phase_times_ms(self):
         """{phase: milliseconds} of the last forward() since enable_phase_timing(); waits for the device."""
-        ev = getattr(self, "_events", None) or []
+        ev = self._events or []
         torch.cuda.synchronize()
         out = {}
         for (_, a), (name, bb) in zip(ev[:-1], ev[1:]):
@@ -141,7 +157,8 @@ class ExpertParallelLayer:
 
 
 class CudaBackend:
-    """The product arithmetic: every call goes through the C ABI (edge0_b200.moe)."""
+    """The product arithmetic: every call goes through the C ABI (edge0_b200.moe).  Buffers of a step are allocated once and
+    reused, so a captured step replays on fixed addresses."""
 
     def __init__(self, ctx, host_layer, rank: int = 0, world: int = 1):
         from . import moe
@@ -150,9 +167,10 @@ class CudaBackend:
         if cfg.n_latent:
             # The owner of an expert sees a plain layer of the latent width and cannot know that its rows are re-quantised
             # again by the up-projection on the token's rank: pin what the library does by default for a latent layer it sees
-            # whole (tensor-core gate/up with the exact re-quantisation fix-up, integer down: bit-identical results).
-            ctx.set_expert_path(5)
-        E, per = cfg.n_expert, cfg.n_expert // world
+            # whole (FP4 tensor-core gate/up with the exact re-quantisation fix-up, FP4 down).  A pinned path also keeps the
+            # choice of kernels - and with it every routed row's arithmetic - independent of how many rows a rank receives.
+            ctx.set_expert_path(8)
+        per = cfg.n_expert // world
         lo, hi = rank * per, (rank + 1) * per
         if host_layer.gate.shape[0] == per and world > 1:      # generated for this shard only (make_layer(expert_range=...))
             assert host_layer.expert_lo == lo
@@ -160,38 +178,47 @@ class CudaBackend:
         else:
             sl = lambda a: None if a is None else a[lo:hi]
         dev = torch.device("cuda", ctx.device)
-        put = lambda a, dt: None if a is None else torch.from_numpy(np.ascontiguousarray(a)).to(dev, dt)
         # full layer descriptor for routing (router only needs router_w; expert pointers point at the local shard)
         self.route_layer = moe.MoeLayer(ctx, wtype=cfg.wtype, top_k=cfg.top_k, router_w=host_layer.router_w, router_bias=host_layer.router_bias,
                                         gate=host_layer.gate[:1], up=host_layer.up[:1], down=host_layer.down[:1],
-                                        lat_down=host_layer.lat_down, lat_up=host_layer.lat_up, check_shapes=False)  # used for routing only
+                                        lat_down=host_layer.lat_down, lat_up=host_layer.lat_up, lat_down_scale=host_layer.lat_down_scale,
+                                        lat_up_scale=host_layer.lat_up_scale, check_shapes=False)   # router and latent projections only
         # local experts as a plain (non-latent) layer of width L with one slot per row
         self.local = moe.MoeLayer(ctx, wtype=cfg.wtype, top_k=1, router_w=np.zeros((per, cfg.n_in), np.float32), gate=sl(host_layer.gate),
                                   up=sl(host_layer.up), down=sl(host_layer.down), gate_scale=sl(host_layer.gate_scale),
                                   up_scale=sl(host_layer.up_scale), down_scale=sl(host_layer.down_scale))
-        self.lat_down, self.lat_up = put(host_layer.lat_down, torch.uint8), put(host_layer.lat_up, torch.uint8)
-        self.s_d, self.s_u = put(host_layer.lat_down_scale, torch.float32), put(host_layer.lat_up_scale, torch.float32)
-        self.ones = None
+        self.dev = dev
+        self._buf = {}
+
+    def _get(self, name, shape, dtype, zero=False):
+        t = self._buf.get(name)
+        if t is None or tuple(t.shape) != tuple(shape) or t.dtype != dtype:
+            t = (torch.zeros if zero else torch.empty)(tuple(shape), dtype=dtype, device=self.dev)
+            self._buf[name] = t
+        return t
 
     def route(self, x):
         return self.route_layer.route(x)
 
     def project_down(self, x):
-        return self.ctx.mul_mat(self.cfg.wtype, self.lat_down, x.float() if x.dtype != torch.float32 else x, self.cfg.n_embd, self.s_d)
+        return self.route_layer.latent_down(x)
 
     def project_up(self, m):
-        return self.ctx.mul_mat(self.cfg.wtype, self.lat_up, m, self.cfg.n_latent, self.s_u)
+        return self.route_layer.latent_up(m)
 
-    def expert_rows(self, rows, local_eid):
-        R = rows.shape[0]
-        if R == 0:
-            return torch.empty((0, self.cfg.n_in), dtype=torch.float32, device=rows.device)
-        if self.ones is None or self.ones.shape[0] < R:
-            self.ones = torch.ones((max(R, 1024), 1), dtype=torch.float32, device=rows.device)
-        return self.local.ffn(rows, local_eid.reshape(R, 1), self.ones[:R])
+    def pack(self, xl, ids, world, per, capacity):
+        sb = int(self.ctx.lib.b200moe_ep_slot_bytes(xl.shape[1]))
+        slots = self._get("slots", (world, capacity, sb), torch.uint8)
+        slot_of = self._get("slot_of", tuple(ids.shape), torch.int32)
+        fill = self._get("fill", (world,), torch.int32)
+        return self.ctx.ep_pack(xl, ids, world, per, capacity, slots, slot_of, fill)
 
-    def gather_rows(self, src, idx):
-        return self.ctx.gather_rows(src, idx)
+    def exchange_buffer(self, t):
+        return self._get("xchg_%s" % t.dtype, tuple(t.shape), t.dtype)
 
-    def combine(self, y, w):
-        return self.ctx.combine(y.contiguous(), w)
+    def expert_rows(self, slots):
+        y = self._get("y", (slots.shape[0], self.cfg.n_in), torch.float32, zero=True)
+        return self.local.ep_expert_rows(slots, y)
+
+    def combine(self, back, slot_of, w):
+        return self.ctx.ep_combine(back, slot_of, w)

@@ -122,11 +122,11 @@ class Context:
         self.check(self.lib.b200moe_enable_kernel_timing(self.handle, int(on)))
 
     def kernel_times(self):
-        """[(launches, total_ms) for the fused gate/up kernel, (launches, total_ms) for the single-matrix kernel]; clears the record."""
-        n = (C.c_int64 * 2)()
-        ms = (C.c_double * 2)()
+        """[(launches, total_ms)] for the fused gate/up kernel, the single indexed matmul (down) and dense products; clears the record."""
+        n = (C.c_int64 * 3)()
+        ms = (C.c_double * 3)()
         self.check(self.lib.b200moe_kernel_times(self.handle, n, ms))
-        return [(int(n[0]), float(ms[0])), (int(n[1]), float(ms[1]))]
+        return [(int(n[i]), float(ms[i])) for i in range(3)]
 
     def mul_mat(self, wtype: int, w: torch.Tensor, x: torch.Tensor, ne00: int, scale: Optional[torch.Tensor] = None) -> torch.Tensor:
         """w uint8 [ne01, row_bytes]; x float32 [T, ne00] -> float32 [T, ne01] (ggml_mul_mat with a quantised matrix)."""
@@ -147,6 +147,32 @@ class Context:
         dst = torch.empty((idx.shape[0], src.shape[1]), dtype=torch.float32, device=src.device)
         self.check(self.lib.b200moe_gather_rows(self.handle, _ptr(src), src.shape[0], _ptr(idx), _ptr(dst), idx.shape[0], src.shape[1], self._stream()))
         return dst
+
+    # ---- expert-parallel exchange (b200moe_ep_*): outputs may be passed in so a step allocates nothing
+    def ep_pack(self, rows: torch.Tensor, ids: torch.Tensor, n_ranks: int, experts_per_rank: int, capacity: int,
+                slots: Optional[torch.Tensor] = None, slot_of: Optional[torch.Tensor] = None, fill: Optional[torch.Tensor] = None):
+        """rows float32 [T, w], ids int32 [T, k] -> (slots uint8 [n_ranks, capacity, slot_bytes], slot_of int32 [T, k])."""
+        T, w = rows.shape
+        k = ids.shape[1]
+        sb = int(self.lib.b200moe_ep_slot_bytes(w))
+        if slots is None:
+            slots = torch.empty((n_ranks, capacity, sb), dtype=torch.uint8, device=rows.device)
+        if slot_of is None:
+            slot_of = torch.empty((T, k), dtype=torch.int32, device=rows.device)
+        if fill is None:
+            fill = torch.empty((n_ranks,), dtype=torch.int32, device=rows.device)
+        self.check(self.lib.b200moe_ep_pack(self.handle, _ptr(rows), _ptr(ids), T, k, w, n_ranks, experts_per_rank, capacity, _ptr(slots),
+                                            _ptr(slot_of), _ptr(fill), self._stream()))
+        return slots, slot_of
+
+    def ep_combine(self, back: torch.Tensor, slot_of: torch.Tensor, weights: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """back float32 [n_slots, w], slot_of int32 [T, k], weights float32 [T, k] -> float32 [T, w]."""
+        n_slots, w = back.shape
+        T, k = slot_of.shape
+        if out is None:
+            out = torch.empty((T, w), dtype=torch.float32, device=back.device)
+        self.check(self.lib.b200moe_ep_combine(self.handle, _ptr(back), n_slots, _ptr(slot_of), _ptr(weights), T, k, w, _ptr(out), self._stream()))
+        return out
 
     def mul_mat_id(self, wtype: int, experts: torch.Tensor, b: torch.Tensor, ids: torch.Tensor, ne00: int) -> torch.Tensor:
         """experts uint8 [n_as, ne01, row_bytes]; b float32 [T, ne11, ne00]; ids int32 [T, n_ids] (may be a
@@ -237,6 +263,31 @@ class MoeLayer:
         c.check(c.lib.b200moe_ffn(c.handle, C.byref(self.desc), _ptr(x), _x_type(x), T, _ptr(ids.contiguous()), _ptr(weights.contiguous()),
                                   _ptr(out), None, c._stream()))
         return out
+
+    def latent_down(self, x: torch.Tensor) -> torch.Tensor:
+        """x [T, n_embd] -> latent rows float32 [T, n_latent] (edge0-strata latent_moe.cpp: xl = D x)."""
+        T = x.shape[0]
+        xl = torch.empty((T, self.n_latent), dtype=torch.float32, device=x.device)
+        c = self.ctx
+        c.check(c.lib.b200moe_latent_down(c.handle, C.byref(self.desc), _ptr(x), _x_type(x), T, _ptr(xl), c._stream()))
+        return xl
+
+    def latent_up(self, m: torch.Tensor) -> torch.Tensor:
+        """m float32 [T, n_latent] -> float32 [T, n_embd] (y = U m)."""
+        T = m.shape[0]
+        out = torch.empty((T, self.n_embd), dtype=torch.float32, device=m.device)
+        c = self.ctx
+        c.check(c.lib.b200moe_latent_up(c.handle, C.byref(self.desc), _ptr(m), T, _ptr(out), c._stream()))
+        return out
+
+    def ep_expert_rows(self, slots: torch.Tensor, y: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """slots uint8 [n_slots, slot_bytes] as received from the exchange -> float32 [n_slots, n_in] (rows of empty slots untouched)."""
+        n_slots = slots.numel() // slots.shape[-1]
+        if y is None:
+            y = torch.zeros((n_slots, self.n_in), dtype=torch.float32, device=slots.device)
+        c = self.ctx
+        c.check(c.lib.b200moe_ep_expert_rows(c.handle, C.byref(self.desc), _ptr(slots), n_slots, _ptr(y), c._stream()))
+        return y
 
     def forward(self, x: torch.Tensor, observe: bool = False, out: Optional[torch.Tensor] = None):
         """The whole layer on device tensors: x [T, n_embd] -> float32 [T, n_embd] (and the observation tensors)."""

@@ -91,6 +91,9 @@ typedef struct b200moe_counters {
     int64_t experts_touched;  /* distinct experts with at least one routed row */
     int64_t weight_bytes;     /* expert + router bytes the kernels streamed   */
     int64_t kernel_launches;
+    int64_t fixup_overflow;   /* values the exact re-quantisation fix-up marked but could not list (its list holds a quarter of
+                                 `hidden`): they kept the tensor-core result.  Updated by b200moe_synchronize.  Non-zero only for
+                                 degenerate inputs such as blocks of equal values */
 } b200moe_counters;
 
 /* ---- lifetime (reference: ggml_backend_dev_init / ggml_backend_free through
@@ -108,22 +111,32 @@ B200MOE_API int  b200moe_get_counters(const b200moe_ctx * ctx, b200moe_counters 
 B200MOE_API int  b200moe_synchronize(b200moe_ctx * ctx, void * stream); /* ggml_backend_synchronize */
 
 /* Which kernels run the expert matmuls (reference: model option switches such as `routing` / `experts`,
- * edge0-infer/docs/configuration.md:62-72; plain struct-style option, no environment variables):
- *   0  default: below two routed rows per expert everything runs on the integer kernels, which follow the reference's fp32
- *      summation order and are bit-identical to the CPU path.  Above that `down` runs on the tcgen05 grouped GEMM (its ~3e-5
- *      accumulation error is not re-quantised afterwards: ~1e-5 of RMS on the output) and so does gate/up.  The reference
- *      re-quantises `hidden` to int8, which turns the GEMM's error into occasional flipped values (2e-3 of RMS on the output at
- *      64 tokens, 4e-3 at 256, 1e-2 at 4096): up to 4096 routed rows (512 tokens at top-8) that is accepted; beyond, and for
- *      latent layers (n_latent > 0, which re-quantise once more after `down` and keep `down` on the integer kernel), the values
- *      of `hidden` whose rounding the error could change are recomputed exactly (see 4).
- *   1  integer kernels everywhere: the whole layer is bit-identical to the reference CPU path
- *   2  tcgen05 grouped GEMM wherever the type and widths allow (NVFP4, n_ff and n_in multiples of 128), no exact recomputation;
- *      output error growing to 1e-2 of RMS at 4096 tokens
- *   4  as 2, plus the exact re-quantisation fix-up after gate/up: every value of `hidden` within a safe margin of an int8
- *      rounding boundary or of its block's maximum (a few per cent) is recomputed with the integer kernels' arithmetic, so the
- *      quantised `hidden` equals the reference's; what remains is the ~1e-5 of the `down` GEMM
- *   5  tcgen05 gate/up + exact fix-up, integer down: bit-identical whenever the fix-up's margin holds (what 0 does for latent layers)
- *   3  integer gate/up, tcgen05 down at any batch size */
+ * edge0-infer/docs/configuration.md:62-72; plain struct-style option, no environment variables).  Three engines exist:
+ *   integer   dp4a kernels that follow the reference's fp32 summation order: bit-identical to the CPU path
+ *   FP4       tcgen05 kind::mxf4nvf4 (block-scaled FP4 MMA, UE4M3 scale per 16): NVFP4 rows exactly as they lie in memory,
+ *             activations as exact digit planes of the reference's int8 grid; differs from the integer engine only by fp32
+ *             accumulation (~5e-6 of RMS on `hidden`); one pass over an expert's weights per 14 routed rows: batched decode
+ *   f16       tcgen05 kind::f16: weights dequantised to fp16, activations as fp16 hi + lo (~1.4e-4 of RMS on `hidden`); one pass
+ *             per 128 routed rows: prefill
+ * The reference re-quantises `hidden` to int8 before `down`, which turns a tensor-core gate/up's error into a few flipped
+ * values; the "fix-up" recomputes every value of `hidden` within a safe margin of a rounding boundary or of its block's maximum
+ * with the integer engine's arithmetic, so the quantised `hidden` is the reference's own.
+ *   0  default.  Up to 16 routed rows (one or two tokens at top-8): integer (bit-identical).  Fewer than 24 routed rows per
+ *      expert on average: FP4 for gate/up and down (output within ~3e-3 of RMS at 256 tokens; latent layers, which re-quantise
+ *      once more after `down`, add the fix-up).  More: f16 for gate/up and down, with the fix-up beyond 4096 routed rows;
+ *      latent layers add the fix-up and keep `down` on the integer engine.  Types or widths an engine has no kernel for
+ *      (Q3_K; n_ff not a multiple of 128; n_in not a multiple of 256 for FP4, of 128 for f16) fall back to integer.
+ *      Dense products (b200moe_mul_mat, the latent projections) of NVFP4 matrices with at least 4 tokens use the FP4 engine
+ *      under paths 0, 2, 3, 4, 6 and 8, the integer engine otherwise.
+ *   1  integer everywhere: the whole layer is bit-identical to the reference CPU path
+ *   2  f16 wherever the type and widths allow, no fix-up: output error growing to 1e-2 of RMS at 4096 tokens
+ *   3  integer gate/up, f16 down
+ *   4  as 2 plus the fix-up after gate/up: what remains is the ~1e-5 of the `down` GEMM
+ *   5  f16 gate/up + fix-up, integer down: bit-identical whenever the fix-up's margin holds
+ *   6  FP4 gate/up and down, no fix-up
+ *   7  FP4 gate/up + fix-up, integer down: bit-identical whenever the fix-up's margin holds
+ *   8  FP4 gate/up + fix-up, FP4 down
+ * Paths 6-8 fail with B200MOE_ERR_UNSUPPORTED when the layer is not NVFP4 with n_ff % 128 == 0 and n_in % 256 == 0. */
 B200MOE_API int  b200moe_set_expert_path(b200moe_ctx * ctx, int path);
 
 /* Launch overlap (no counterpart in the reference; comparable to a backend's own stream options).  OFF by default.  When on, calls
@@ -134,10 +147,11 @@ B200MOE_API int  b200moe_set_expert_path(b200moe_ctx * ctx, int path);
 B200MOE_API int  b200moe_set_launch_overlap(b200moe_ctx * ctx, int enable);
 /* Per-kernel device timing (reference: DecodeTiming with an injectable clock, include/edge0/timing.h:4-9).
  * When enabled, every expert-matmul launch is bracketed by CUDA events on its stream; b200moe_kernel_times
- * waits for them and returns, for kind 0 (fused gate+up+SwiGLU) and kind 1 (single indexed matmul / down),
- * the number of launches and their summed duration since the last call, then clears the record. */
+ * waits for them and returns, for kind 0 (fused gate+up+SwiGLU), kind 1 (single indexed matmul / down) and kind 2 (dense
+ * products: b200moe_mul_mat, the latent projections), the number of launches and their summed duration since the last call.
+ * Do not enable it while a stream is being captured. */
 B200MOE_API int  b200moe_enable_kernel_timing(b200moe_ctx * ctx, int enable);
-B200MOE_API int  b200moe_kernel_times(b200moe_ctx * ctx, int64_t launches[2], double total_ms[2]);
+B200MOE_API int  b200moe_kernel_times(b200moe_ctx * ctx, int64_t launches[3], double total_ms[3]);
 
 /* ---- data formats (reference: ggml_row_size, ggml.h:761; quantize_row_nvfp4_ref, ggml-quants.c:384-417;
  *      dequantize_row_q3_K / _nvfp4, ggml-quants.c:1305-1353, 589-612).  Host memory. */
@@ -171,6 +185,14 @@ B200MOE_API int b200moe_mul_mat_id(b200moe_ctx * ctx, int wtype, const void * as
 B200MOE_API int b200moe_mul_mat(b200moe_ctx * ctx, int wtype, const void * w, int64_t ne00, int64_t ne01, const float * x, int64_t n_tokens,
                                 const float * scale, float * dst, void * stream);
 
+/* The two shared projections of a latent layer as calls of their own (edge0-strata/src/latent/latent_moe.cpp:38-92: xl = D x before
+ * the experts, y = U m behind the combine); the expert-parallel layer runs them on the token's rank.  x: [n_embd, T] in x_type;
+ * xl F32 [n_latent, T]; m F32 [n_latent, T]; out F32 [n_embd, T].  The latent rows are re-quantised by whoever runs the experts:
+ * whatever engine computes them, their quantised (Q8_0) form is the reference's (exact fix-up behind the FP4 engine). */
+B200MOE_API int b200moe_latent_down(b200moe_ctx * ctx, const b200moe_layer * layer, const void * x, int x_type, int32_t n_tokens, float * xl,
+                                    void * stream);
+B200MOE_API int b200moe_latent_up(b200moe_ctx * ctx, const b200moe_layer * layer, const float * m, int32_t n_tokens, float * out, void * stream);
+
 /* The tail of Builder::ffn (forward.cpp:308-310): out[:, t] = sum over slots s = 0..k-1, in that order, of y[:, s, t] * weights[s, t].
  * y F32 [n, k, T], weights F32 [k, T], out F32 [n, T]. */
 B200MOE_API int b200moe_combine(b200moe_ctx * ctx, const float * y, const float * weights, float * out, int64_t n, int64_t k, int64_t n_tokens,
@@ -180,6 +202,30 @@ B200MOE_API int b200moe_combine(b200moe_ctx * ctx, const float * y, const float 
  * returned rows back into slot order.  width must be a multiple of 4. */
 B200MOE_API int b200moe_gather_rows(b200moe_ctx * ctx, const float * src, int64_t src_rows, const int32_t * idx, float * dst, int64_t n_rows,
                                     int64_t width, void * stream);
+
+/* ---- expert-parallel exchange.  The reference has no multi-GPU form of the latent layer (edge0-strata/src/latent/latent_moe.cpp:38-92
+ * runs on one device; its peer experts are staged through the host, src/core/peer_experts.cpp:186-192), so these three entry
+ * points replace nothing: they are the device side of an all-to-all whose split sizes never depend on the routing.
+ *   Expert e lives on rank e / experts_per_rank.  Every rank sends every peer `capacity` SLOTS (capacity >= the rank's routed
+ *   rows T * k, its worst case), so one equal-split all-to-all of n_ranks * capacity slots moves the rows and a second one of
+ *   n_ranks * capacity result rows brings them back, with no count read on the host between routing and the collective.
+ *   A slot is (width + 4) * 4 bytes (b200moe_ep_slot_bytes): the F32 row, the expert id local to the destination rank, padding;
+ *   id -1 marks an empty slot. */
+B200MOE_API int64_t b200moe_ep_slot_bytes(int64_t width);
+/* rows F32 [width, T], ids I32 [k, T] (global expert ids) -> slots [n_ranks][capacity] ordered by destination rank, slot_of I32 [k, T]
+ * (where routed row (t, s) went: dest * capacity + position), fill I32 [n_ranks] scratch (rows per destination afterwards). */
+B200MOE_API int b200moe_ep_pack(b200moe_ctx * ctx, const float * rows, const int32_t * ids, int64_t n_tokens, int64_t k, int64_t width,
+                                int64_t n_ranks, int64_t experts_per_rank, int64_t capacity, void * slots, int32_t * slot_of, int32_t * fill,
+                                void * stream);
+/* The owner's side: `layer` holds this rank's experts as a plain layer of the exchanged width (n_embd = width, n_latent = 0,
+ * n_expert = experts_per_rank; router_w may be NULL).  Every non-empty slot is one routed row: y[slot] = down_e(silu(gate_e x) * up_e x),
+ * the arithmetic of b200moe_ffn with one slot of weight 1.  y F32 [width, n_slots]; rows of empty slots are left untouched. */
+B200MOE_API int b200moe_ep_expert_rows(b200moe_ctx * ctx, const b200moe_layer * layer, const void * slots, int64_t n_slots, float * y,
+                                       void * stream);
+/* Back on the token's rank: out[:, t] = sum over s = 0..k-1, in that order, of back[:, slot_of[s, t]] * weights[s, t]
+ * (the tail of Builder::ffn, forward.cpp:308-310, behind an index).  back F32 [width, n_slots]. */
+B200MOE_API int b200moe_ep_combine(b200moe_ctx * ctx, const float * back, int64_t n_slots, const int32_t * slot_of, const float * weights,
+                                   int64_t n_tokens, int64_t k, int64_t width, float * out, void * stream);
 
 /* Builder::ffn with given routing (forward.cpp:300-311): gate/up mul_mat_id -> silu*up -> down mul_mat_id ->
  * * weights -> sum over slots in slot order.  x: [n_in, T] in x_type; out F32 [n_in, T].
@@ -198,6 +244,17 @@ B200MOE_API int b200moe_layer_forward(b200moe_ctx * ctx, const b200moe_layer * l
 B200MOE_API int b200moe_layer_forward_host(b200moe_ctx * ctx, const b200moe_layer * layer, const void * x_host, int x_type,
                                            int32_t n_tokens, float * out_host, int32_t * ids_host, float * weights_host,
                                            void * stream);
+
+/* ---- probe of the block-scaled FP4 tensor-core instruction (tcgen05.mma kind::mxf4nvf4, UE4M3 scale per 16 values; the reference's only
+ * Blackwell kernel is the warp-level form of it, ggml-cuda/mma.cuh:1186-1214).  Not part of the layer: it pins the operand formats
+ * the FP4 engine relies on and measures the denominator of "% of FP4 peak".  Both allocate and free their own device memory.
+ *   tile: D[128][256] (host, F32) = A[128][256] . B[256][256]^T with one E2M1 code per byte in a_codes / b_codes (row-major, K = 256)
+ *         and one UE4M3 byte per 16 values in sfa [128][16] / sfb [256][16].
+ *   rate: dense TFLOP/s of `rounds` x 4 x n_acc instructions (M = 128, N = n_mma, K = 64) per SM that alternate between n_acc
+ *         accumulators, operands resident in shared memory, every SM busy.  n_mma % 8 == 0, n_acc * n_mma + 48 <= 512. */
+B200MOE_API int b200moe_probe_fp4_tile(int device, const uint8_t * a_codes, const uint8_t * b_codes, const uint8_t * sfa, const uint8_t * sfb,
+                                       float * d_host);
+B200MOE_API int b200moe_probe_fp4_rate(int device, int n_mma, int n_acc, int rounds, double * tflops);
 
 /* Routing without any allocation.  (No counterpart in the reference: its backends always own a workspace.)
  *

@@ -1,6 +1,7 @@
-"""Bookkeeping of the expert-parallel layer (token split, dispatch order, all-to-all split sizes, inverse permutation,
-slot-order combine) exercised with 2 gloo ranks on CPU.  The arithmetic is plugged in from the CPU checker, so the
-result must equal the single-process checker's latent layer bit for bit, for any world size."""
+"""The expert-parallel layer's exchange (token split, fixed-capacity slots per destination, equal-split all-to-alls, slot-order
+combine behind the slot index) exercised with 2 gloo ranks on CPU.  The arithmetic is plugged in from the CPU checker and the
+slot format from its host statement in edge0_b200.expert_parallel, so the result must equal the single-process checker's
+latent layer bit for bit, for any world size."""
 import os
 import socket
 
@@ -12,7 +13,8 @@ import torch.multiprocessing as mp
 
 from edge0_b200 import workloads as W
 from edge0_b200.capi import TYPE_NVFP4
-from edge0_b200.expert_parallel import ExpertParallelLayer, expert_owner, token_range
+from edge0_b200.expert_parallel import (SLOT_EXTRA_WORDS, ExpertParallelLayer, combine_slots, expert_owner, pack_slots, slot_capacity,
+                                        token_range)
 
 
 class CheckerBackend:
@@ -45,12 +47,26 @@ class CheckerBackend:
     def project_up(self, m):
         return torch.from_numpy(self._matvec(self.layer.lat_up, m.numpy(), self.cfg.n_latent, self.layer.lat_up_scale))
 
-    def expert_rows(self, rows, local_eid):
+    def pack(self, xl, ids, world, per, capacity):
+        slots, slot_of = pack_slots(xl.numpy(), ids.numpy(), world, per, capacity)
+        return torch.from_numpy(slots), torch.from_numpy(slot_of)
+
+    def exchange_buffer(self, t):
+        return torch.empty_like(t)
+
+    def expert_rows(self, slots):
+        """slots float32 [n_slots, w + 4]: word w is the local expert id (as int), -1 = empty."""
         L, wt, lib = self.layer, self.cfg.wtype, self.o.lib
-        out = np.zeros((rows.shape[0], self.cfg.n_in), np.float32)
-        for i in range(rows.shape[0]):
-            e = int(local_eid[i]) + self.lo
-            aq = self.o.quantize_activation(wt, rows[i].numpy())
+        w = self.cfg.n_in
+        slots = slots.numpy()
+        assert slots.shape[1] == w + SLOT_EXTRA_WORDS
+        eids = np.ascontiguousarray(slots[:, w]).view(np.int32)
+        out = np.zeros((slots.shape[0], w), np.float32)
+        for i in range(slots.shape[0]):
+            if eids[i] < 0:
+                continue
+            e = int(eids[i]) + self.lo
+            aq = self.o.quantize_activation(wt, np.ascontiguousarray(slots[i, :w]))
             h = np.zeros(self.cfg.n_ff, np.float32)
             for r in range(self.cfg.n_ff):
                 g = np.float32(self.o.vec_dot(wt, self.cfg.n_in, L.gate[e, r], aq))
@@ -64,14 +80,8 @@ class CheckerBackend:
                 out[i, r] = d * L.down_scale[e] if L.down_scale is not None else d
         return torch.from_numpy(out)
 
-    def gather_rows(self, src, idx):
-        return src[idx.long()].contiguous()
-
-    def combine(self, y, w):
-        acc = y[:, 0, :] * w[:, 0:1]
-        for s in range(1, y.shape[1]):
-            acc = acc + y[:, s, :] * w[:, s:s + 1]
-        return acc
+    def combine(self, back, slot_of, w):
+        return torch.from_numpy(combine_slots(back.numpy(), slot_of.numpy(), w.numpy()))
 
 
 def make_case():
@@ -84,11 +94,31 @@ def _worker(rank, world, port, ret):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     cfg, layer, x = make_case()
     lo, hi = token_range(x.shape[0], world, rank)
-    ep = ExpertParallelLayer(CheckerBackend(layer, rank, world), cfg.n_expert, cfg.top_k, rank, world)
+    ep = ExpertParallelLayer(CheckerBackend(layer, rank, world), cfg.n_expert, cfg.top_k, rank, world,
+                             capacity=slot_capacity(x.shape[0], world, cfg.top_k))
     out, ids, w = ep.forward(torch.from_numpy(x[lo:hi]), return_routing=True)
     ret[rank] = (lo, hi, out.numpy(), ids.numpy())
     dist.barrier()
     dist.destroy_process_group()
+
+
+def test_slot_format_round_trip():
+    rng = np.random.default_rng(3)
+    rows = rng.normal(0, 1, (5, 8)).astype(np.float32)
+    ids = np.array([[0, 5], [7, 2], [3, 3], [6, 1], [4, 0]], np.int32)
+    cap = slot_capacity(10, 2, 2)
+    assert cap == 12 and slot_capacity(1, 8, 1) == 4
+    slots, slot_of = pack_slots(rows, ids, 2, 4, cap)
+    eid = slots.view(np.int32)[:, :, 8]
+    assert (eid >= 0).sum() == 10 and sorted(slot_of.reshape(-1).tolist()) == sorted(set(slot_of.reshape(-1).tolist()))
+    for t in range(5):
+        for s_ in range(2):
+            d, p_ = divmod(int(slot_of[t, s_]), cap)
+            assert d == ids[t, s_] // 4 and eid[d, p_] == ids[t, s_] % 4 and np.array_equal(slots[d, p_, :8], rows[t])
+    back = slots.reshape(-1, 12)[:, :8].copy()
+    w = rng.uniform(0, 1, (5, 2)).astype(np.float32)
+    want = rows * w[:, 0:1] + rows * w[:, 1:2]
+    assert np.array_equal(combine_slots(back, slot_of, w), want.astype(np.float32))
 
 
 def test_partition_helpers():

@@ -7,7 +7,11 @@
   `down` goes to the tcgen05 grouped GEMM (`down`/output differ by the tensor core's accumulation error: bar here 2e-4 of
   RMS, measured ~3e-5) and, up to 4096 routed rows, so does gate/up: then `hidden` carries that error too, the reference's
   re-quantisation of `hidden` amplifies it, and the outputs are held to the stated bar of the path, max-abs <= 1e-2 * RMS.
-* Expert path 2 forces the tensor cores wherever the shape allows; path 3 keeps gate/up on the integer kernels.
+* Expert path 2 forces the f16 tensor-core engine wherever the shape allows; path 3 keeps gate/up on the integer kernels.
+* Expert paths 6-8 are the block-scaled FP4 tensor-core engine (exact digit planes of the int8 grid): `hidden` within 5e-5 of RMS;
+  with the fix-up and an integer `down` (path 7) the layer is bit-identical again.
+* Latent layers under a path that lets dense products use the FP4 engine carry its accumulation error through three
+  re-quantisations: they are held to the stated bar on the output, max-abs <= 1e-2 * RMS.
 """
 import os
 
@@ -39,14 +43,21 @@ def expected_engines(cfg, T, path):
     """(gate/up on tensor cores, down on tensor cores, exact re-quantisation fix-up) under the library's documented policy for
     b200moe_set_expert_path."""
     rows = T * cfg.top_k
-    can = cfg.wtype == TYPE_NVFP4 and cfg.n_ff % 128 == 0 and cfg.n_in % 128 == 0 and \
-        all(k in (256, 512, 768, 1024, 2048) for k in (cfg.n_ff, cfg.n_in))
-    many = rows >= 2 * cfg.n_expert
+    widths = (256, 512, 768, 1024, 2048)
+    can_f16 = cfg.wtype == TYPE_NVFP4 and cfg.n_ff % 128 == 0 and cfg.n_in % 128 == 0 and all(k in widths for k in (cfg.n_ff, cfg.n_in))
+    can_fp4 = cfg.wtype == TYPE_NVFP4 and cfg.n_ff % 128 == 0 and cfg.n_in % 256 == 0 and all(k in widths + (4096,) for k in (cfg.n_ff, cfg.n_in))
     latent = bool(cfg.n_latent)
-    gu = can and (path in (2, 4, 5) or (path == 0 and many))
-    down = can and (path in (2, 3, 4) or (path == 0 and many and not latent))
-    fix = gu and (path in (4, 5) or (path == 0 and many and (rows > 4096 or latent)))
-    return gu, down, fix
+    if path == 0:
+        if rows <= 16:
+            return False, False, False
+        if can_fp4 and rows < 24 * cfg.n_expert:
+            return True, True, latent
+        if can_f16 and rows >= 2 * cfg.n_expert:
+            return True, not latent, rows > 4096 or latent
+        return False, False, False
+    table = {1: (False, False, False), 2: (can_f16, can_f16, False), 3: (False, can_f16, False), 4: (can_f16, can_f16, can_f16),
+             5: (can_f16, False, can_f16), 6: (True, True, False), 7: (True, False, True), 8: (True, True, True)}
+    return table[path]
 
 
 def run_and_compare(gpu_ctx, checker, layer, x_np, bf16, path=0):
@@ -67,21 +78,29 @@ def run_and_compare(gpu_ctx, checker, layer, x_np, bf16, path=0):
     assert np.array_equal(ob.weights_norm.cpu().numpy(), r.weights)
     hidden, down, o = ob.hidden.cpu().numpy(), ob.down.cpu().numpy(), out.cpu().numpy()
     errs = dict(hidden=rel_err(hidden, r.hidden), down=rel_err(down, r.down_out), out=rel_err(o, r.out))
-    gu_tensor, down_tensor, fix = expected_engines(layer.cfg, x_np.shape[0], path)
+    T = x_np.shape[0]
+    gu_tensor, down_tensor, fix = expected_engines(layer.cfg, T, path)
+    fp4 = path in (6, 7, 8) or (path == 0 and gu_tensor and T * layer.cfg.top_k < 24 * layer.cfg.n_expert)
+    dense_fp4 = bool(layer.cfg.n_latent) and layer.cfg.wtype == TYPE_NVFP4 and T >= 4 and path not in (1, 5, 7)
+    if dense_fp4:
+        # the latent input already differs by the FP4 engine's accumulation error and is re-quantised: everything behind it is
+        # held to the bar of the path
+        assert errs["hidden"] <= 3 * TOL and errs["down"] <= 3 * TOL and errs["out"] <= TOL, errs
+        return errs
     if not gu_tensor:
         assert np.array_equal(hidden, r.hidden), ("hidden must be bit-identical on the integer gate/up kernels", errs)
     if not gu_tensor and not down_tensor:
         assert np.array_equal(down, r.down_out) and np.array_equal(o, r.out), ("integer path must be bit-identical", errs)
     elif not gu_tensor or fix:
         # tensor-core down: accumulation error only.  With the fix-up the int8 `hidden` is the reference's, so the same bar holds;
-        # with an integer down kernel behind it (latent layers) the rest of the layer is bit-identical.
-        assert errs["hidden"] <= 5e-4, errs
+        # with an integer down kernel behind it the rest of the layer is bit-identical.
+        assert errs["hidden"] <= (5e-5 if fp4 else 5e-4), errs
         if down_tensor:
             assert errs["down"] <= 2e-4 and errs["out"] <= 2e-4, errs
         else:
             assert np.array_equal(down, r.down_out) and np.array_equal(o, r.out), ("exact re-quantisation + integer down must be bit-identical", errs)
     else:
-        assert errs["hidden"] <= 5e-4 and errs["down"] <= 3 * TOL and errs["out"] <= TOL, errs
+        assert errs["hidden"] <= (5e-5 if fp4 else 5e-4) and errs["down"] <= 3 * TOL and errs["out"] <= TOL, errs
     return errs
 
 
@@ -175,7 +194,7 @@ def test_hot_expert_spans_several_token_tiles(gpu_ctx, checker):
     layer.router_bias = layer.router_bias.copy()
     layer.router_bias[3] += 12.0
     x_np = W.make_tokens(cfg, 80, bf16=True)
-    for path in (2, 4, 0):
+    for path in (2, 4, 6, 7, 8, 0):
         errs = run_and_compare(gpu_ctx, checker, layer, x_np, bf16=True, path=path)
         print("hot expert path %d" % path, errs)
 
@@ -191,7 +210,11 @@ def test_c5_latent_layer_full_shape(gpu_ctx, checker):
     # the latent projection moved the output by 3.6e-2 of RMS before the kernels were made bit-exact.  Integer path only.
     errs = run_and_compare(gpu_ctx, checker, layer, x_np, bf16=True, path=1)
     print("c5 errors", errs)
-    # default policy on a latent layer: tensor-core gate/up + exact fix-up + integer down = still bit-identical
+    # tensor-core gate/up + exact fix-up + integer down, integer latent projections: still bit-identical (f16 and FP4 engines)
+    for path in (5, 7):
+        errs = run_and_compare(gpu_ctx, checker, layer, x_np, bf16=True, path=path)
+        print("c5 path %d errors" % path, errs)
+    # default policy on a latent layer: FP4 engine for the latent projections and the experts, with the fix-up
     errs = run_and_compare(gpu_ctx, checker, layer, x_np, bf16=True, path=0)
     print("c5 default-path errors", errs)
 
@@ -218,6 +241,70 @@ def test_tensor_core_path_vs_checker(T, shape, gpu_ctx, checker):
                 out=rel_err(out.cpu().numpy(), r.out))
     print("tensor-core path T=%d" % T, errs)
     assert errs["hidden"] <= 5e-4 and errs["down"] <= 3 * TOL and errs["out"] <= TOL, errs
+
+
+@pytest.mark.parametrize("path", [6, 7, 8])
+@pytest.mark.parametrize("T,shape", [(1, (512, 16, 4, 256)), (5, (512, 16, 4, 256)), (33, (256, 8, 2, 256)), (8, (2048, 128, 8, 768)),
+                                     (64, (2048, 128, 8, 768)), (256, (2048, 128, 8, 768))])
+def test_fp4_tensor_core_paths_vs_checker(T, shape, path, gpu_ctx, checker):
+    """Block-scaled FP4 engine (tcgen05 kind::mxf4nvf4) on NVFP4 experts: weights untouched, activations as exact digit planes of
+    the int8 grid.  Path 6: gate/up and down; 7: gate/up + fix-up + integer down (bit-identical); 8: gate/up + fix-up + FP4 down.
+    256 tokens of the 128-expert shape give experts with more than 14 rows: several token tiles per expert."""
+    H, E, k, I = shape
+    cfg = W.small_config(TYPE_NVFP4, n_embd=H, n_expert=E, top_k=k, n_ff=I, seed=190 + T)
+    layer = W.make_layer(cfg)
+    errs = run_and_compare(gpu_ctx, checker, layer, W.make_tokens(cfg, T, bf16=True), bf16=True, path=path)
+    print("FP4 path %d T=%d" % (path, T), errs)
+
+
+def test_fp4_paths_refuse_other_types(gpu_ctx):
+    cfg = W.small_config(TYPE_Q3_K, seed=4)
+    layer = W.make_layer(cfg)
+    gpu_ctx.set_expert_path(6)
+    try:
+        with pytest.raises(B200MoeError):
+            layer.to_device(gpu_ctx).forward(torch.zeros((4, cfg.n_embd), device="cuda"))
+    finally:
+        gpu_ctx.set_expert_path(0)
+
+
+def test_scale_byte_0x7f_decodes_to_zero(gpu_ctx, checker):
+    """ggml_ue4m3_to_fp32 maps the scale byte 0x7f to zero (to the tensor core it is NaN): the FP4 engine must agree."""
+    cfg = W.small_config(TYPE_NVFP4, seed=11)
+    layer = W.make_layer(cfg)
+    for name in ("gate", "up", "down"):
+        a = getattr(layer, name).copy()
+        blocks = a.reshape(-1, 36)
+        blocks[::7, 1] = 0x7f
+        blocks[::11, 3] = 0x7f
+        setattr(layer, name, a)
+    errs = run_and_compare(gpu_ctx, checker, layer, W.make_tokens(cfg, 24, bf16=True), bf16=True, path=6)
+    print("0x7f scale bytes", errs)
+
+
+def test_dense_product_on_the_fp4_engine(gpu_ctx, checker):
+    """b200moe_mul_mat with at least 4 tokens runs NVFP4 matrices on the FP4 engine (path 0) and on the integer engine (path 1):
+    the two agree to fp32 accumulation error, and the integer one is the reference's dot product bit for bit."""
+    rng = np.random.default_rng(21)
+    K, N, T = 1024, 512, 37
+    wq = moe.quantize_nvfp4(rng.normal(0, 0.02, (N, K)).astype(np.float32))
+    x = rng.normal(0, 1, (T, K)).astype(np.float32)
+    dw, dx = torch.from_numpy(wq).cuda(), torch.from_numpy(x).cuda()
+    gpu_ctx.set_expert_path(1)
+    try:
+        exact = gpu_ctx.mul_mat(TYPE_NVFP4, dw, dx, K)
+        gpu_ctx.synchronize()
+    finally:
+        gpu_ctx.set_expert_path(0)
+    fast = gpu_ctx.mul_mat(TYPE_NVFP4, dw, dx, K)
+    gpu_ctx.synchronize()
+    want = np.zeros((T, N), np.float32)
+    for t in range(T):
+        aq = checker.quantize_activation(TYPE_NVFP4, x[t])
+        for r in range(N):
+            want[t, r] = checker.vec_dot(TYPE_NVFP4, K, wq[r], aq)
+    assert np.array_equal(exact.cpu().numpy(), want)
+    assert rel_err(fast.cpu().numpy(), want) <= 5e-5
 
 
 def test_route_and_ffn_entry_points_compose(gpu_ctx, checker):
