@@ -48,7 +48,6 @@ SIGNATURES = {
     "b200moe_kernel_times": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_double)]),
     "b200moe_row_size": (C.c_int64, [C.c_int, C.c_int64]),
     "b200moe_quantize_nvfp4_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]),
-    "b200moe_quantize_q3_K_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]),
     "b200moe_dequantize_host": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]),
     "b200moe_route": (C.c_int, [C.c_void_p, C.POINTER(Layer), C.c_void_p, C.c_int, C.c_int32, C.c_void_p, C.c_void_p,
                                 C.POINTER(Observe), C.c_void_p]),

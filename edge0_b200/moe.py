@@ -39,17 +39,6 @@ def quantize_nvfp4(w: np.ndarray) -> np.ndarray:
     return out
 
 
-def quantize_q3_K(w: np.ndarray) -> np.ndarray:
-    """float32 [..., n] -> ggml block_q3_K bytes [..., n/256*110] (quantize_row_q3_K_ref, ggml-quants.c:1229-1303)."""
-    w = np.ascontiguousarray(w, dtype=np.float32)
-    n = w.shape[-1]
-    out = np.empty(w.shape[:-1] + (row_size(TYPE_Q3_K, n),), dtype=np.uint8)
-    rc = capi.load().b200moe_quantize_q3_K_host(w.ctypes.data, out.ctypes.data, w.size // n, n)
-    if rc:
-        raise B200MoeError(rc, "quantize_q3_K_host")
-    return out
-
-
 def dequantize(wtype: int, q: np.ndarray, n: int) -> np.ndarray:
     q = np.ascontiguousarray(q, dtype=np.uint8)
     rows = q.size // row_size(wtype, n)

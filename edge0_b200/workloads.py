@@ -3,6 +3,8 @@
 No dataset is involved: every tensor is drawn from a seeded numpy Generator and quantised on the host.
   router   F32 [E, H]   ~ N(0, 0.02)
   experts  gate/up [E, I, n_in], down [E, n_in, I] ~ N(0, 0.02), then Q3_K or NVFP4
+           (Q3_K: through the quantiser the caller passes - the tests pass the checker's, i.e. the reference's algorithm; without
+           one the blocks are drawn directly in the quantised domain with the statistics such draws have, see synth_q3_K)
   x        [T, H] ~ N(0, 1) (F32, or rounded to bf16)
 NVFP4 uses a two-level scheme: each expert matrix is divided by its fp32 tensor scale
 s = amax / (6 * 448) before block quantisation (so the UE4M3 block scales sit in their normal range) and s
@@ -82,10 +84,44 @@ class HostLayer:
                     lat_d=self.lat_down, lat_u=self.lat_up, s_lat_d=self.lat_down_scale, s_lat_u=self.lat_up_scale)
 
 
+# code frequencies (-4 .. 3) of block_q3_K quantised from N(0, sigma) draws by the reference quantiser
+_Q3K_CODE_P = np.array([0.0757, 0.0633, 0.1142, 0.1757, 0.2051, 0.1757, 0.1135, 0.0768])
+
+
+def synth_q3_K(rng: np.random.Generator, shape) -> np.ndarray:
+    """ggml block_q3_K bytes [..., n/256*110] drawn in the QUANTISED domain: 3-bit codes with the frequencies that quantised
+    Gaussian weights show, 6-bit sub-block scales of magnitude 12..32 (one of them the extreme -32, as the quantiser's
+    normalisation leaves it), an fp16 super-block scale near 4.9e-4 of either sign: dequantised values ~ N(0, 0.02).
+    For timing and for kernel tests that need no particular weights; parity tests quantise real draws with the checker."""
+    *lead, n = shape
+    nb = int(np.prod(lead)) * (n // 256)
+    codes = rng.choice(8, size=(nb, 256), p=_Q3K_CODE_P / _Q3K_CODE_P.sum()).astype(np.uint8)      # code + 4
+    sc = (rng.integers(12, 33, (nb, 16)) * rng.choice([-1, 1], (nb, 16))).astype(np.int32)
+    sc[np.arange(nb), rng.integers(0, 16, nb)] = -32
+    sc = np.clip(sc, -32, 31) + 32
+    out = np.zeros((nb, 110), np.uint8)
+    lo2, hb = codes & 3, codes >> 2                      # element idx = 128*half + 32*shift + l
+    for half in range(2):
+        for shift in range(4):
+            cols = slice(128 * half + 32 * shift, 128 * half + 32 * shift + 32)
+            out[:, 32 + 32 * half:64 + 32 * half] |= (lo2[:, cols] << (2 * shift)).astype(np.uint8)
+            out[:, 0:32] |= (hb[:, cols] << (4 * half + shift)).astype(np.uint8)
+    for j in range(16):                                  # 6-bit scales: low 4 bits in nibbles of bytes 0-7, high 2 bits in bytes 8-11
+        l = sc[:, j]
+        if j < 8:
+            out[:, 96 + j] |= (l & 0xF).astype(np.uint8)
+        else:
+            out[:, 96 + j - 8] |= ((l & 0xF) << 4).astype(np.uint8)
+        out[:, 96 + 8 + j % 4] |= ((l >> 4) << (2 * (j // 4))).astype(np.uint8)
+    d = (rng.uniform(3.5e-4, 6.5e-4, nb) * rng.choice([-1.0, 1.0], nb)).astype(np.float16)
+    out[:, 108:110] = d.view(np.uint8).reshape(nb, 2)
+    return out.reshape(*lead, n // 256 * 110)
+
+
 def _quantize(wtype: int, w: np.ndarray, quantize_q3k: Optional[Callable]) -> np.ndarray:
     if wtype == TYPE_NVFP4:
         return moe.quantize_nvfp4(w)
-    return quantize_q3k(w) if quantize_q3k is not None else moe.quantize_q3_K(w)
+    return quantize_q3k(w)
 
 
 CHUNK_EXPERTS = 32
@@ -102,8 +138,11 @@ def _matrix(seed_key, shape, wtype, scaled, quantize_q3k, expert_range=None):
         if e1 <= lo or e0 >= hi:
             continue
         rng = np.random.default_rng(list(seed_key) + [e0 // CHUNK_EXPERTS])
-        w = rng.normal(0.0, 0.02, (e1 - e0,) + tuple(shape[1:])).astype(np.float32)
         a, b = max(lo, e0) - e0, min(hi, e1) - e0
+        if wtype == TYPE_Q3_K and quantize_q3k is None:
+            outs.append(synth_q3_K(rng, (e1 - e0,) + tuple(shape[1:]))[a:b])
+            continue
+        w = rng.normal(0.0, 0.02, (e1 - e0,) + tuple(shape[1:])).astype(np.float32)
         w = w[a:b]
         if scaled:
             s = (np.abs(w).reshape(b - a, -1).max(axis=1) / np.float32(6 * 448)).astype(np.float32)

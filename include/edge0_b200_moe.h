@@ -157,8 +157,6 @@ B200MOE_API int  b200moe_kernel_times(b200moe_ctx * ctx, int64_t launches[3], do
  *      dequantize_row_q3_K / _nvfp4, ggml-quants.c:1305-1353, 589-612).  Host memory. */
 B200MOE_API int64_t b200moe_row_size(int type, int64_t n);
 B200MOE_API int  b200moe_quantize_nvfp4_host(const float * src, void * dst, int64_t nrows, int64_t n_per_row);
-/* quantize_row_q3_K_ref (ggml-quants.c:1229-1303 with make_q3_quants, :697-754) */
-B200MOE_API int  b200moe_quantize_q3_K_host(const float * src, void * dst, int64_t nrows, int64_t n_per_row);
 B200MOE_API int  b200moe_dequantize_host(int type, const void * src, float * dst, int64_t nrows, int64_t n_per_row);
 
 /* ---- compute.  `stream` is a cudaStream_t (NULL = default stream); calls are asynchronous on it. */

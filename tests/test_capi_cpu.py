@@ -54,18 +54,6 @@ def test_no_device_means_no_compute():
     assert lib.b200moe_reserve(None, None, 1) == 1   # null context is an argument error, not a crash
 
 
-def test_q3k_quantiser_matches_reference_bytes():
-    """Product quantiser vs the compiled reference quantiser (when present) and vs the stored reference bytes of the fixture."""
-    z = np.load(os.path.join(ROOT, "tests", "golden", "kat.npz"))
-    assert np.array_equal(moe.quantize_q3_K(z["q3k_w"]), z["q3k_wq"])
-    from oracle import oracle as O
-    if O.have_reference():
-        rng = np.random.default_rng(12)
-        w = rng.normal(0, 0.02, (4, 24, 768)).astype(np.float32)
-        w[0, 0, :32] = 0
-        assert np.array_equal(moe.quantize_q3_K(w), O.reference().quantize(TYPE_Q3_K, w))
-
-
 def test_ggml_adapter_loads_without_gpu():
     """libggml-b200.so (built where the host application's ggml headers are present) loads next to that ggml, exports
     the entry points include/ggml-b200.h declares, and reports no device on a machine without a B200."""

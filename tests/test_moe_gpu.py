@@ -35,8 +35,9 @@ def rel_err(got, want):
 
 
 def q3k_quantizer(checker):
-    """The product's host quantiser (bit-identical to quantize_row_q3_K_ref, see tests/test_capi_cpu.py)."""
-    return moe.quantize_q3_K
+    """The checker's Q3_K weight quantiser: the reference's own when it is compiled, else its restatement (same bytes, see
+    tests/test_oracle.py)."""
+    return lambda w: checker.quantize(TYPE_Q3_K, w)
 
 
 def expected_engines(cfg, T, path):

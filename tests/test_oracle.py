@@ -97,3 +97,25 @@ def test_restatement_matches_compiled_reference(wname, latent, bias, restatement
     b = restatement.moe_layer(x=x, **layer.checker_kwargs())
     for f in FIELDS:
         assert np.array_equal(getattr(a, f), getattr(b, f)), f
+
+
+def test_restated_q3k_quantiser_matches_reference_bytes(restatement):
+    """The restated weight quantiser (quantize_row_q3_K_ref) against the reference's bytes stored in the fixture and, when the
+    compiled reference is present, against it on fresh draws with zero blocks and large values."""
+    z = np.load(os.path.join(GOLD, "kat.npz"))
+    assert np.array_equal(restatement.quantize(TYPE_Q3_K, z["q3k_w"]), z["q3k_wq"])
+    if O.have_reference():
+        rng = np.random.default_rng(12)
+        w = rng.normal(0, 0.02, (4, 24, 768)).astype(np.float32)
+        w[0, 0, :32] = 0
+        w[1] *= 3000
+        assert np.array_equal(restatement.quantize(TYPE_Q3_K, w), O.reference().quantize(TYPE_Q3_K, w))
+
+
+def test_synthetic_q3k_blocks_are_valid_and_gaussian_like(restatement):
+    """workloads.synth_q3_K draws block_q3_K bytes in the quantised domain (bench inputs): they must decode, with the spread the
+    configurations ask for."""
+    q = W.synth_q3_K(np.random.default_rng(5), (64, 1024))
+    assert q.shape == (64, 440) and q.dtype == np.uint8
+    w = restatement.dequantize(TYPE_Q3_K, q, 1024)
+    assert np.isfinite(w).all() and 0.012 < float(w.std()) < 0.03 and abs(float(w.mean())) < 2e-3

@@ -31,12 +31,15 @@ def call_noalloc(layer: moe.MoeLayer, x: torch.Tensor):
 def test_noalloc_route_equals_route_twice_in_a_row():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
+    from oracle import oracle as O
     ctx = moe.Context(0)
     cfg = W.CONFIGS["c2_nvfp4"]
     small = W.small_config(TYPE_NVFP4, n_embd=cfg.n_embd, n_expert=cfg.n_expert, top_k=cfg.top_k, n_ff=256, seed=41)
-    layer = W.make_layer(small).to_device(ctx)
+    host = W.make_layer(small)
+    layer = host.to_device(ctx)
     for call, T in enumerate((64, 37)):            # two calls in a row share the built-in array
-        x = torch.from_numpy(W.make_tokens(small, T, bf16=True, seed_offset=call)).cuda().to(torch.bfloat16)
+        x_np = W.make_tokens(small, T, bf16=True, seed_offset=call)
+        x = torch.from_numpy(x_np).cuda().to(torch.bfloat16)
         torch.cuda.synchronize()
         free_before = torch.cuda.mem_get_info()[0]
         rc, msg, ids, w = call_noalloc(layer, x)
@@ -48,6 +51,9 @@ def test_noalloc_route_equals_route_twice_in_a_row():
         ctx.synchronize()
         assert torch.equal(ids, ids_ref), f"call {call}: expert ids differ"
         assert torch.equal(w, w_ref), f"call {call}: route weights differ"
+        # and directly against the checker (the reference's CPU path): ids and route weights bit for bit
+        want = O.best_checker().moe_layer(x=x_np, **host.checker_kwargs())
+        assert np.array_equal(ids.cpu().numpy(), want.ids) and np.array_equal(w.cpu().numpy(), want.weights), f"call {call}"
     # beyond the built-in scratch: refused with a message, nothing launched
     big = torch.zeros((capi.NOALLOC_MAX_LOGITS // small.n_expert + 1, small.n_embd), device="cuda")
     rc, msg, _, _ = call_noalloc(layer, big)
