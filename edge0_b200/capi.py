@@ -28,6 +28,11 @@ class Observe(C.Structure):
                                           "ffn_moe_hidden", "ffn_moe_down")]
 
 
+class Tensor(C.Structure):
+    """b200moe_tensor: data pointer, ne[4] elements, nb[4] byte strides (ggml's description of a tensor)."""
+    _fields_ = [("data", C.c_void_p), ("ne", C.c_int64 * 4), ("nb", C.c_int64 * 4)]
+
+
 class Counters(C.Structure):
     _fields_ = [(n, C.c_int64) for n in ("tokens", "experts_touched", "weight_bytes", "kernel_launches", "fixup_overflow")]
 
@@ -68,6 +73,14 @@ SIGNATURES = {
                               C.POINTER(Observe), C.c_void_p]),
     "b200moe_layer_forward": (C.c_int, [C.c_void_p, C.POINTER(Layer), C.c_void_p, C.c_int, C.c_int32, C.c_void_p,
                                         C.POINTER(Observe), C.c_void_p]),
+    "b200moe_op_binary": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),
+    "b200moe_op_unary": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(Tensor), C.POINTER(Tensor), C.c_float, C.c_float, C.c_void_p]),
+    "b200moe_op_repeat": (C.c_int, [C.c_void_p, C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),
+    "b200moe_op_get_rows": (C.c_int, [C.c_void_p, C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),
+    "b200moe_op_sum_rows": (C.c_int, [C.c_void_p, C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),
+    "b200moe_op_soft_max": (C.c_int, [C.c_void_p, C.POINTER(Tensor), C.POINTER(Tensor), C.c_float, C.c_void_p]),
+    "b200moe_op_argsort_desc": (C.c_int, [C.c_void_p, C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),
+    "b200moe_op_mul_mat_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "b200moe_probe_fp4_tile": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200moe_probe_fp4_rate": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double)]),
     "b200moe_route_noalloc": (C.c_int, [C.c_int, C.POINTER(Layer), C.c_void_p, C.c_int, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,

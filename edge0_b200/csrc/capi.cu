@@ -23,6 +23,7 @@
 #include "expert_gemv.cuh"
 #include "expert_mma.cuh"
 #include "fp4_probe.cuh"
+#include "graph_ops.cuh"
 #include "requant_fixup.cuh"
 #include "router.cuh"
 
@@ -539,7 +540,7 @@ bool fp4_supported(int wtype, int n_in, int n_ff) { return wtype == TYPE_NVFP4 &
 int launch_act_planes(b200moe_ctx * ctx, ActQuant act, const float * src, const int32_t * ids, int rows, int k, int n_ids, int ne11, int n_as,
                       cudaStream_t st) {
     Plan & p = ctx->plan;
-    PlaneOut po{ reinterpret_cast<uint8_t *>(p.afp16), p.asf, p.arow_scale };
+    PlaneOut po{ reinterpret_cast<uint8_t *>(p.afp16), p.asf, p.arow_scale, p.groups.pos /* free once the rows are grouped */ };
     const int * tiles = p.groups.cost + 3 * (n_as + 1);
     if (src) act_planes_kernel<true><<<rows, 256, 0, st>>>(act, src, k, p.groups.perm, ids, p.groups.offsets, tiles, p.groups.meta, rows, k, n_ids, ne11, n_as, po);
     else act_planes_kernel<false><<<rows, 256, 0, st>>>(act, nullptr, 0, p.groups.perm, ids, p.groups.offsets, tiles, p.groups.meta, rows, k, n_ids, ne11, n_as, po);
@@ -550,7 +551,7 @@ Fp4Params fp4_params(b200moe_ctx * ctx, const float * s0, const float * s1, floa
     Plan & p = ctx->plan;
     Fp4Params f{};
     f.scale0 = s0; f.scale1 = s1; f.sf = p.asf; f.row_scale = p.arow_scale; f.offsets = p.groups.offsets; f.perm = p.groups.perm;
-    f.active = p.groups.active; f.meta = p.groups.meta; f.tile_of_expert = p.groups.cost + 3 * (n_as + 1); f.out = out; f.n_out = n_out;
+    f.active = p.groups.active; f.meta = p.groups.meta; f.tile_of_expert = p.groups.cost + 3 * (n_as + 1); f.tile_expert = p.groups.pos; f.out = out; f.n_out = n_out;
     f.n_as = n_as; f.err = ctx->d_err; f.prof = nullptr;
     return f;
 }
@@ -582,6 +583,13 @@ int launch_quantize(b200moe_ctx * ctx, const XT * src, int64_t stride, ActQuant 
 template <typename XT>
 int launch_logits(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, cudaStream_t st) {
     Plan & p = ctx->plan;
+    if (T >= 16) {   // batches: 4 experts x 8 tokens per warp
+        constexpr int TE = 4, TT = 8;
+        const int64_t warps = (int64_t) ((l->n_expert + TE - 1) / TE) * ((T + TT - 1) / TT);
+        router_logits_tiled_kernel<TE, TT, XT><<<(unsigned) ((warps * 32 + 255) / 256), 256, 0, st>>>(l->router_w, l->router_bias, x, p.logits, l->n_embd,
+                                                                                                   l->n_expert, T, p.groups.counts, l->n_expert);
+        return check_launch(ctx, "router_logits");
+    }
     constexpr int TT = 4;
     const int64_t warps = (int64_t) l->n_expert * ((T + TT - 1) / TT);
     const int blocks = (int) ((warps * 32 + 255) / 256);
@@ -1511,6 +1519,139 @@ int b200moe_ep_combine(b200moe_ctx * ctx, const float * back, int64_t n_slots, c
     dim3 grid((unsigned) ((width / 4 + 255) / 256), (unsigned) T);
     ep_combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(back, slot_of, weights, out, (int) width, (int) k, (int) T, (int) n_slots);
     return check_launch(ctx, "ep_combine");
+}
+
+// ---- single graph operators (graph_ops.cuh) ------------------------------------------------------------------------------
+
+namespace {
+
+bool to_view(const b200moe_tensor * t, TensorView & v, int64_t * count) {
+    if (!t || !t->data) return false;
+    v.data = static_cast<char *>(t->data);
+    int64_t n = 1;
+    for (int i = 0; i < 4; ++i) {
+        if (t->ne[i] <= 0 || t->nb[i] < 0) return false;
+        v.ne[i] = t->ne[i];
+        v.nb[i] = t->nb[i];
+        n *= t->ne[i];
+    }
+    if (t->nb[0] % 4) return false;
+    if (count) *count = n;
+    return n < ((int64_t) 1 << 40);
+}
+
+bool broadcastable(const TensorView & small, const TensorView & big) {
+    for (int i = 0; i < 4; ++i) if (big.ne[i] % small.ne[i]) return false;
+    return true;
+}
+
+int grid_for(int64_t n) { return (int) std::min<int64_t>((n + 255) / 256, 148 * 32); }
+
+}  // namespace
+
+int b200moe_op_binary(b200moe_ctx * ctx, int op, const b200moe_tensor * a, const b200moe_tensor * b, const b200moe_tensor * dst, void * stream) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    TensorView va, vb, vd;
+    int64_t n = 0;
+    if (op < 0 || op > 2 || !to_view(a, va, nullptr) || !to_view(b, vb, nullptr) || !to_view(dst, vd, &n)) return fail(ctx, B200MOE_ERR_INVALID_ARG, "bad operator or tensor");
+    for (int i = 0; i < 4; ++i) if (va.ne[i] != vd.ne[i]) return fail(ctx, B200MOE_ERR_INVALID_ARG, "dst must have the shape of the first operand");
+    if (!broadcastable(vb, vd)) return fail(ctx, B200MOE_ERR_INVALID_ARG, "second operand does not repeat over the first");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    op_binary_kernel<<<grid_for(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(op, va, vb, vd);
+    return check_launch(ctx, "op_binary");
+}
+
+int b200moe_op_unary(b200moe_ctx * ctx, int op, const b200moe_tensor * a, const b200moe_tensor * dst, float p0, float p1, void * stream) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    TensorView va, vd;
+    int64_t n = 0;
+    if (op < 0 || op > 2 || !to_view(a, va, nullptr) || !to_view(dst, vd, &n)) return fail(ctx, B200MOE_ERR_INVALID_ARG, "bad operator or tensor");
+    for (int i = 0; i < 4; ++i) if (va.ne[i] != vd.ne[i]) return fail(ctx, B200MOE_ERR_INVALID_ARG, "shapes differ");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    op_unary_kernel<<<grid_for(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(op, va, vd, p0, p1);
+    return check_launch(ctx, "op_unary");
+}
+
+int b200moe_op_repeat(b200moe_ctx * ctx, const b200moe_tensor * a, const b200moe_tensor * dst, void * stream) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    TensorView va, vd;
+    int64_t n = 0;
+    if (!to_view(a, va, nullptr) || !to_view(dst, vd, &n) || !broadcastable(va, vd)) return fail(ctx, B200MOE_ERR_INVALID_ARG, "bad tensor or shapes do not repeat");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    op_repeat_kernel<<<grid_for(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(va, vd);
+    return check_launch(ctx, "op_repeat");
+}
+
+int b200moe_op_get_rows(b200moe_ctx * ctx, const b200moe_tensor * a, const b200moe_tensor * ids, const b200moe_tensor * dst, void * stream) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    TensorView va, vi, vd;
+    int64_t rows = 0;
+    if (!to_view(a, va, nullptr) || !to_view(ids, vi, &rows) || !to_view(dst, vd, nullptr)) return fail(ctx, B200MOE_ERR_INVALID_ARG, "bad tensor");
+    if (vi.ne[3] != 1 || vd.ne[0] != va.ne[0] || vd.ne[1] != vi.ne[0] || vd.ne[2] != vi.ne[1] || vd.ne[3] != vi.ne[2] ||
+        (va.ne[2] != vi.ne[1] && va.ne[2] != 1) || (va.ne[3] != vi.ne[2] && va.ne[3] != 1))
+        return fail(ctx, B200MOE_ERR_INVALID_ARG, "get_rows shapes");
+    if (va.ne[2] == 1) va.nb[2] = 0;
+    if (va.ne[3] == 1) va.nb[3] = 0;
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    op_get_rows_kernel<<<(unsigned) ((rows * 32 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(va, vi, vd, ctx->d_err);
+    return check_launch(ctx, "op_get_rows");
+}
+
+int b200moe_op_sum_rows(b200moe_ctx * ctx, const b200moe_tensor * a, const b200moe_tensor * dst, void * stream) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    TensorView va, vd;
+    if (!to_view(a, va, nullptr) || !to_view(dst, vd, nullptr)) return fail(ctx, B200MOE_ERR_INVALID_ARG, "bad tensor");
+    if (vd.ne[0] != 1 || vd.ne[1] != va.ne[1] || vd.ne[2] != va.ne[2] || vd.ne[3] != va.ne[3]) return fail(ctx, B200MOE_ERR_INVALID_ARG, "sum_rows shapes");
+    const int64_t rows = va.ne[1] * va.ne[2] * va.ne[3];
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    op_sum_rows_kernel<<<(unsigned) ((rows + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(va, vd);
+    return check_launch(ctx, "op_sum_rows");
+}
+
+int b200moe_op_soft_max(b200moe_ctx * ctx, const b200moe_tensor * a, const b200moe_tensor * dst, float scale, void * stream) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    TensorView va, vd;
+    if (!to_view(a, va, nullptr) || !to_view(dst, vd, nullptr)) return fail(ctx, B200MOE_ERR_INVALID_ARG, "bad tensor");
+    for (int i = 0; i < 4; ++i) if (va.ne[i] != vd.ne[i]) return fail(ctx, B200MOE_ERR_INVALID_ARG, "shapes differ");
+    if (va.ne[0] % 8 || va.ne[0] > 1024) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "soft_max rows must be multiples of 8, at most 1024 long");
+    const int64_t rows = va.ne[1] * va.ne[2] * va.ne[3];
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    op_soft_max_kernel<<<(unsigned) ((rows * 32 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(va, vd, scale);
+    return check_launch(ctx, "op_soft_max");
+}
+
+int b200moe_op_argsort_desc(b200moe_ctx * ctx, const b200moe_tensor * a, const b200moe_tensor * dst, void * stream) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    TensorView va, vd;
+    if (!to_view(a, va, nullptr) || !to_view(dst, vd, nullptr)) return fail(ctx, B200MOE_ERR_INVALID_ARG, "bad tensor");
+    for (int i = 0; i < 4; ++i) if (va.ne[i] != vd.ne[i]) return fail(ctx, B200MOE_ERR_INVALID_ARG, "shapes differ");
+    if (va.ne[0] > 1024) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "argsort rows of at most 1024 values");
+    const int64_t rows = va.ne[1] * va.ne[2] * va.ne[3];
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    op_argsort_desc_kernel<<<(unsigned) rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(va, vd);
+    return check_launch(ctx, "op_argsort");
+}
+
+// dst[e, t] = dot(w[:, e], x[:, t]) in ggml_vec_dot_f32's summation order (the router matmul's kernel without a router behind it)
+int b200moe_op_mul_mat_f32(b200moe_ctx * ctx, const float * w, int64_t ne00, int64_t ne01, const float * x, int64_t T, float * dst, void * stream) {
+    if (!ctx) return B200MOE_ERR_INVALID_ARG;
+    if (T == 0) return B200MOE_OK;
+    if (!w || !x || !dst || ne00 <= 0 || ne01 <= 0 || T < 0) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null pointer or non-positive size");
+    if (ne00 % 32) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "F32 matmul rows must be multiples of 32 long");
+    if (ne01 * T > ((int64_t) 1 << 30)) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "result too large");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    if (T >= 16 && ne01 >= 4) {
+        constexpr int TE = 4, TT = 8;
+        const int64_t warps = ((ne01 + TE - 1) / TE) * ((T + TT - 1) / TT);
+        router_logits_tiled_kernel<TE, TT, float><<<(unsigned) ((warps * 32 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(w, nullptr, x, dst, (int) ne00,
+                                                                                                                                   (int) ne01, (int) T, nullptr, 0);
+    } else {
+        constexpr int TT = 4;
+        const int64_t warps = ne01 * ((T + TT - 1) / TT);
+        router_logits_kernel<TT, float><<<(unsigned) ((warps * 32 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(w, nullptr, x, dst, (int) ne00,
+                                                                                                                        (int) ne01, (int) T, nullptr, 0);
+    }
+    return check_launch(ctx, "op_mul_mat_f32");
 }
 
 // ---- probe of the block-scaled FP4 instruction (fp4_probe.cuh) -----------------------------------------------------------

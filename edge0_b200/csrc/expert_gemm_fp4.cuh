@@ -89,12 +89,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 // ---- activation planes ---------------------------------------------------------------------------------------------------
 // Expert-sorted routed row i -> seven plane rows 7i .. 7i+6 of `planes` (K/2 bytes each, ggml nibble order inside every
 // 16-block), its scale bytes in the scale tiles of its token tile, and the power of two the epilogue multiplies with.
-//   tile_of_expert[e]: index of expert e's first token tile (prefix of ceil(rows_e / 14))
+//   tile_of_expert[e]: index of expert e's first token tile (prefix of ceil(rows_e / 14)); tile_expert[tile]: the inverse
 //   sf tiles: [tile][K / 256][4 steps][512 bytes], byte for (plane row n of the tile, 16-block g of the step) at sf_tile_offset(n) + g
 struct PlaneOut {
     uint8_t * planes;       // [rows * 7][K / 2]
     uint8_t * sf;           // [tiles][K / 256][2048]
     float *   row_scale;    // [rows] by sorted position
+    int *     tile_expert;  // [tiles] expert of every token tile
 };
 
 // digits, codes and scale bytes of one item: 16-block g, byte j (elements 16g + j and 16g + j + 8) with int8 values q0, q1 and
@@ -148,6 +149,7 @@ __global__ void __launch_bounds__(256) act_planes_kernel(ActQuant act, const flo
     const int row_beg = offsets[e];
     const int in_tile = (i - row_beg) % FP4_RPT;
     const int tile = tile_of_expert[e] + (i - row_beg) / FP4_RPT;
+    if (in_tile == 0 && tid == 0) out.tile_expert[tile] = e;
     const int nb32 = K / 32;
     uint8_t * prow = out.planes + (size_t) i * FP4_PLANES * (K / 2);
     uint8_t * sft = out.sf + (size_t) tile * (K / 256) * FP4_SF_TILE;
@@ -227,7 +229,8 @@ struct Fp4Params {
     const int * perm;       // [rows]
     const int * active;     // [n_as]
     const int * meta;
-    const int * tile_of_expert;
+    const int * tile_of_expert;   // [n_as + 1]: first token tile of every expert, total number of tiles at the end
+    const int * tile_expert;      // [tiles]
     float * out;            // [rows][n_out] indexed by routed row
     int n_out;
     int n_as;
@@ -296,9 +299,22 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
     tc_fence_after();
     const uint32_t tmem = s_tmem;
 
-    const int n_active = p.meta[0];
+    // Work unit = (token tile of an expert, feature tile): every role walks the same units, blockIdx.x, blockIdx.x + gridDim.x, ...
+    // Feature tiles of one token tile are neighbours in that order, so they find the tile's planes in L2; token tiles of one
+    // expert follow each other, so a second pass over an expert's weights comes from L2 as well.
     const int f_tiles = p.n_out / FEAT;
-    const int n_items = n_active * f_tiles;
+    const int n_units = p.tile_of_expert[p.n_as] * f_tiles;
+    struct Unit { int e, ft, row0, nt, tile; };
+    auto unit_at = [&](int u) {
+        Unit w;
+        w.tile = u / f_tiles;
+        w.ft = u - w.tile * f_tiles;
+        w.e = p.tile_expert[w.tile];
+        const int row_beg = p.offsets[w.e], t0 = (w.tile - p.tile_of_expert[w.e]) * FP4_RPT;
+        w.row0 = row_beg + t0;                                   // first expert-sorted row of the token tile
+        w.nt = min(FP4_RPT, p.offsets[w.e + 1] - w.row0);
+        return w;
+    };
     // weight stage: [A0][A1][SFA0][SFA1]; activation stage: [B][SFB]
     constexpr uint32_t OFF_A1 = C::A_TILE, OFF_SFA = 2 * C::A_TILE, OFF_SFB = C::B_TILE;
 
@@ -307,23 +323,19 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
         if (lane == 0) {
             Ring raw;
             FP4_PROF_DECL();
-            for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
-                const int a = item / f_tiles, ft = item % f_tiles;
-                const int e = p.active[a];
-                const int n_e = p.offsets[e + 1] - p.offsets[e];
-                const int row0 = e * p.n_out + ft * FEAT;
-                for (int t0 = 0; t0 < n_e && !s_abort; t0 += FP4_RPT) {
-                    for (int kc = 0; kc < KC; ++kc) {
-                        FP4_PROF_T0();
-                        if (!wait_or_abort<200>(&raw_empty[raw.stage], raw.phase ^ 1u, &s_abort, p.err)) break;
-                        FP4_PROF_ADD(0);
-                        uint8_t * dst = raws + (size_t) raw.stage * C::RAW_STAGE;
-                        mbar_arrive_expect_tx(&raw_full[raw.stage], C::RAW_STAGE);
-                        tma_load_2d(dst, &map_w0, kc * GEMM_RAW_ROW, row0, &raw_full[raw.stage]);
-                        if (DUAL) tma_load_2d(dst + 128 * GEMM_RAW_ROW, &map_w1, kc * GEMM_RAW_ROW, row0, &raw_full[raw.stage]);
-                        else tma_load_2d(dst + 128 * GEMM_RAW_ROW, &map_w0, kc * GEMM_RAW_ROW, row0 + 128, &raw_full[raw.stage]);
-                        raw.template advance<RS>();
-                    }
+            for (int u = blockIdx.x; u < n_units && !s_abort; u += gridDim.x) {
+                const Unit w = unit_at(u);
+                const int row0 = w.e * p.n_out + w.ft * FEAT;
+                for (int kc = 0; kc < KC; ++kc) {
+                    FP4_PROF_T0();
+                    if (!wait_or_abort<200>(&raw_empty[raw.stage], raw.phase ^ 1u, &s_abort, p.err)) break;
+                    FP4_PROF_ADD(0);
+                    uint8_t * dst = raws + (size_t) raw.stage * C::RAW_STAGE;
+                    mbar_arrive_expect_tx(&raw_full[raw.stage], C::RAW_STAGE);
+                    tma_load_2d(dst, &map_w0, kc * GEMM_RAW_ROW, row0, &raw_full[raw.stage]);
+                    if (DUAL) tma_load_2d(dst + 128 * GEMM_RAW_ROW, &map_w1, kc * GEMM_RAW_ROW, row0, &raw_full[raw.stage]);
+                    else tma_load_2d(dst + 128 * GEMM_RAW_ROW, &map_w0, kc * GEMM_RAW_ROW, row0 + 128, &raw_full[raw.stage]);
+                    raw.template advance<RS>();
                 }
             }
             FP4_PROF_STORE(0, 1);
@@ -333,22 +345,18 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
         if (lane == 0) {
             Ring act;
             FP4_PROF_DECL();
-            for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
-                const int e = p.active[item / f_tiles];
-                const int row_beg = p.offsets[e], n_e = p.offsets[e + 1] - row_beg;
-                const int tile0 = p.tile_of_expert[e];
-                for (int t0 = 0; t0 < n_e && !s_abort; t0 += FP4_RPT) {
-                    const uint8_t * sft = p.sf + (size_t) (tile0 + t0 / FP4_RPT) * KC * FP4_SF_TILE;
-                    for (int kc = 0; kc < KC; ++kc) {
-                        FP4_PROF_T0();
-                        if (!wait_or_abort<100>(&act_empty[act.stage], act.phase ^ 1u, &s_abort, p.err)) break;
-                        FP4_PROF_ADD(0);
-                        uint8_t * st = acts + (size_t) act.stage * C::ACT_STAGE;
-                        mbar_arrive_expect_tx(&act_full[act.stage], C::B_BYTES + FP4_SF_TILE);
-                        tma_load_2d(st, &map_planes, kc * 128, FP4_PLANES * (row_beg + t0), &act_full[act.stage]);
-                        bulk_g2s(st + OFF_SFB, sft + (size_t) kc * FP4_SF_TILE, FP4_SF_TILE, &act_full[act.stage]);
-                        act.template advance<AS>();
-                    }
+            for (int u = blockIdx.x; u < n_units && !s_abort; u += gridDim.x) {
+                const Unit w = unit_at(u);
+                const uint8_t * sft = p.sf + (size_t) w.tile * KC * FP4_SF_TILE;
+                for (int kc = 0; kc < KC; ++kc) {
+                    FP4_PROF_T0();
+                    if (!wait_or_abort<100>(&act_empty[act.stage], act.phase ^ 1u, &s_abort, p.err)) break;
+                    FP4_PROF_ADD(0);
+                    uint8_t * st = acts + (size_t) act.stage * C::ACT_STAGE;
+                    mbar_arrive_expect_tx(&act_full[act.stage], C::B_BYTES + FP4_SF_TILE);
+                    tma_load_2d(st, &map_planes, kc * 128, FP4_PLANES * w.row0, &act_full[act.stage]);
+                    bulk_g2s(st + OFF_SFB, sft + (size_t) kc * FP4_SF_TILE, FP4_SF_TILE, &act_full[act.stage]);
+                    act.template advance<AS>();
                 }
             }
             FP4_PROF_STORE(2, 1);
@@ -358,11 +366,9 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
         if (lane == 0) {
             Ring tile, act, acc;
             FP4_PROF_DECL();
-            for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
-                const int e = p.active[item / f_tiles];
-                const int n_e = p.offsets[e + 1] - p.offsets[e];
-                for (int t0 = 0; t0 < n_e && !s_abort; t0 += FP4_RPT) {
-                    const int nt = min(FP4_RPT, n_e - t0);
+            for (int u = blockIdx.x; u < n_units && !s_abort; u += gridDim.x) {
+                {
+                    const int nt = unit_at(u).nt;
                     const uint32_t idesc = umma_idesc_fp4((FP4_PLANES * nt + 7) & ~7);
                     {
                         FP4_PROF_T0();
@@ -418,15 +424,13 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
         Ring acc;
         FP4_PROF_DECL();
         const int q = warp & 3;                 // TMEM lane quarter this warp may read
-        for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
-            const int a = item / f_tiles, ft = item % f_tiles;
-            const int e = p.active[a];
-            const int row_beg = p.offsets[e], n_e = p.offsets[e + 1] - row_beg;
-            const float sc0 = p.scale0 ? p.scale0[e] : 1.0f;
-            const float sc1 = DUAL ? (p.scale1 ? p.scale1[e] : 1.0f) : sc0;
-            const int feature = ft * FEAT + q * 32 + lane;
-            for (int t0 = 0; t0 < n_e && !s_abort; t0 += FP4_RPT) {
-                const int nt = min(FP4_RPT, n_e - t0);
+        for (int u = blockIdx.x; u < n_units && !s_abort; u += gridDim.x) {
+            const Unit w = unit_at(u);
+            const float sc0 = p.scale0 ? p.scale0[w.e] : 1.0f;
+            const float sc1 = DUAL ? (p.scale1 ? p.scale1[w.e] : 1.0f) : sc0;
+            const int feature = w.ft * FEAT + q * 32 + lane;
+            {
+                const int nt = w.nt;
                 // lanes leave the polling loop one by one: the vote reconverges the warp (tcgen05.ld below needs all of it)
                 {
                     FP4_PROF_T0();
@@ -442,7 +446,7 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
 #pragma unroll
                     for (int rr = 0; rr < 4; ++rr) {
                         if (g + rr < nt) {
-                            const int i = row_beg + t0 + g + rr;
+                            const int i = w.row0 + g + rr;
                             const float rs = p.row_scale[i];
                             // sum_p 8^p * plane_p, highest plane first
                             float x0 = v0[7 * rr + 6], x1 = v1[7 * rr + 6];
@@ -477,10 +481,8 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
         const uint32_t raw_off = (uint32_t) dq * GEMM_RAW_ROW;
         Ring raw, tile;
         FP4_PROF_DECL();
-        for (int item = blockIdx.x; item < n_items && !s_abort; item += gridDim.x) {
-            const int e = p.active[item / f_tiles];
-            const int n_e = p.offsets[e + 1] - p.offsets[e];
-            for (int t0 = 0; t0 < n_e && !s_abort; t0 += FP4_RPT) {
+        for (int u = blockIdx.x; u < n_units && !s_abort; u += gridDim.x) {
+            {
                 for (int kc = 0; kc < KC && !s_abort; ++kc) {
                     {
                         FP4_PROF_T0();

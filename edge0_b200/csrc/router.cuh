@@ -70,6 +70,62 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const float * __rest
     }
 }
 
+// Register-tiled form for batches: one warp per (TE experts x TT tokens).  Every (expert, token) pair still runs the reference's
+// chains - lane l owns elements l, l + 32, ... in increasing order - but a weight value now meets TT tokens and an activation value
+// TE experts per load, so the kernel is bound by FMAs instead of by re-reading x once per expert from L2.
+template <int TE, int TT, typename XT>
+__global__ void __launch_bounds__(256) router_logits_tiled_kernel(const float * __restrict__ W, const float * __restrict__ bias,
+                                                                 const XT * __restrict__ x, float * __restrict__ logits, int H, int E, int T,
+                                                                 int * __restrict__ zero_buf, int zero_n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    if (blockIdx.x == 0)
+        for (int i = threadIdx.x; i < zero_n; i += blockDim.x) zero_buf[i] = 0;
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const int n_te = (E + TE - 1) / TE, n_tt = (T + TT - 1) / TT;
+    if (warp >= n_te * n_tt) return;
+    const int e0 = (warp % n_te) * TE, t0 = (warp / n_te) * TT;
+    float acc[TE][TT];
+#pragma unroll
+    for (int a = 0; a < TE; ++a)
+#pragma unroll
+        for (int b = 0; b < TT; ++b) acc[a][b] = 0.0f;
+    const float * wrow[TE];
+    const XT * xrow[TT];
+#pragma unroll
+    for (int a = 0; a < TE; ++a) wrow[a] = W + (size_t) min(e0 + a, E - 1) * H;
+#pragma unroll
+    for (int b = 0; b < TT; ++b) xrow[b] = x + (size_t) min(t0 + b, T - 1) * H;
+#pragma unroll 2
+    for (int j = lane; j < H; j += 32) {
+        float wv[TE], xv[TT];
+#pragma unroll
+        for (int a = 0; a < TE; ++a) wv[a] = __ldg(wrow[a] + j);
+#pragma unroll
+        for (int b = 0; b < TT; ++b) xv[b] = (float) xrow[b][j];
+#pragma unroll
+        for (int a = 0; a < TE; ++a)
+#pragma unroll
+            for (int b = 0; b < TT; ++b) acc[a][b] = __fmaf_rn(wv[a], xv[b], acc[a][b]);
+    }
+#pragma unroll
+    for (int a = 0; a < TE; ++a)
+#pragma unroll
+        for (int b = 0; b < TT; ++b) {
+            float v = acc[a][b];
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 16));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 8));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+            if (lane == 0 && e0 + a < E && t0 + b < T) {
+                if (bias) v = __fadd_rn(v, bias[e0 + a]);
+                logits[(size_t) (t0 + b) * E + e0 + a] = v;
+            }
+        }
+}
+
 // ---- activation quantisers -------------------------------------------------------------------------
 // Q8_0 as the reference's AVX2 quantize_row_q8_0 (ggml-cpu/arch/x86/quants.c:302-367): d = amax/127 kept
 // as half, multiplier 127/amax in fp32, round to nearest even.  One warp per 32-element block... here one

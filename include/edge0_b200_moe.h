@@ -243,6 +243,32 @@ B200MOE_API int b200moe_layer_forward_host(b200moe_ctx * ctx, const b200moe_laye
                                            int32_t n_tokens, float * out_host, int32_t * ids_host, float * weights_host,
                                            void * stream);
 
+/* ---- the small F32 operators around the MoE sub-graphs, one call per ggml op, for graph nodes that are not part of a fused
+ * pattern (reference: the CPU backend's operators, ggml-cpu/ops.cpp; what exec::Plan needs a backend to run for every node it
+ * said it supports, edge0-infer/src/exec/execution.cpp:256-260).  Tensors are described as ggml does: ne[] elements, nb[] byte
+ * strides.  add / mul / div (second operand repeated over the first), clamp, repeat, get_rows and sum_rows are bit-identical to
+ * the CPU operators; soft_max and silu are for rows that are multiples of 8 long (beyond, the reference finishes with libm's
+ * expf); sigmoid differs from the reference's libm call by at most 2 ulp; argsort is descending with equal values in index
+ * order (the reference leaves their order unspecified). */
+typedef struct b200moe_tensor {
+    void *  data;
+    int64_t ne[4];
+    int64_t nb[4];
+} b200moe_tensor;
+enum { B200MOE_OP_ADD = 0, B200MOE_OP_MUL = 1, B200MOE_OP_DIV = 2 };
+enum { B200MOE_OP_SILU = 0, B200MOE_OP_SIGMOID = 1, B200MOE_OP_CLAMP = 2 };   /* clamp: p0 = min, p1 = max */
+B200MOE_API int b200moe_op_binary(b200moe_ctx * ctx, int op, const b200moe_tensor * a, const b200moe_tensor * b, const b200moe_tensor * dst,
+                                  void * stream);
+B200MOE_API int b200moe_op_unary(b200moe_ctx * ctx, int op, const b200moe_tensor * a, const b200moe_tensor * dst, float p0, float p1, void * stream);
+B200MOE_API int b200moe_op_repeat(b200moe_ctx * ctx, const b200moe_tensor * a, const b200moe_tensor * dst, void * stream);
+B200MOE_API int b200moe_op_get_rows(b200moe_ctx * ctx, const b200moe_tensor * a, const b200moe_tensor * ids, const b200moe_tensor * dst, void * stream);
+B200MOE_API int b200moe_op_sum_rows(b200moe_ctx * ctx, const b200moe_tensor * a, const b200moe_tensor * dst, void * stream);
+B200MOE_API int b200moe_op_soft_max(b200moe_ctx * ctx, const b200moe_tensor * a, const b200moe_tensor * dst, float scale, void * stream);
+B200MOE_API int b200moe_op_argsort_desc(b200moe_ctx * ctx, const b200moe_tensor * a, const b200moe_tensor * dst, void * stream);
+/* ggml_mul_mat of two F32 matrices in ggml_vec_dot_f32's summation order (ggml-cpu/vec.cpp:11): dst [ne01, T] = w [ne00, ne01] . x [ne00, T] */
+B200MOE_API int b200moe_op_mul_mat_f32(b200moe_ctx * ctx, const float * w, int64_t ne00, int64_t ne01, const float * x, int64_t n_tokens, float * dst,
+                                       void * stream);
+
 /* ---- probe of the block-scaled FP4 tensor-core instruction (tcgen05.mma kind::mxf4nvf4, UE4M3 scale per 16 values; the reference's only
  * Blackwell kernel is the warp-level form of it, ggml-cuda/mma.cuh:1186-1214).  Not part of the layer: it pins the operand formats
  * the FP4 engine relies on and measures the denominator of "% of FP4 peak".  Both allocate and free their own device memory.
