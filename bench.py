@@ -194,6 +194,17 @@ def roll_layer(host, shift):
     return h
 
 
+def finish(world, barrier):
+    """End of a multi-rank run: every rank has finished its device work, the line is out.  The process then exits without tearing
+    the communicator down: destroying a process group while captured graphs still hold its collectives was seen to block for
+    good (the measurement had long been printed)."""
+    sys.stdout.flush()
+    sys.stderr.flush()
+    if world > 1:
+        barrier()
+        os._exit(0)
+
+
 def make_graph_stepper(eager, n_sets, ctx, use_graphs):
     """eager(i) launches step i.  Returns step(i) that replays one CUDA graph per weight set (the step's launches captured once,
     so the host's launch cost is off the critical path), or eager itself.  The library's calls are plain stream work and capture
@@ -494,8 +505,7 @@ def run_c5_arm(args):
                                             "frac_of_aggregate_peak": alg / (step_ms * 1e-3) / 1e9 / (peak * world)}},
                 "cpu_baseline": cpu, "library_call_one_gpu": lib_call, "other_configurations": extras}
         print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    finish(world, barrier)
 
 
 # ------------------------------------------------------------------------------------------------ --workload c2_nvfp4
@@ -590,8 +600,7 @@ def run_c2_arm(args):
                              "whole_step": {"algorithmic_bytes": alg, "achieved": alg / (ms_per_step * 1e-3) / 1e9, "frac": alg / (ms_per_step * 1e-3) / 1e9 / peak}},
                 "cpu_baseline": cpu}
         print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    finish(world, barrier)
 
 
 def main():

@@ -20,12 +20,14 @@ STATUS = {0: "OK", 1: "INVALID_ARG", 2: "UNSUPPORTED", 3: "ALLOC", 4: "CUDA", 5:
 class Layer(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("n_embd", "n_latent", "n_expert", "n_expert_used", "n_ff", "wtype")] + [
         (n, C.c_void_p) for n in ("router_w", "router_bias", "gate", "up", "down", "gate_scale", "up_scale", "down_scale",
-                                  "lat_down", "lat_up", "lat_down_scale", "lat_up_scale")]
+                                  "lat_down", "lat_up", "lat_down_scale", "lat_up_scale", "gate_shexp", "up_shexp", "down_shexp",
+                                  "gate_inp_shexp")] + [
+        ("n_ff_shexp", C.c_int32), ("reserved_", C.c_int32)]
 
 
 class Observe(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("ffn_moe_logits", "ffn_moe_probs", "ffn_moe_topk", "ffn_moe_weights_norm",
-                                          "ffn_moe_hidden", "ffn_moe_down")]
+                                          "ffn_moe_hidden", "ffn_moe_down", "ffn_shexp_gated")]
 
 
 class Tensor(C.Structure):
@@ -52,6 +54,7 @@ SIGNATURES = {
     "b200moe_enable_kernel_timing": (C.c_int, [C.c_void_p, C.c_int]),
     "b200moe_kernel_times": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_double)]),
     "b200moe_row_size": (C.c_int64, [C.c_int, C.c_int64]),
+    "b200moe_mul_mat_id_width_ok": (C.c_int, [C.c_int, C.c_int64]),
     "b200moe_quantize_nvfp4_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]),
     "b200moe_dequantize_host": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]),
     "b200moe_route": (C.c_int, [C.c_void_p, C.POINTER(Layer), C.c_void_p, C.c_int, C.c_int32, C.c_void_p, C.c_void_p,

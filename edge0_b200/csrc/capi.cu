@@ -37,7 +37,7 @@ struct Scratch {
 };
 
 struct Plan {  // carved out of the scratch arena for one (layer shape, max_tokens)
-    int max_tokens = 0, n_embd = 0, n_in = 0, n_expert = 0, k = 0, n_ff = 0, wtype = 0;
+    int max_tokens = 0, n_embd = 0, n_in = 0, n_expert = 0, k = 0, n_ff = 0, wtype = 0, n_ff_sh = 0;
     float * logits = nullptr;
     float * probs = nullptr;
     int32_t * ids = nullptr;
@@ -59,6 +59,11 @@ struct Plan {  // carved out of the scratch arena for one (layer shape, max_toke
     uint8_t * asf = nullptr;        // scale tiles of the FP4 digit planes: [token tiles][K / 256][2048]
     size_t asf_bytes = 0;
     float * arow_scale = nullptr;   // [T*k] power of two per expert-sorted routed row (FP4 digit planes)
+    float * sh_a = nullptr;         // [T][n_ff_sh] shared expert: gate product, then silu(gate) * up
+    float * sh_b = nullptr;         // [T][n_ff_sh] shared expert: up product
+    float * sh_out = nullptr;       // [T][n_embd]  shared expert: down product
+    float * sh_gate = nullptr;      // [T]          shared expert: logit of its sigmoid gate
+    ActQuant shq{};                 // [T][n_ff_sh] quantised input of the shared expert's down product
     size_t total = 0;
 };
 
@@ -127,7 +132,7 @@ struct Carver {
 void carve(Plan & p, uint8_t * base) {
     Carver c{base};
     const size_t T = p.max_tokens, E = p.n_expert, k = p.k, R = T * k;
-    const size_t kin = p.n_in, H = p.n_embd, I = p.n_ff;
+    const size_t kin = p.n_in, H = p.n_embd, I = p.n_ff, Ish = p.n_ff_sh;
     p.logits = c.take<float>(T * E);
     p.probs = c.take<float>(T * E);
     p.ids = c.take<int32_t>(R);
@@ -151,10 +156,17 @@ void carve(Plan & p, uint8_t * base) {
     p.xin = c.take<float>(T * H);
     p.outb = c.take<float>(T * H);
     p.one_group_ids = c.take<int>(T);
-    p.afp16 = c.take<__half>(2 * std::max<size_t>(std::max(R, T), 64) * std::max({kin, I, H}));   // hi plane, then lo plane
-    p.asf_bytes = (std::min(E, std::max(R, T)) + std::max(R, T) / FP4_RPT + 1) * ((std::max({kin, I, H}) + 255) / 256) * FP4_SF_TILE;
+    p.afp16 = c.take<__half>(2 * std::max<size_t>(std::max(R, T), 64) * std::max({kin, I, H, Ish}));   // hi plane, then lo plane
+    p.asf_bytes = (std::min(E, std::max(R, T)) + std::max(R, T) / FP4_RPT + 1) * ((std::max({kin, I, H, Ish}) + 255) / 256) * FP4_SF_TILE;
     p.asf = c.take<uint8_t>(p.asf_bytes);
     p.arow_scale = c.take<float>(std::max(R, T));
+    if (Ish) {
+        p.sh_a = c.take<float>(T * Ish);
+        p.sh_b = c.take<float>(T * Ish);
+        p.sh_out = c.take<float>(T * H);
+        p.sh_gate = c.take<float>(T);
+        p.shq = c.act(T, Ish);
+    }
     p.total = align_up(c.off, 256);
 }
 
@@ -221,19 +233,27 @@ int validate_layer(b200moe_ctx * ctx, const b200moe_layer * l, bool need_router 
     if (need_experts && (!l->gate || !l->up || !l->down)) return fail(ctx, B200MOE_ERR_INVALID_ARG, "null weight pointer");
     if (need_router && need_experts && l->n_latent && (!l->lat_down || !l->lat_up))
         return fail(ctx, B200MOE_ERR_INVALID_ARG, "latent layer without projections");
-    const uintptr_t al = (uintptr_t) l->gate | (uintptr_t) l->up | (uintptr_t) l->down | (uintptr_t) l->lat_down | (uintptr_t) l->lat_up;
+    if (l->gate_shexp || l->up_shexp || l->down_shexp || l->gate_inp_shexp || l->n_ff_shexp) {
+        if (!l->gate_shexp || !l->up_shexp || !l->down_shexp || !l->gate_inp_shexp || l->n_ff_shexp <= 0)
+            return fail(ctx, B200MOE_ERR_INVALID_ARG, "shared expert needs its three matrices, its gate vector and n_ff_shexp");
+        if (l->n_latent) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "shared expert on a latent layer");
+        if (!gemv_supported(l->wtype, l->n_ff_shexp) || l->n_ff_shexp % 8)
+            return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no kernel for shared-expert width %d of type %d", l->n_ff_shexp, l->wtype);
+    }
+    const uintptr_t al = (uintptr_t) l->gate | (uintptr_t) l->up | (uintptr_t) l->down | (uintptr_t) l->lat_down | (uintptr_t) l->lat_up |
+                         (uintptr_t) l->gate_shexp | (uintptr_t) l->up_shexp | (uintptr_t) l->down_shexp;
     if (al & 15) return fail(ctx, B200MOE_ERR_INVALID_ARG, "quantised tensors must be 16-byte aligned");
     return B200MOE_OK;
 }
 
-int ensure_plan(b200moe_ctx * ctx, int n_embd, int n_in, int n_expert, int k, int n_ff, int wtype, int tokens) {
+int ensure_plan(b200moe_ctx * ctx, int n_embd, int n_in, int n_expert, int k, int n_ff, int wtype, int tokens, int n_ff_sh = 0) {
     Plan & p = ctx->plan;
     if (p.max_tokens >= tokens && p.n_embd == n_embd && p.n_in == n_in && p.n_expert == n_expert && p.k == k && p.n_ff == n_ff &&
-        p.wtype == wtype && ctx->scratch.base)
+        p.wtype == wtype && p.n_ff_sh >= n_ff_sh && ctx->scratch.base)
         return B200MOE_OK;
     Plan np;
     np.max_tokens = std::max(tokens, 1);
-    np.n_embd = n_embd; np.n_in = n_in; np.n_expert = n_expert; np.k = k; np.n_ff = n_ff; np.wtype = wtype;
+    np.n_embd = n_embd; np.n_in = n_in; np.n_expert = n_expert; np.k = k; np.n_ff = n_ff; np.wtype = wtype; np.n_ff_sh = n_ff_sh;
     carve(np, nullptr);
     if (np.total > ctx->scratch.bytes) {
         CUDA_TRY(ctx, cudaDeviceSynchronize());
@@ -711,7 +731,33 @@ __global__ void fill_group_ids_kernel(int * ids, int T, int group_size) {
 // groups that all point at the same matrix (expert stride 0), so a matrix with few rows and many tokens still fills the grid
 // (one group would leave a 1024-row matrix on a fifth of the SMs, walking all tokens in turn).  The matrix is re-read from L2.
 int dense_matmul_fp4(b200moe_ctx * ctx, const void * w, const float * scale, const float * x, int k, int n_out, int T, float * y, cudaStream_t st,
-                     bool exact_requant, ActQuant xq, void * list_room, size_t list_room_bytes);
+                     bool exact_requant, ActQuant xq, void * list_room, size_t list_room_bytes, const void * w1 = nullptr);
+
+// a[i] = silu(a[i]) * b[i]: ggml_silu then ggml_mul, the same bits as the fused swiglu of the expert kernels
+__global__ void silu_mul_kernel(float * __restrict__ a, const float * __restrict__ b, size_t n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) a[i] = __fmul_rn(ggml_silu(a[i]), b[i]);
+}
+
+// Shared expert onto the routed sum (forward.cpp:313-314): gated = sh * sigmoid(logit), out += gated.  The reference's
+// sigmoid is 1 / (1 + expf(-x)) through the C library (ggml-cpu/vec.h:936); expf is evaluated here as the double-precision
+// exponential rounded to float, which is the correctly rounded value but for double-rounding cases rarer than 1 in 2^28.
+__global__ void shexp_add_kernel(float * __restrict__ out, const float * __restrict__ sh, const float * __restrict__ logit, int H, int T,
+                                 float * __restrict__ gated_out) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T || i >= H) return;
+    const float e = (float) exp((double) -logit[t]);
+    const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, e));
+    const size_t at = (size_t) t * H + i;
+    const float g = __fmul_rn(sh[at], sig);
+    if (gated_out) gated_out[at] = g;
+    out[at] = __fadd_rn(out[at], g);
+}
 
 // The FP4 tensor-core kernel takes a dense product when the type and shape fit, several tokens share the matrix, and the caller
 // has not asked for bit-identical results (expert paths 1, 5 and 7 are the ones documented as bit-identical).
@@ -721,14 +767,23 @@ bool dense_on_fp4(const b200moe_ctx * ctx, int wtype, int k, int n_out, int T) {
 }
 
 // exact_requant: see dense_matmul_fp4; `hidden` scratch holds the list (free before the experts run)
+// w1 != null: y = silu(w . x) * (w1 . x), the gate/up pair of a dense expert in one pass over x (no tensor scales, no exact_requant);
+// y1_tmp [T][n_out] is used when the pair cannot be fused (integer kernel beyond 2048 columns)
 int dense_matvec(b200moe_ctx * ctx, int wtype, const void * w, const float * scale, const float * x, ActQuant xq, int k, int n_out, int T,
-                 float * y, cudaStream_t st, bool exact_requant = false) {
+                 float * y, cudaStream_t st, bool exact_requant = false, const void * w1 = nullptr, float * y1_tmp = nullptr) {
     Plan & p = ctx->plan;
     struct DenseMark { b200moe_ctx * c; DenseMark(b200moe_ctx * c_) : c(c_) { c->dense_now = true; } ~DenseMark() { c->dense_now = false; } } mark(ctx);
     if (dense_on_fp4(ctx, wtype, k, n_out, T) && (!exact_requant || n_out % 32 == 0))
-        return dense_matmul_fp4(ctx, w, scale, x, k, n_out, T, y, st, exact_requant, xq, p.hid, (size_t) p.max_tokens * p.k * p.n_ff * sizeof(float));
-    int rc = launch_quantize<float>(ctx, x, k, xq, T, k, wtype, st);
-    if (rc) return rc;
+        return dense_matmul_fp4(ctx, w, scale, x, k, n_out, T, y, st, exact_requant, xq, p.hid, (size_t) p.max_tokens * p.k * p.n_ff * sizeof(float), w1);
+    int rc;
+    if (w1 && k > 2048) {   // the fused pair is not built for this width: two products, then silu(a) * b
+        if ((rc = dense_matvec(ctx, wtype, w, nullptr, x, xq, k, n_out, T, y, st))) return rc;
+        if ((rc = dense_matvec(ctx, wtype, w1, nullptr, x, xq, k, n_out, T, y1_tmp, st))) return rc;
+        const size_t n = (size_t) T * n_out;
+        silu_mul_kernel<<<(unsigned) ((n + 255) / 256), 256, 0, st>>>(y, y1_tmp, n);
+        return check_launch(ctx, "silu_mul");
+    }
+    if ((rc = launch_quantize<float>(ctx, x, k, xq, T, k, wtype, st))) return rc;
     const int G = std::max(1, std::min({32, T / 8, p.n_expert}));
     const int gsize = (T + G - 1) / G;
     const int groups = (T + gsize - 1) / gsize;
@@ -740,8 +795,9 @@ int dense_matvec(b200moe_ctx * ctx, int wtype, const void * w, const float * sca
     if ((rc = check_launch(ctx, "count_ids"))) return rc;
     // perm is about to be overwritten by the scan: read the ids from one_group_ids
     if ((rc = launch_group(ctx, p.one_group_ids, groups, T, st))) return rc;
-    GemvParams g = gemv_params(ctx, w, nullptr, nullptr, nullptr, xq, y, n_out, 1, 1, groups);
+    GemvParams g = gemv_params(ctx, w, w1, nullptr, nullptr, xq, y, n_out, 1, 1, groups);
     g.w_stride = 0;
+    if (w1) return launch_gemv<true>(ctx, wtype, k, g, 4, st);
     if ((rc = launch_gemv<false>(ctx, wtype, k, g, 4, st))) return rc;
     if (scale) {
         const size_t n = (size_t) T * n_out;
@@ -763,7 +819,7 @@ int launch_fix_single_t(b200moe_ctx * ctx, const FixSingleParams & fp, cudaStrea
 // could change are recomputed with the integer kernel's arithmetic (requant_fixup.cuh), so the quantised y is the reference's.
 // The list lives in `list_room`, memory the caller does not need yet.
 int dense_matmul_fp4(b200moe_ctx * ctx, const void * w, const float * scale, const float * x, int k, int n_out, int T, float * y, cudaStream_t st,
-                     bool exact_requant, ActQuant xq, void * list_room, size_t list_room_bytes) {
+                     bool exact_requant, ActQuant xq, void * list_room, size_t list_room_bytes, const void * w1) {
     Plan & p = ctx->plan;
     int rc;
     fill_group_ids_kernel<<<(T + 255) / 256, 256, 0, st>>>(p.one_group_ids, T, T);
@@ -778,6 +834,7 @@ int dense_matmul_fp4(b200moe_ctx * ctx, const void * w, const float * scale, con
     } else {
         if ((rc = launch_act_planes(ctx, ActQuant{}, x, p.one_group_ids, T, k, 1, 1, 1, st))) return rc;
     }
+    if (w1) return launch_gemm_fp4<true>(ctx, k, fp4_params(ctx, nullptr, nullptr, y, n_out, 1), w, w1, reinterpret_cast<const uint8_t *>(p.afp16), T, st);
     if ((rc = launch_gemm_fp4<false>(ctx, k, fp4_params(ctx, scale, nullptr, y, n_out, 1), w, nullptr, reinterpret_cast<const uint8_t *>(p.afp16), T, st))) return rc;
     if (!exact_requant) return B200MOE_OK;
     FixList list;
@@ -975,6 +1032,34 @@ void account(b200moe_ctx * ctx, const b200moe_layer * l, int T) {
     ctx->counters.kernel_launches = ctx->launches;
 }
 
+// The layer's shared expert and its sigmoid gate, added to the routed sum in `out` (forward.cpp:312-314).  Runs after the
+// routed experts: the dense products borrow the plan's grouping buffers.
+template <typename XT>
+int shared_expert_impl(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, float * out, const b200moe_observe * ob, cudaStream_t st) {
+    Plan & p = ctx->plan;
+    const int H = l->n_embd, Is = l->n_ff_shexp;
+    int rc;
+    const float * xf32;
+    if (std::is_same<XT, float>::value) {
+        xf32 = reinterpret_cast<const float *>(x);
+    } else {
+        const size_t n = (size_t) T * H;
+        bf16_to_f32_kernel<<<(unsigned) ((n + 255) / 256), 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16 *>(x), p.xf, n);
+        if ((rc = check_launch(ctx, "bf16_to_f32"))) return rc;
+        xf32 = p.xf;
+    }
+    // logit of the gate: the reference's F32 dot product, lane chains as in the router
+    constexpr int TT = 4;
+    const int64_t warps = (T + TT - 1) / TT;
+    router_logits_kernel<TT, float><<<(unsigned) ((warps * 32 + 255) / 256), 256, 0, st>>>(l->gate_inp_shexp, nullptr, xf32, p.sh_gate, H, 1, T, nullptr, 0);
+    if ((rc = check_launch(ctx, "shexp_gate_logit"))) return rc;
+    if ((rc = dense_matvec(ctx, l->wtype, l->gate_shexp, nullptr, xf32, p.xq, H, Is, T, p.sh_a, st, false, l->up_shexp, p.sh_b))) return rc;
+    if ((rc = dense_matvec(ctx, l->wtype, l->down_shexp, nullptr, p.sh_a, p.shq, Is, H, T, p.sh_out, st))) return rc;
+    dim3 grid((H + 255) / 256, T);
+    shexp_add_kernel<<<grid, 256, 0, st>>>(out, p.sh_out, p.sh_gate, H, T, ob ? ob->ffn_shexp_gated : nullptr);
+    return check_launch(ctx, "shexp_add");
+}
+
 template <typename XT>
 int layer_impl(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, float * out, const b200moe_observe * ob, cudaStream_t st) {
     Plan & p = ctx->plan;
@@ -1003,6 +1088,7 @@ int layer_impl(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, 
     if (!l->n_latent) {
         if (!fused_front && (rc = launch_quantize<XT>(ctx, x, l->n_embd, p.xq, T, l->n_embd, l->wtype, st))) return rc;
         rc = experts_impl(ctx, l, p.xq, p.ids, p.wts, T, out, ob, st);
+        if (!rc && l->gate_shexp) rc = shared_expert_impl<XT>(ctx, l, x, T, out, ob, st);
         account(ctx, l, T);
         return rc;
     }
@@ -1150,8 +1236,10 @@ int b200moe_reserve(b200moe_ctx * ctx, const b200moe_layer * l, int32_t max_toke
     if (rc) return rc;
     if (max_tokens <= 0) return fail(ctx, B200MOE_ERR_INVALID_ARG, "max_tokens must be positive");
     CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-    return ensure_plan(ctx, l->n_embd, l->n_latent ? l->n_latent : l->n_embd, l->n_expert, l->n_expert_used, l->n_ff, l->wtype, max_tokens);
+    return ensure_plan(ctx, l->n_embd, l->n_latent ? l->n_latent : l->n_embd, l->n_expert, l->n_expert_used, l->n_ff, l->wtype, max_tokens, l->n_ff_shexp);
 }
+
+int b200moe_mul_mat_id_width_ok(int type, int64_t ne00) { return gemv_supported(type, ne00) ? 1 : 0; }
 
 int64_t b200moe_row_size(int type, int64_t n) {
     if (n < 0) return -1;

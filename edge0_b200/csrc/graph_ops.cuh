@@ -7,7 +7,8 @@
 //     (float)(1/sum) (ops.cpp:5584-5694, vec.cpp:531-551) - bit-identical for rows that are multiples of 8;
 //   * silu: x / (1 + exp(-x)) with ggml_v_expf (vec.cpp:380-392, the SIMD body) - bit-identical for rows that are multiples of 8
 //     (the reference finishes a ragged tail with libm's expf);
-//   * sigmoid: the reference calls libm's expf per element (vec.h:936); CUDA's expf differs from it by at most 2 ulp;
+//   * sigmoid: the reference calls libm's expf per element (vec.h:936); here expf is the double-precision exponential rounded to
+//     float (the correctly rounded value but for double-rounding cases rarer than 1 in 2^28);
 //   * argsort: the reference's std::sort leaves the order of equal values unspecified; here equal values keep index order.
 // Tensors are described as ggml describes them: ne[4] elements, nb[4] byte strides.
 #pragma once
@@ -47,7 +48,7 @@ __global__ void __launch_bounds__(256) op_unary_kernel(int op, TensorView a, Ten
         const float x = *reinterpret_cast<const float *>(a.data + view_offset(a, i0, i1, i2, i3));
         float r;
         if (op == UN_SILU) r = ggml_silu(x);
-        else if (op == UN_SIGMOID) r = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x)));
+        else if (op == UN_SIGMOID) r = __fdiv_rn(1.0f, __fadd_rn(1.0f, (float) exp((double) -x)));
         else r = x < p0 ? p0 : (x > p1 ? p1 : x);
         *reinterpret_cast<float *>(d.data + view_offset(d, i0, i1, i2, i3)) = r;
     }

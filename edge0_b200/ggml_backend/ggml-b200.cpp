@@ -4,10 +4,16 @@
 // src/ggml-backend-impl.h); the ggml symbols it calls are resolved from the host application's ggml at load time.
 // Device memory and copies use the CUDA runtime directly, compute goes through the b200moe_* entry points only.
 //
-// graph_compute does not interpret ggml nodes one by one: it recognises the sub-graphs that
-// Builder::route / Builder::ffn emit (edge0-infer/src/models/edge0_35b/forward.cpp:262-271, 300-311) and runs each
-// as one fused call, the way the reference's CUDA backend fuses its top-k MoE and MUL_MAT_ID + scale patterns
-// (third_party/ggml/src/ggml-cuda/ggml-cuda.cu:3655-3673).
+// graph_compute recognises the sub-graphs that Builder::route / Builder::ffn emit
+// (edge0-infer/src/models/edge0_35b/forward.cpp:262-271, 300-311) and runs each as one fused call, the way the reference's
+// CUDA backend fuses its top-k MoE and MUL_MAT_ID + scale patterns (third_party/ggml/src/ggml-cuda/ggml-cuda.cu:3655-3673).
+// Every other node it says it supports - the F32 operators around those sub-graphs, among them the shared expert and its
+// sigmoid gate (forward.cpp:312-314) - runs as one operator call (b200moe_op_*), so supports_op promises nothing that
+// graph_compute refuses (edge0-infer accepts a plan on supports_op and drops a backend for good on the first failed status,
+// src/exec/execution.cpp:256-260, 404-407).
+// A failure that only shows on the device (a rejected expert id, a wait that ran out) is latched when synchronize finds it and
+// returned by the next graph_compute, empty graphs included: that is how the application confirms completion
+// (src/platform/backend.cpp:151-159).
 #include "ggml-b200.h"
 
 #include <cuda_runtime.h>
@@ -44,7 +50,12 @@ struct BackendCtx {
     size_t        scratch_bytes = 0;
     ggml_b200_graph_stats stats = {};
     std::string   error;
+    bool          failed = false;          // a device-side failure was found by synchronize and not yet reported
+    struct GraphPlan * plan = nullptr;     // analysis of the last graph, reused while the graph stays the same
+    uint64_t      plan_key = 0;
 };
+
+void free_plan(BackendCtx * b);
 
 void set_error(BackendCtx * b, const char * fmt, ...) {
     char buf[512];
@@ -655,6 +666,84 @@ ggml_status run_dense(BackendCtx * b, GraphPlan & p, Group & g) {
     return GGML_STATUS_SUCCESS;
 }
 
+b200moe_tensor as_view(const ggml_tensor * t) {
+    b200moe_tensor v;
+    v.data = t->data;
+    for (int i = 0; i < 4; ++i) { v.ne[i] = t->ne[i]; v.nb[i] = (int64_t) t->nb[i]; }
+    return v;
+}
+
+bool f32(const ggml_tensor * t) { return t && t->type == GGML_TYPE_F32; }
+bool same_shape(const ggml_tensor * a, const ggml_tensor * b) { return a->ne[0] == b->ne[0] && a->ne[1] == b->ne[1] && a->ne[2] == b->ne[2] && a->ne[3] == b->ne[3]; }
+bool repeats_over(const ggml_tensor * small, const ggml_tensor * big) {
+    for (int i = 0; i < 4; ++i) if (small->ne[i] <= 0 || big->ne[i] % small->ne[i]) return false;
+    return true;
+}
+
+// Can this node run as one operator call?  The same answer serves supports_op and graph_compute.
+bool operator_runs(const ggml_tensor * t) {
+    const ggml_tensor * a = t->src[0], * c = t->src[1];
+    switch (t->op) {
+        case GGML_OP_ADD: case GGML_OP_MUL: case GGML_OP_DIV:
+            return f32(t) && f32(a) && f32(c) && same_shape(a, t) && repeats_over(c, t);
+        case GGML_OP_UNARY:
+            return f32(t) && f32(a) && same_shape(a, t) && (ggml_get_unary_op(t) == GGML_UNARY_OP_SILU || ggml_get_unary_op(t) == GGML_UNARY_OP_SIGMOID);
+        case GGML_OP_CLAMP:
+            return f32(t) && f32(a) && same_shape(a, t);
+        case GGML_OP_REPEAT:
+            return f32(t) && f32(a) && repeats_over(a, t);
+        case GGML_OP_GET_ROWS:
+            return f32(t) && f32(a) && c && c->type == GGML_TYPE_I32 && c->ne[3] == 1 && t->ne[0] == a->ne[0] && t->ne[1] == c->ne[0] &&
+                   t->ne[2] == c->ne[1] && t->ne[3] == c->ne[2] && (a->ne[2] == c->ne[1] || a->ne[2] == 1) && (a->ne[3] == c->ne[2] || a->ne[3] == 1);
+        case GGML_OP_SUM_ROWS:
+            return f32(t) && f32(a) && t->ne[0] == 1 && t->ne[1] == a->ne[1] && t->ne[2] == a->ne[2] && t->ne[3] == a->ne[3];
+        case GGML_OP_SOFT_MAX:
+            return f32(t) && f32(a) && !t->src[1] && !t->src[2] && same_shape(a, t) && a->ne[0] % 8 == 0 && a->ne[0] <= 1024 && op_param_f32(t, 1) == 0.0f;
+        case GGML_OP_ARGSORT:
+            return t->type == GGML_TYPE_I32 && f32(a) && same_shape(a, t) && a->ne[0] <= 1024 && op_param_i32(t, 0) == (int32_t) GGML_SORT_ORDER_DESC;
+        case GGML_OP_MUL_MAT:
+            return f32(t) && f32(a) && f32(c) && ggml_is_contiguous(a) && ggml_is_contiguous(c) && ggml_is_contiguous(t) && a->ne[2] == 1 && a->ne[3] == 1 &&
+                   c->ne[2] == 1 && c->ne[3] == 1 && a->ne[0] == c->ne[0] && a->ne[0] % 32 == 0;
+        default:
+            return false;
+    }
+}
+
+// returns B200MOE_OK, a positive library status, or -1 when the node is no operator of this backend
+int run_operator(BackendCtx * b, ggml_tensor * t) {
+    if (!operator_runs(t)) return -1;
+    const b200moe_tensor d = as_view(t);
+    const b200moe_tensor a = as_view(t->src[0]);
+    switch (t->op) {
+        case GGML_OP_ADD: case GGML_OP_MUL: case GGML_OP_DIV: {
+            const b200moe_tensor c = as_view(t->src[1]);
+            const int op = t->op == GGML_OP_ADD ? B200MOE_OP_ADD : t->op == GGML_OP_MUL ? B200MOE_OP_MUL : B200MOE_OP_DIV;
+            return b200moe_op_binary(b->moe, op, &a, &c, &d, b->stream);
+        }
+        case GGML_OP_UNARY:
+            return b200moe_op_unary(b->moe, ggml_get_unary_op(t) == GGML_UNARY_OP_SILU ? B200MOE_OP_SILU : B200MOE_OP_SIGMOID, &a, &d, 0.0f, 0.0f, b->stream);
+        case GGML_OP_CLAMP:
+            return b200moe_op_unary(b->moe, B200MOE_OP_CLAMP, &a, &d, op_param_f32(t, 0), op_param_f32(t, 1), b->stream);
+        case GGML_OP_REPEAT:
+            return b200moe_op_repeat(b->moe, &a, &d, b->stream);
+        case GGML_OP_GET_ROWS: {
+            const b200moe_tensor c = as_view(t->src[1]);
+            return b200moe_op_get_rows(b->moe, &a, &c, &d, b->stream);
+        }
+        case GGML_OP_SUM_ROWS:
+            return b200moe_op_sum_rows(b->moe, &a, &d, b->stream);
+        case GGML_OP_SOFT_MAX:
+            return b200moe_op_soft_max(b->moe, &a, &d, op_param_f32(t, 0), b->stream);
+        case GGML_OP_ARGSORT:
+            return b200moe_op_argsort_desc(b->moe, &a, &d, b->stream);
+        case GGML_OP_MUL_MAT:
+            return b200moe_op_mul_mat_f32(b->moe, (const float *) t->src[0]->data, t->src[0]->ne[0], t->src[0]->ne[1], (const float *) t->src[1]->data,
+                                          t->src[1]->ne[1], (float *) t->data, b->stream);
+        default:
+            return -1;
+    }
+}
+
 ggml_status run_single(BackendCtx * b, GraphPlan & p, ggml_tensor * t) {
     if (t->op == GGML_OP_CONT || t->op == GGML_OP_CPY || t->op == GGML_OP_DUP) {
         const ggml_tensor * s = t->src[0];
@@ -680,14 +769,50 @@ ggml_status run_single(BackendCtx * b, GraphPlan & p, ggml_tensor * t) {
         if (rc) return moe_failed(b, "mul_mat_id", rc);
         return GGML_STATUS_SUCCESS;
     }
-    set_error(b, "node '%s' (%s) is outside the route / ffn sub-graphs this backend runs", t->name, ggml_op_desc(t));
+    // the F32 operators around the fused sub-graphs, one call each
+    const int rc = run_operator(b, t);
+    if (rc == B200MOE_OK) return GGML_STATUS_SUCCESS;
+    if (rc > 0) return moe_failed(b, ggml_op_name(t->op), rc);
+    set_error(b, "node '%s' (%s) is not an operator this backend runs", t->name, ggml_op_desc(t));
     return GGML_STATUS_FAILED;
+}
+
+// Identity of a graph for the plan cache: the nodes, what they compute, where their operands and results live.
+uint64_t graph_key(ggml_cgraph * cg) {
+    uint64_t h = 1469598103934665603ull;
+    auto mix = [&](uint64_t v) { h = (h ^ v) * 1099511628211ull; };
+    const int n = ggml_graph_n_nodes(cg);
+    mix((uint64_t) n);
+    for (int i = 0; i < n; ++i) {
+        const ggml_tensor * t = ggml_graph_node(cg, i);
+        mix((uint64_t) (uintptr_t) t); mix((uint64_t) t->op); mix((uint64_t) (uintptr_t) t->data); mix((uint64_t) t->flags);
+        mix((uint64_t) t->ne[0]); mix((uint64_t) t->ne[1]); mix((uint64_t) t->ne[2]); mix((uint64_t) t->ne[3]);
+        mix((uint64_t) t->nb[1]); mix((uint64_t) t->view_offs);
+        for (int s = 0; s < GGML_MAX_SRC; ++s) {
+            const ggml_tensor * z = t->src[s];
+            mix((uint64_t) (uintptr_t) z);
+            if (z) { mix((uint64_t) (uintptr_t) z->data); mix((uint64_t) z->nb[1]); }
+        }
+        for (int k = 0; k < 4; ++k) mix((uint64_t) (uint32_t) op_param_i32(t, k));
+    }
+    return h ? h : 1;
 }
 
 ggml_status graph_compute_impl(BackendCtx * b, ggml_cgraph * cg) {
     B200_CUDA(b, cudaSetDevice(b->device));
-    GraphPlan p;
-    if (!build_plan(b, cg, p)) return GGML_STATUS_FAILED;
+    // The pattern match is kept for as long as the application submits the same graph (decode loops do): only the run-time
+    // state of the plan is reset.
+    const uint64_t key = graph_key(cg);
+    if (b->plan && b->plan_key == key) {
+        for (auto & v : b->plan->deferred_at) v.clear();
+        b->plan->resolved.clear();
+    } else {
+        free_plan(b);
+        b->plan = new GraphPlan();
+        if (!build_plan(b, cg, *b->plan)) { free_plan(b); return GGML_STATUS_FAILED; }
+        b->plan_key = key;
+    }
+    GraphPlan & p = *b->plan;
     // backend scratch for results that cannot be written into graph memory yet
     if (p.scratch_need > b->scratch_bytes) {
         B200_CUDA(b, cudaStreamSynchronize(b->stream));
@@ -733,6 +858,12 @@ ggml_status graph_compute_impl(BackendCtx * b, ggml_cgraph * cg) {
     return GGML_STATUS_SUCCESS;
 }
 
+void free_plan(BackendCtx * b) {
+    delete b->plan;
+    b->plan = nullptr;
+    b->plan_key = 0;
+}
+
 }  // namespace
 
 // ------------------------------------------------------------------------------------------------ backend, device, registry
@@ -750,6 +881,7 @@ void backend_free(ggml_backend_t backend) {
     cudaSetDevice(b->device);
     if (b->stream) cudaStreamSynchronize(b->stream);
     if (b->moe) b200moe_destroy(b->moe);
+    free_plan(b);
     if (b->scratch) cudaFree(b->scratch);
     if (b->stream) cudaStreamDestroy(b->stream);
     delete b;
@@ -760,9 +892,10 @@ void backend_synchronize(ggml_backend_t backend) {
     auto * b = (BackendCtx *) backend->context;
     cudaSetDevice(b->device);
     cudaError_t e = cudaStreamSynchronize(b->stream);
-    if (e != cudaSuccess) set_error(b, "synchronize: %s", cudaGetErrorString(e));
+    if (e != cudaSuccess) { set_error(b, "synchronize: %s", cudaGetErrorString(e)); b->failed = true; }
     const int rc = b200moe_synchronize(b->moe, b->stream);   // also reads the kernels' own error flag
-    if (rc) set_error(b, "synchronize: %s (%s)", b200moe_status_string(rc), b200moe_last_error(b->moe));
+    if (rc) { set_error(b, "synchronize: %s (%s)", b200moe_status_string(rc), b200moe_last_error(b->moe)); b->failed = true; }
+    // synchronize returns nothing: the failure is handed to the next graph_compute
 }
 
 void backend_set_tensor_async(ggml_backend_t backend, ggml_tensor * t, const void * data, size_t offset, size_t size) {
@@ -778,7 +911,13 @@ void backend_get_tensor_async(ggml_backend_t backend, const ggml_tensor * t, voi
 }
 
 ggml_status backend_graph_compute(ggml_backend_t backend, ggml_cgraph * cg) {
-    return graph_compute_impl((BackendCtx *) backend->context, cg);
+    auto * b = (BackendCtx *) backend->context;
+    if (b->failed) {   // found by the last synchronize; reported once, to whatever graph comes next (the empty one included)
+        b->failed = false;
+        return GGML_STATUS_FAILED;
+    }
+    const ggml_status s = graph_compute_impl(b, cg);
+    return s;
 }
 
 const ggml_backend_i backend_iface = {
@@ -861,31 +1000,32 @@ bool dev_supports_buft(ggml_backend_dev_t dev, ggml_backend_buffer_type_t buft) 
     return buft->iface.get_name == buft_get_name && buft->device == dev;
 }
 
-// Op kinds that occur in the sub-graphs graph_compute recognises.  Whether a particular graph is accepted is decided
-// by graph_compute, which sees the whole pattern.
+// A node is supported when graph_compute can run it on its own: as a view, as an indexed or dense quantised matmul, as a
+// row-strided copy, or as one of the F32 operators (operator_runs).  Nodes inside a recognised route / ffn sub-graph are a
+// subset of these, so fusing never adds a requirement.
 bool dev_supports_op(ggml_backend_dev_t, const ggml_tensor * op) {
     switch (op->op) {
         case GGML_OP_NONE: case GGML_OP_VIEW: case GGML_OP_RESHAPE: case GGML_OP_PERMUTE: case GGML_OP_TRANSPOSE:
             return true;
-        case GGML_OP_MUL_MAT_ID:
-            return is_expert_type(op->src[0]->type) && op->src[1]->type == GGML_TYPE_F32 && op->src[2]->ne[0] <= 32 &&
-                   b200moe_row_size(op->src[0]->type, op->src[0]->ne[0]) > 0;
+        case GGML_OP_MUL_MAT_ID: {
+            const ggml_tensor * as = op->src[0], * x = op->src[1], * ids = op->src[2];
+            return is_expert_type(as->type) && x->type == GGML_TYPE_F32 && ids->type == GGML_TYPE_I32 && ids->nb[0] == 4 && ids->ne[0] <= 32 &&
+                   ggml_is_contiguous(as) && ggml_is_contiguous(x) && as->ne[3] == 1 && x->ne[3] == 1 && as->ne[1] % 8 == 0 && as->ne[2] <= 1024 &&
+                   b200moe_mul_mat_id_width_ok((int) as->type, as->ne[0]);
+        }
         case GGML_OP_MUL_MAT:
-            return op->src[1]->type == GGML_TYPE_F32 &&
-                   ((op->src[0]->type == GGML_TYPE_F32 && op->src[0]->ne[2] == 1 && op->src[0]->ne[1] <= 1024 && op->src[0]->ne[1] % 8 == 0) ||
-                    (is_expert_type(op->src[0]->type) && op->src[0]->ne[2] == 1));
-        case GGML_OP_SOFT_MAX:
-            return !op->src[1] && op->type == GGML_TYPE_F32;
-        case GGML_OP_ARGSORT:
-            return op_param_i32(op, 0) == (int32_t) GGML_SORT_ORDER_DESC && op->src[0]->ne[0] <= 1024;
-        case GGML_OP_UNARY:
-            return ggml_get_unary_op(op) == GGML_UNARY_OP_SILU;
-        case GGML_OP_ADD: case GGML_OP_MUL: case GGML_OP_DIV: case GGML_OP_GET_ROWS: case GGML_OP_SUM_ROWS: case GGML_OP_CLAMP: case GGML_OP_REPEAT:
-            return op->type == GGML_TYPE_F32;
-        case GGML_OP_CONT: case GGML_OP_CPY: case GGML_OP_DUP:
-            return !ggml_is_quantized(op->type) && op->src[0]->type == op->type;
+            if (is_expert_type(op->src[0]->type))
+                return op->src[1]->type == GGML_TYPE_F32 && ggml_is_contiguous(op->src[0]) && ggml_is_contiguous(op->src[1]) && op->src[0]->ne[2] == 1 &&
+                       op->src[0]->ne[3] == 1 && op->src[1]->ne[2] == 1 && op->src[1]->ne[3] == 1 && op->src[0]->ne[1] % 8 == 0 &&
+                       b200moe_mul_mat_id_width_ok((int) op->src[0]->type, op->src[0]->ne[0]);
+            return operator_runs(op);
+        case GGML_OP_CONT: case GGML_OP_CPY: case GGML_OP_DUP: {
+            const ggml_tensor * z = op->src[0];
+            return !ggml_is_quantized(z->type) && z->type == op->type && z->nb[0] == ggml_type_size(z->type) && ggml_is_contiguous(op) && z->ne[2] == 1 &&
+                   z->ne[3] == 1 && ggml_nelements(z) == ggml_nelements(op);
+        }
         default:
-            return false;
+            return operator_runs(op);
     }
 }
 
@@ -989,3 +1129,10 @@ const char * ggml_backend_b200_last_error(ggml_backend_t backend) {
 }
 
 }  // extern "C"
+
+// Entry points for ggml's dynamic backend loader (ggml-backend-impl.h:251-287): built with -DGGML_BACKEND_DL the library exports
+// ggml_backend_init / ggml_backend_score and can be dropped next to the application's other backends instead of being registered
+// explicitly.  The score is the number of sm_100 devices found.
+static int b200_score() { return (int) registry()->devices.size(); }
+GGML_BACKEND_DL_IMPL(ggml_backend_b200_reg)
+GGML_BACKEND_DL_SCORE_IMPL(b200_score)

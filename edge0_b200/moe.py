@@ -183,13 +183,15 @@ class Observed:
     weights_norm: torch.Tensor
     hidden: torch.Tensor
     down: torch.Tensor
+    shexp_gated: Optional[torch.Tensor] = None
 
 
 class MoeLayer:
     """Weights of one MoE FFN layer on one GPU plus the calls the reference graph makes on them."""
 
     def __init__(self, ctx: Context, *, wtype: int, top_k: int, router_w, gate, up, down, router_bias=None, gate_scale=None,
-                 up_scale=None, down_scale=None, lat_down=None, lat_up=None, lat_down_scale=None, lat_up_scale=None, check_shapes=True):
+                 up_scale=None, down_scale=None, lat_down=None, lat_up=None, lat_down_scale=None, lat_up_scale=None,
+                 gate_shexp=None, up_shexp=None, down_shexp=None, gate_inp_shexp=None, check_shapes=True):
         dev = torch.device("cuda", ctx.device)
 
         def put(a, dtype):
@@ -206,6 +208,8 @@ class MoeLayer:
         self.gate_scale, self.up_scale, self.down_scale = (put(s, torch.float32) for s in (gate_scale, up_scale, down_scale))
         self.lat_down, self.lat_up = put(lat_down, torch.uint8), put(lat_up, torch.uint8)
         self.lat_down_scale, self.lat_up_scale = put(lat_down_scale, torch.float32), put(lat_up_scale, torch.float32)
+        self.gate_shexp, self.up_shexp, self.down_shexp = put(gate_shexp, torch.uint8), put(up_shexp, torch.uint8), put(down_shexp, torch.uint8)
+        self.gate_inp_shexp = put(gate_inp_shexp, torch.float32)
         self.n_expert, self.n_embd = self.router_w.shape
         self.n_ff = self.gate.shape[1]
         self.n_latent = 0 if self.lat_down is None else self.lat_down.shape[0]
@@ -216,8 +220,10 @@ class MoeLayer:
             raise ValueError(f"down tensor has shape {tuple(self.down.shape)}")
         self.desc = Layer(n_embd=self.n_embd, n_latent=self.n_latent, n_expert=self.n_expert, n_expert_used=top_k, n_ff=self.n_ff,
                           wtype=wtype)
+        if self.gate_shexp is not None:
+            self.desc.n_ff_shexp = self.gate_shexp.shape[0]
         for name in ("router_w", "router_bias", "gate", "up", "down", "gate_scale", "up_scale", "down_scale", "lat_down", "lat_up",
-                     "lat_down_scale", "lat_up_scale"):
+                     "lat_down_scale", "lat_up_scale", "gate_shexp", "up_shexp", "down_shexp", "gate_inp_shexp"):
             t = getattr(self, name)
             setattr(self.desc, name, None if t is None else t.data_ptr())
 
@@ -233,6 +239,9 @@ class MoeLayer:
                      down=torch.empty((T, k, self.n_in), dtype=torch.float32, device=dev))
         s = Observe(ffn_moe_logits=o.logits.data_ptr(), ffn_moe_probs=o.probs.data_ptr(), ffn_moe_topk=o.topk.data_ptr(),
                     ffn_moe_weights_norm=o.weights_norm.data_ptr(), ffn_moe_hidden=o.hidden.data_ptr(), ffn_moe_down=o.down.data_ptr())
+        if self.gate_shexp is not None:
+            o.shexp_gated = torch.empty((T, self.n_embd), dtype=torch.float32, device=dev)
+            s.ffn_shexp_gated = o.shexp_gated.data_ptr()
         return s, o
 
     def route(self, x: torch.Tensor):

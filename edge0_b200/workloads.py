@@ -30,6 +30,7 @@ class LayerConfig:
     top_k: int = 8
     n_ff: int = 768
     n_latent: int = 0
+    n_ff_shexp: int = 0          # > 0: shared expert of this intermediate width with a sigmoid gate (edge0-infer forward.cpp:312-314)
     router_bias: bool = False
     tensor_scales: bool = True   # NVFP4 only
     seed: int = 0
@@ -66,6 +67,10 @@ class HostLayer:
     lat_up: Optional[np.ndarray] = None
     lat_down_scale: Optional[np.ndarray] = None
     lat_up_scale: Optional[np.ndarray] = None
+    gate_shexp: Optional[np.ndarray] = None
+    up_shexp: Optional[np.ndarray] = None
+    down_shexp: Optional[np.ndarray] = None
+    gate_inp_shexp: Optional[np.ndarray] = None
     expert_lo: int = 0   # first expert held in gate/up/down when the layer was generated for a shard
 
     def kwargs(self) -> dict:
@@ -76,12 +81,14 @@ class HostLayer:
         return moe.MoeLayer(ctx, wtype=self.cfg.wtype, top_k=self.cfg.top_k, router_w=self.router_w, gate=self.gate, up=self.up,
                             down=self.down, router_bias=self.router_bias, gate_scale=self.gate_scale, up_scale=self.up_scale,
                             down_scale=self.down_scale, lat_down=self.lat_down, lat_up=self.lat_up,
-                            lat_down_scale=self.lat_down_scale, lat_up_scale=self.lat_up_scale)
+                            lat_down_scale=self.lat_down_scale, lat_up_scale=self.lat_up_scale, gate_shexp=self.gate_shexp,
+                            up_shexp=self.up_shexp, down_shexp=self.down_shexp, gate_inp_shexp=self.gate_inp_shexp)
 
     def checker_kwargs(self) -> dict:
         return dict(wtype=self.cfg.wtype, router_w=self.router_w, gate=self.gate, up=self.up, down=self.down, top_k=self.cfg.top_k,
                     router_bias=self.router_bias, s_gate=self.gate_scale, s_up=self.up_scale, s_down=self.down_scale,
-                    lat_d=self.lat_down, lat_u=self.lat_up, s_lat_d=self.lat_down_scale, s_lat_u=self.lat_up_scale)
+                    lat_d=self.lat_down, lat_u=self.lat_up, s_lat_d=self.lat_down_scale, s_lat_u=self.lat_up_scale,
+                    sh_gate=self.gate_shexp, sh_up=self.up_shexp, sh_down=self.down_shexp, sh_gate_inp=self.gate_inp_shexp)
 
 
 # code frequencies (-4 .. 3) of block_q3_K quantised from N(0, sigma) draws by the reference quantiser
@@ -167,6 +174,13 @@ def make_layer(cfg: LayerConfig, quantize_q3k: Optional[Callable] = None, seed_o
     layer.expert_lo = expert_range[0] if expert_range is not None else 0
     if cfg.router_bias:
         layer.router_bias = rng.normal(0.0, 1.0, E).astype(np.float32)
+    if cfg.n_ff_shexp:
+        # shared expert: dense tensors of the experts' type, quantised without a tensor scale; its gate vector stays F32
+        Is = cfg.n_ff_shexp
+        layer.gate_shexp = _matrix([seed, 6], (1, Is, H), cfg.wtype, False, quantize_q3k)[0][0]
+        layer.up_shexp = _matrix([seed, 7], (1, Is, H), cfg.wtype, False, quantize_q3k)[0][0]
+        layer.down_shexp = _matrix([seed, 8], (1, H, Is), cfg.wtype, False, quantize_q3k)[0][0]
+        layer.gate_inp_shexp = np.random.default_rng([seed, 9]).normal(0.0, 0.02, H).astype(np.float32)
     if cfg.n_latent:
         d, s_d = _matrix([seed, 4], (1, cfg.n_latent, H), cfg.wtype, scaled, quantize_q3k)
         u, s_u = _matrix([seed, 5], (1, H, cfg.n_latent), cfg.wtype, scaled, quantize_q3k)
@@ -186,9 +200,10 @@ def make_tokens(cfg: LayerConfig, n_tokens: int, bf16: bool = False, seed_offset
     return x
 
 
-def small_config(wtype: int, *, n_embd=512, n_expert=16, top_k=4, n_ff=256, n_latent=0, router_bias=False, seed=1, tensor_scales=True):
+def small_config(wtype: int, *, n_embd=512, n_expert=16, top_k=4, n_ff=256, n_latent=0, router_bias=False, seed=1, tensor_scales=True,
+                 n_ff_shexp=0):
     return LayerConfig(f"small_{wtype}", wtype, n_embd=n_embd, n_expert=n_expert, top_k=top_k, n_ff=n_ff, n_latent=n_latent,
-                       router_bias=router_bias, seed=seed, tensor_scales=tensor_scales)
+                       router_bias=router_bias, seed=seed, tensor_scales=tensor_scales, n_ff_shexp=n_ff_shexp)
 
 
 def algorithmic_bytes(cfg: LayerConfig, n_tokens: int, experts_touched: int, x_bytes_per_elt: int = 4) -> int:

@@ -72,6 +72,15 @@ typedef struct b200moe_layer {
     const void  * lat_up;
     const float * lat_down_scale; /* F32 [1] or NULL */
     const float * lat_up_scale;   /* F32 [1] or NULL */
+    /* shared expert with its sigmoid gate (forward.cpp:312-314): out += down_shexp(silu(gate_shexp x) * up_shexp x) * sigmoid(gate_inp_shexp . x).
+     * All NULL / 0 when the layer has none; plain (non-latent) layers only.  Tensors of type wtype, [n_ff_shexp][n_embd] and
+     * [n_embd][n_ff_shexp] rows; gate_inp_shexp F32 [n_embd].  The reference multiplies these without tensor scales. */
+    const void  * gate_shexp;
+    const void  * up_shexp;
+    const void  * down_shexp;
+    const float * gate_inp_shexp;
+    int32_t n_ff_shexp;
+    int32_t reserved_;
 } b200moe_layer;
 
 /* Optional observation outputs, named after the reference's ForwardRequest::observe labels
@@ -83,6 +92,7 @@ typedef struct b200moe_observe {
     float   * ffn_moe_weights_norm; /* F32 [k, T]        */
     float   * ffn_moe_hidden;       /* F32 [n_ff, k, T]  silu(gate)*up         */
     float   * ffn_moe_down;         /* F32 [n_in, k, T]  down, before weights  */
+    float   * ffn_shexp_gated;      /* F32 [n_embd, T]   shared expert times its sigmoid gate (layers that have one) */
 } b200moe_observe;
 
 /* per-call counters (reference: WeightActivity / DecodeTiming, include/edge0/weight_activity.h, timing.h) */
@@ -156,6 +166,8 @@ B200MOE_API int  b200moe_kernel_times(b200moe_ctx * ctx, int64_t launches[3], do
 /* ---- data formats (reference: ggml_row_size, ggml.h:761; quantize_row_nvfp4_ref, ggml-quants.c:384-417;
  *      dequantize_row_q3_K / _nvfp4, ggml-quants.c:1305-1353, 589-612).  Host memory. */
 B200MOE_API int64_t b200moe_row_size(int type, int64_t n);
+/* 1 when b200moe_mul_mat_id / b200moe_mul_mat have a kernel for rows of ne00 values of this type (what a backend's supports_op asks) */
+B200MOE_API int  b200moe_mul_mat_id_width_ok(int type, int64_t ne00);
 B200MOE_API int  b200moe_quantize_nvfp4_host(const float * src, void * dst, int64_t nrows, int64_t n_per_row);
 B200MOE_API int  b200moe_dequantize_host(int type, const void * src, float * dst, int64_t nrows, int64_t n_per_row);
 
@@ -248,7 +260,8 @@ B200MOE_API int b200moe_layer_forward_host(b200moe_ctx * ctx, const b200moe_laye
  * said it supports, edge0-infer/src/exec/execution.cpp:256-260).  Tensors are described as ggml does: ne[] elements, nb[] byte
  * strides.  add / mul / div (second operand repeated over the first), clamp, repeat, get_rows and sum_rows are bit-identical to
  * the CPU operators; soft_max and silu are for rows that are multiples of 8 long (beyond, the reference finishes with libm's
- * expf); sigmoid differs from the reference's libm call by at most 2 ulp; argsort is descending with equal values in index
+ * expf); sigmoid evaluates the reference's expf as the double-precision exponential rounded to float (the correctly rounded value
+ * but for rare double-rounding cases); argsort is descending with equal values in index
  * order (the reference leaves their order unspecified). */
 typedef struct b200moe_tensor {
     void *  data;

@@ -41,6 +41,15 @@ typedef struct orc_moe_args {
     float   * out;
     double  * ms_best;
     double  * ms_median;
+    /* shared expert with its sigmoid gate (edge0-infer/src/models/edge0_35b/forward.cpp:312-314); all null / 0 when the layer has none.
+     * Non-latent layers only. */
+    const void  * sh_gate;      /* [I_sh][H] quantised rows */
+    const void  * sh_up;        /* [I_sh][H] */
+    const void  * sh_down;      /* [H][I_sh] */
+    const float * sh_gate_inp;  /* [H] F32 */
+    float   * shexp_gated;      /* [T][H] output: shared expert times its gate, or null */
+    int32_t   I_sh;
+    int32_t   pad_;
 } orc_moe_args;
 
 int64_t  orc_row_size(int type, int64_t n);

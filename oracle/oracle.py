@@ -31,8 +31,9 @@ class MoeArgs(C.Structure):
             "x", "router_w", "router_bias", "gate", "up", "down", "s_gate", "s_up", "s_down",
             "lat_d", "lat_u", "s_lat_d", "s_lat_u",
             "logits", "probs", "ids", "weights", "hidden", "down_out", "moe_out", "out", "ms_best", "ms_median",
+            "sh_gate", "sh_up", "sh_down", "sh_gate_inp", "shexp_gated",
         )
-    ]
+    ] + [("I_sh", C.c_int32), ("pad_", C.c_int32)]
 
 
 def build(which: str = "restatement") -> None:
@@ -64,6 +65,7 @@ class LayerResult:
     out: np.ndarray
     ms_best: float
     ms_median: float
+    shexp_gated: np.ndarray = None
 
 
 class _Checker:
@@ -128,6 +130,7 @@ class _Checker:
     # -- the layer
     def moe_layer(self, *, wtype, x, router_w, gate, up, down, top_k, router_bias=None,
                   s_gate=None, s_up=None, s_down=None, lat_d=None, lat_u=None, s_lat_d=None, s_lat_u=None,
+                  sh_gate=None, sh_up=None, sh_down=None, sh_gate_inp=None,
                   n_threads=1, repeats=0, backend=None, use_gallocr=False) -> LayerResult:
         """backend: a ggml_backend_t (ctypes void pointer) to run the reference's graph on instead of its CPU backend
         (compiled reference only); use_gallocr: let ggml's graph allocator place the intermediate tensors."""
@@ -142,7 +145,8 @@ class _Checker:
         u8 = lambda a: None if a is None else np.ascontiguousarray(a, dtype=np.uint8)
         keep = dict(x=x, router_w=f32(router_w), router_bias=f32(router_bias), gate=u8(gate), up=u8(up), down=u8(down),
                     s_gate=f32(s_gate), s_up=f32(s_up), s_down=f32(s_down), lat_d=u8(lat_d), lat_u=u8(lat_u),
-                    s_lat_d=f32(s_lat_d), s_lat_u=f32(s_lat_u))
+                    s_lat_d=f32(s_lat_d), s_lat_u=f32(s_lat_u), sh_gate=u8(sh_gate), sh_up=u8(sh_up), sh_down=u8(sh_down),
+                    sh_gate_inp=f32(sh_gate_inp))
         assert keep["router_w"].shape == (E, H)
         assert keep["gate"].shape == (E, I, row_size(wtype, L)), (keep["gate"].shape, (E, I, row_size(wtype, L)))
         assert keep["down"].shape == (E, L, row_size(wtype, I))
@@ -154,6 +158,11 @@ class _Checker:
             ms_best=0.0, ms_median=0.0)
         best, med = C.c_double(0), C.c_double(0)
         a = MoeArgs(H=H, L=L, E=E, K=K, I=I, T=T, wtype=wtype, n_threads=n_threads, repeats=repeats, latent=int(latent))
+        if sh_gate is not None:
+            assert not latent, "the shared expert is defined for plain layers"
+            a.I_sh = keep["sh_gate"].shape[0]
+            res.shexp_gated = np.zeros((T, H), np.float32)
+            a.shexp_gated = _ptr(res.shexp_gated)
         for k, v in keep.items():
             setattr(a, k, _ptr(v))
         for k in ("logits", "probs", "ids", "weights", "hidden", "down_out", "moe_out", "out"):
@@ -197,11 +206,33 @@ class Reference(_Checker):
         self.lib.ref_isa.restype = C.c_char_p
         self.lib.ref_moe_layer_backend.argtypes = [C.POINTER(MoeArgs), C.c_void_p, C.c_int]
         self.lib.ref_moe_layer_backend.restype = C.c_int
+        self.lib.ref_mul_mat_id_backend.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
+                                                    C.c_int64, C.c_int64, C.c_void_p, C.c_int]
+        self.lib.ref_mul_mat_id_backend.restype = C.c_int
+        self.lib.ref_backend_confirm.argtypes = [C.c_void_p]
+        self.lib.ref_backend_confirm.restype = C.c_int
         self.lib.ref_backend_free.argtypes = [C.c_void_p]
         self.lib.ref_backend_free.restype = None
 
     def isa(self) -> str:
         return self.lib.ref_isa().decode()
+
+    def mul_mat_id_backend(self, backend, wtype, experts, x, ids, n_threads=1):
+        """One MUL_MAT_ID node on `backend` (None: the reference's CPU backend).  experts [n_as][ne01][row bytes] uint8,
+        x [T][n_ids][ne00] F32 (every slot its own row), ids [T][n_ids] int32.  Returns (status 0/4, dst [T][n_ids][ne01])."""
+        experts = np.ascontiguousarray(experts)
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        T, n_ids, ne00 = x.shape
+        n_as, ne01 = experts.shape[0], experts.shape[1]
+        dst = np.zeros((T, n_ids, ne01), dtype=np.float32)
+        rc = self.lib.ref_mul_mat_id_backend(backend, int(wtype), experts.ctypes.data, ne00, ne01, n_as, x.ctypes.data, ids.ctypes.data,
+                                             n_ids, T, dst.ctypes.data, n_threads)
+        return rc, dst
+
+    def backend_confirm(self, backend) -> int:
+        """Synchronize, then compute an empty graph on `backend`: 0 when everything before it completed, else 4."""
+        return self.lib.ref_backend_confirm(backend)
 
 
 _cache = {}

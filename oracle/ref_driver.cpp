@@ -62,6 +62,14 @@ struct ref_moe_args {
     float   * out;      // [T][H or L] final (== moe_out unless latent)
     double  * ms_best;
     double  * ms_median;
+    // shared expert with its sigmoid gate (forward.cpp:312-314); null / 0 when the layer has none (non-latent layers only)
+    const void  * sh_gate;      // [I_sh][H] quantised rows
+    const void  * sh_up;        // [I_sh][H]
+    const void  * sh_down;      // [H][I_sh]
+    const float * sh_gate_inp;  // [H] F32
+    float   * shexp_gated;      // [T][H] output or null
+    int32_t   I_sh;
+    int32_t   pad_;
 };
 
 int ref_type_row_size(int type, int64_t n, int64_t * out) {
@@ -116,7 +124,7 @@ static int run_layer(const ref_moe_args * a, ggml_backend_t backend, int use_gal
     const int H = a->H, L = a->latent ? a->L : a->H, E = a->E, K = a->K, I = a->I, T = a->T;
     const ggml_type wt = (ggml_type) a->wtype;
 
-    ggml_init_params ipw = { ggml_tensor_overhead() * 32, nullptr, true };
+    ggml_init_params ipw = { ggml_tensor_overhead() * 40, nullptr, true };
     ggml_init_params ip  = { ggml_tensor_overhead() * 256 + ggml_graph_overhead_custom(512, false), nullptr, true };
     ggml_context * cw = ggml_init(ipw);
     ggml_context * c  = ggml_init(ip);
@@ -135,6 +143,11 @@ static int run_layer(const ref_moe_args * a, ggml_backend_t backend, int use_gal
     ggml_tensor * lu  = a->latent ? ggml_new_tensor_2d(cw, wt, L, H) : nullptr;
     ggml_tensor * sld = (a->latent && a->s_lat_d) ? ggml_new_tensor_1d(cw, GGML_TYPE_F32, 1) : nullptr;
     ggml_tensor * slu = (a->latent && a->s_lat_u) ? ggml_new_tensor_1d(cw, GGML_TYPE_F32, 1) : nullptr;
+    const bool shexp = a->sh_gate && !a->latent;
+    ggml_tensor * shg = shexp ? ggml_new_tensor_2d(cw, wt, H, a->I_sh) : nullptr;
+    ggml_tensor * shu = shexp ? ggml_new_tensor_2d(cw, wt, H, a->I_sh) : nullptr;
+    ggml_tensor * shd = shexp ? ggml_new_tensor_2d(cw, wt, a->I_sh, H) : nullptr;
+    ggml_tensor * shi = shexp ? ggml_new_tensor_2d(cw, GGML_TYPE_F32, H, 1) : nullptr;
 
     // ---- route (forward.cpp:262-271)
     ggml_tensor * logits = ggml_mul_mat(c, rw, x);                       // [E, T]
@@ -161,6 +174,14 @@ static int run_layer(const ref_moe_args * a, ggml_backend_t backend, int use_gal
     ggml_tensor * sum   = ggml_view_2d(c, dw, L, T, dw->nb[2], 0);
     for (int i = 1; i < K; ++i) sum = ggml_add(c, sum, ggml_view_2d(c, dw, L, T, dw->nb[2], i * dw->nb[1]));
     ggml_tensor * moe = (K == 1) ? ggml_cont(c, sum) : sum;
+    // ---- shared expert and its sigmoid gate (forward.cpp:312-314), added to the routed sum
+    ggml_tensor * gated = nullptr;
+    ggml_tensor * routed = moe;       // "ffn_moe_out" of the reference; `moe` becomes "ffn_out" below
+    if (shexp) {
+        ggml_tensor * sh = ggml_mul_mat(c, shd, ggml_mul(c, ggml_silu(c, ggml_mul_mat(c, shg, x)), ggml_mul_mat(c, shu, x)));
+        gated = ggml_mul(c, sh, ggml_sigmoid(c, ggml_mul_mat(c, shi, x)));
+        moe = ggml_add(c, moe, gated);
+    }
 
     ggml_tensor * out = moe;
     if (a->latent) {
@@ -173,8 +194,8 @@ static int run_layer(const ref_moe_args * a, ggml_backend_t backend, int use_gal
     ggml_build_forward_expand(g, out);
     ggml_build_forward_expand(g, ids_c);
     // observation points must not be overwritten by the allocator: mark them as outputs
-    ggml_tensor * keep[] = { logits, probs, wts, hid, down, moe, out, ids_c };
-    for (ggml_tensor * t : keep) ggml_set_output(t);
+    ggml_tensor * keep[] = { logits, probs, wts, hid, down, routed, moe, out, ids_c, gated };
+    for (ggml_tensor * t : keep) if (t) ggml_set_output(t);
 
     ggml_backend_t be = backend ? backend : ggml_backend_cpu_init();
     if (!be) { ggml_free(c); ggml_free(cw); return 2; }
@@ -205,6 +226,7 @@ static int run_layer(const ref_moe_args * a, ggml_backend_t backend, int use_gal
     set(wg, a->gate); set(wu, a->up); set(wd, a->down);
     set(sg, a->s_gate); set(su, a->s_up); set(sd, a->s_down);
     set(ld, a->lat_d); set(lu, a->lat_u); set(sld, a->s_lat_d); set(slu, a->s_lat_u);
+    set(shg, a->sh_gate); set(shu, a->sh_up); set(shd, a->sh_down); set(shi, a->sh_gate_inp);
 
     ggml_status st = ggml_backend_graph_compute(be, g);
     int rc = st == GGML_STATUS_SUCCESS ? 0 : 4;
@@ -212,10 +234,10 @@ static int run_layer(const ref_moe_args * a, ggml_backend_t backend, int use_gal
     if (rc == 0) {
         auto get = [](ggml_tensor * t, void * p) { if (t && p) ggml_backend_tensor_get(t, p, 0, ggml_nbytes(t)); };
         get(logits, a->logits); get(probs, a->probs); get(ids_c, a->ids); get(wts, a->weights);
-        get(hid, a->hidden); get(down, a->down_out); get(out, a->out);
+        get(hid, a->hidden); get(down, a->down_out); get(out, a->out); get(gated, a->shexp_gated);
         if (a->moe_out) {
             // moe may be a strided view when K > 1? no: ggml_add results are contiguous
-            ggml_backend_tensor_get(moe, a->moe_out, 0, ggml_nbytes(moe));
+            ggml_backend_tensor_get(routed, a->moe_out, 0, ggml_nbytes(routed));
         }
     }
 
@@ -249,6 +271,49 @@ int ref_moe_layer(const ref_moe_args * a) { return run_layer(a, nullptr, 0); }
 
 int ref_moe_layer_backend(const ref_moe_args * a, void * backend, int use_gallocr) {
     return run_layer(a, (ggml_backend_t) backend, use_gallocr);
+}
+
+// One MUL_MAT_ID node, as [K, n_ids, T] = as[ne00, ne01, n_as] x b[ne00, n_ids, T] by ids[n_ids, T], on the given backend (null: the
+// reference's CPU backend).  Returns the status of ggml_backend_graph_compute as 0 (success) or 4.
+int ref_mul_mat_id_backend(void * backend, int wtype, const void * as, int64_t ne00, int64_t ne01, int64_t n_as, const float * b,
+                           const int32_t * ids, int64_t n_ids, int64_t T, float * dst, int n_threads) {
+    ggml_init_params ip = { ggml_tensor_overhead() * 16 + ggml_graph_overhead_custom(16, false), nullptr, true };
+    ggml_context * c = ggml_init(ip);
+    if (!c) return 1;
+    ggml_tensor * w = ggml_new_tensor_3d(c, (ggml_type) wtype, ne00, ne01, n_as);
+    ggml_tensor * x = ggml_new_tensor_3d(c, GGML_TYPE_F32, ne00, n_ids, T);
+    ggml_tensor * id = ggml_new_tensor_2d(c, GGML_TYPE_I32, n_ids, T);
+    ggml_tensor * y = ggml_mul_mat_id(c, w, x, id);
+    ggml_set_output(y);
+    ggml_cgraph * g = ggml_new_graph_custom(c, 16, false);
+    ggml_build_forward_expand(g, y);
+    ggml_backend_t be = backend ? (ggml_backend_t) backend : ggml_backend_cpu_init();
+    if (!be) { ggml_free(c); return 2; }
+    if (!backend) ggml_backend_cpu_set_n_threads(be, n_threads > 0 ? n_threads : 1);
+    ggml_backend_buffer_t buf = ggml_backend_alloc_ctx_tensors(c, be);
+    if (!buf) { if (!backend) ggml_backend_free(be); ggml_free(c); return 3; }
+    ggml_backend_tensor_set(w, as, 0, ggml_nbytes(w));
+    ggml_backend_tensor_set(x, b, 0, ggml_nbytes(x));
+    ggml_backend_tensor_set(id, ids, 0, ggml_nbytes(id));
+    const int rc = ggml_backend_graph_compute(be, g) == GGML_STATUS_SUCCESS ? 0 : 4;
+    if (rc == 0 && dst) ggml_backend_tensor_get(y, dst, 0, ggml_nbytes(y));
+    ggml_backend_buffer_free(buf);
+    if (!backend) ggml_backend_free(be);
+    ggml_free(c);
+    return rc;
+}
+
+// Synchronize, then compute a graph without nodes: the way edge0-infer asks a backend whether earlier work completed
+// (src/platform/backend.cpp:151-159).  Returns 0 (success) or 4.
+int ref_backend_confirm(void * backend) {
+    ggml_init_params ip = { ggml_graph_overhead_custom(4, false) + 1024, nullptr, true };
+    ggml_context * c = ggml_init(ip);
+    if (!c) return 1;
+    ggml_cgraph * g = ggml_new_graph_custom(c, 4, false);
+    ggml_backend_synchronize((ggml_backend_t) backend);
+    const int rc = ggml_backend_graph_compute((ggml_backend_t) backend, g) == GGML_STATUS_SUCCESS ? 0 : 4;
+    ggml_free(c);
+    return rc;
 }
 
 void ref_backend_free(void * backend) { if (backend) ggml_backend_free((ggml_backend_t) backend); }

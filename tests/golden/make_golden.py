@@ -1,7 +1,7 @@
 """Generates tests/golden/*.npz from the COMPILED REFERENCE (oracle/_ref/libedge0_ref.so, built by
 `make -C oracle ref` from the reference's own ggml CPU sources).  Run where the reference tree is present:
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py [case ...]      (no names: every case and the known-answer file)
 
 Each fixture holds the seeded inputs that cannot be regenerated without the reference (Q3_K weight bytes)
 plus every observable output of the layer, so the restatement and the CUDA path can be checked against the
@@ -25,6 +25,7 @@ CASES = {
     "nvfp4_small": (W.small_config(TYPE_NVFP4, n_embd=256, n_expert=8, top_k=2, n_ff=256, seed=12), 4, True),
     "nvfp4_small_bias": (W.small_config(TYPE_NVFP4, n_embd=512, n_expert=16, top_k=4, n_ff=256, router_bias=True, seed=13), 6, True),
     "nvfp4_small_latent": (W.small_config(TYPE_NVFP4, n_embd=512, n_latent=256, n_expert=16, top_k=4, n_ff=256, seed=14), 5, True),
+    "nvfp4_small_shexp": (W.small_config(TYPE_NVFP4, n_embd=512, n_expert=16, top_k=4, n_ff=256, n_ff_shexp=512, seed=15), 6, False),
 }
 
 
@@ -32,12 +33,17 @@ def main():
     ref = O.reference()
     print("reference ISA:", ref.isa())
     q3k = lambda w: ref.quantize(TYPE_Q3_K, w)
+    only = sys.argv[1:]
     for name, (cfg, T, bf16) in CASES.items():
+        if only and name not in only:
+            continue
         layer = W.make_layer(cfg, quantize_q3k=q3k)
         x = W.make_tokens(cfg, T, bf16=bf16)
         r = ref.moe_layer(x=x, n_threads=2, **layer.checker_kwargs())
         out = dict(x=x, logits=r.logits, probs=r.probs, ids=r.ids, weights=r.weights, hidden=r.hidden, down_out=r.down_out,
                    moe_out=r.moe_out, out=r.out)
+        if cfg.n_ff_shexp:
+            out.update(shexp_gated=r.shexp_gated)
         if cfg.wtype == TYPE_Q3_K:   # cannot be regenerated without the reference quantiser
             out.update(gate=layer.gate, up=layer.up, down=layer.down)
         else:                        # regenerated from the seed; keep a checksum to detect drift
@@ -47,6 +53,8 @@ def main():
         np.savez_compressed(path, **out)
         print(name, os.path.getsize(path) // 1024, "KiB", "out rms", float(np.sqrt(np.mean(r.out ** 2))))
 
+    if only:
+        return
     # known-answer vectors for the codecs and the dot products (reference functions called directly)
     rng = np.random.default_rng(5)
     kat = {}

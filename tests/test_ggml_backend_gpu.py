@@ -84,6 +84,53 @@ def test_latent_graph_identical(host, use_gallocr):
     compare(host, cfg, 7, use_gallocr, expect=(1, 1, 2))
 
 
+@pytest.mark.parametrize("use_gallocr", [False, True])
+def test_shared_expert_graph(host, use_gallocr):
+    """The layer with its shared expert and sigmoid gate (forward.cpp:312-314): the routed part runs as the two fused sub-graphs, the
+    shared expert as dense quantised products and per-operator kernels; everything on the backend, results the CPU backend's
+    (the sigmoid's expf is the one step that is not the reference's own arithmetic: 1e-6 of RMS on what follows it)."""
+    ref, lib, be = host
+    assert lib.ggml_backend_b200_set_expert_path(be, 1) == 0
+    cfg = W.small_config(TYPE_NVFP4, n_embd=512, n_expert=16, top_k=4, n_ff=256, n_ff_shexp=512, seed=25)
+    layer = W.make_layer(cfg)
+    x = W.make_tokens(cfg, 6)
+    want = ref.moe_layer(x=x, **layer.checker_kwargs())
+    got = ref.moe_layer(x=x, backend=be, use_gallocr=use_gallocr, **layer.checker_kwargs())
+    st = Stats()
+    assert lib.ggml_backend_b200_graph_stats(be, C.byref(st)) == 0
+    assert (st.n_route, st.n_ffn, st.n_dense) == (1, 1, 3), (st.n_route, st.n_ffn, st.n_dense, st.n_single)
+    for name in ("logits", "probs", "weights", "hidden", "down_out", "moe_out"):
+        assert np.array_equal(getattr(got, name), getattr(want, name)), name
+    assert np.array_equal(got.ids, want.ids)
+    for name in ("shexp_gated", "out"):
+        a, b = getattr(got, name), getattr(want, name)
+        assert float(np.max(np.abs(a - b))) <= 1e-6 * float(np.sqrt(np.mean(b.astype(np.float64) ** 2))), name
+
+
+def test_device_failure_is_latched_and_reported_once(host):
+    """A graph whose device-side check fails (an expert id outside the table: the kernels record it and skip the row) is reported
+    the way the application asks for it: synchronize finds it, the next graph_compute - the empty graph edge0-infer uses to
+    confirm completion - returns FAILED once, and the backend works again afterwards."""
+    ref, lib, be = host
+    lib.ggml_backend_b200_set_expert_path(be, 1)
+    cfg = W.small_config(TYPE_NVFP4, n_embd=512, n_expert=16, top_k=4, n_ff=256, seed=26)
+    layer = W.make_layer(cfg)
+    rng = np.random.default_rng(3)
+    x = rng.normal(0, 1, (3, 4, 512)).astype(np.float32)
+    good = np.array([[0, 1, 2, 3], [4, 5, 6, 7], [8, 9, 10, 11]], dtype=np.int32)
+    bad = good.copy()
+    bad[1, 2] = 99                                  # >= n_expert
+    assert ref.backend_confirm(be) == 0
+    ref.mul_mat_id_backend(be, TYPE_NVFP4, layer.gate, x, bad)      # the check runs on the device: the status comes later
+    assert ref.backend_confirm(be) == 4, "the failure must reach the graph that confirms completion"
+    assert b"device" in lib.ggml_backend_b200_last_error(be).lower() or lib.ggml_backend_b200_last_error(be)
+    assert ref.backend_confirm(be) == 0, "reported once"
+    rc, got = ref.mul_mat_id_backend(be, TYPE_NVFP4, layer.gate, x, good)
+    assert rc == 0 and ref.backend_confirm(be) == 0
+    rc, want = ref.mul_mat_id_backend(None, TYPE_NVFP4, layer.gate, x, good)
+    assert rc == 0 and np.array_equal(got, want)
+
+
 def test_single_expert_per_token(host):
     cfg = W.small_config(TYPE_NVFP4, n_embd=512, n_expert=16, top_k=1, n_ff=256, seed=24)
     compare(host, cfg, 3, False, expect=(1, 1, 0))

@@ -110,7 +110,7 @@ def load_golden(name):
     return load_case(name)
 
 
-@pytest.mark.parametrize("name", ["q3k_small", "nvfp4_small", "nvfp4_small_bias", "nvfp4_small_latent"])
+@pytest.mark.parametrize("name", ["q3k_small", "nvfp4_small", "nvfp4_small_bias", "nvfp4_small_latent", "nvfp4_small_shexp"])
 def test_golden_fixtures(name, gpu_ctx):
     """Against outputs the compiled reference produced (no checker needed at run time)."""
     cfg, layer, x_np, z = load_golden(name)
@@ -132,6 +132,9 @@ def test_golden_fixtures(name, gpu_ctx):
     assert np.array_equal(ob.weights_norm.cpu().numpy(), z["weights"])
     assert np.array_equal(ob.hidden.cpu().numpy(), z["hidden"])       # bit-identical to what the compiled reference produced
     assert np.array_equal(ob.down.cpu().numpy(), z["down_out"])
+    if cfg.n_ff_shexp:   # the sigmoid's expf is the one step that is not the reference's own arithmetic (see the shared-expert test)
+        assert rel_err(ob.shexp_gated.cpu().numpy(), z["shexp_gated"]) <= 1e-6 and rel_err(out.cpu().numpy(), z["out"]) <= 1e-6
+        return
     assert np.array_equal(out.cpu().numpy(), z["out"])
 
 
@@ -306,6 +309,53 @@ def test_dense_product_on_the_fp4_engine(gpu_ctx, checker):
             want[t, r] = checker.vec_dot(TYPE_NVFP4, K, wq[r], aq)
     assert np.array_equal(exact.cpu().numpy(), want)
     assert rel_err(fast.cpu().numpy(), want) <= 5e-5
+
+
+@pytest.mark.parametrize("T", [1, 5, 64])
+@pytest.mark.parametrize("wtype", [TYPE_NVFP4, TYPE_Q3_K])
+def test_shared_expert_with_sigmoid_gate(wtype, T, gpu_ctx, checker):
+    """Layers with a shared expert (forward.cpp:312-314): out = routed sum + down_sh(silu(gate_sh x) * up_sh x) * sigmoid(g . x).
+    On the integer kernels everything up to the sigmoid is the reference's arithmetic; the sigmoid's expf is the double-precision
+    exponential rounded to float where the reference calls the C library, so `gated` and `out` are held to 1e-6 of RMS (and are
+    normally the same bits).  On the default path the dense products may run on the FP4 tensor cores."""
+    cfg = W.small_config(wtype, n_embd=512, n_expert=16, top_k=4, n_ff=256, n_ff_shexp=512, seed=70 + T)
+    layer = W.make_layer(cfg, quantize_q3k=q3k_quantizer(checker) if wtype == TYPE_Q3_K else None)
+    x_np = W.make_tokens(cfg, T)
+    r = checker.moe_layer(x=x_np, n_threads=os.cpu_count() or 1, **layer.checker_kwargs())
+    assert r.shexp_gated is not None and not np.array_equal(r.out, r.moe_out)
+    for path, bar in ((1, 1e-6), (0, 2e-3)):
+        gpu_ctx.set_expert_path(path)
+        try:
+            out, ob = layer.to_device(gpu_ctx).forward(torch.from_numpy(x_np).cuda(), observe=True)
+            gpu_ctx.synchronize()
+        finally:
+            gpu_ctx.set_expert_path(0)
+        assert np.array_equal(ob.topk.cpu().numpy(), r.ids)
+        if path == 1:
+            assert np.array_equal(ob.down.cpu().numpy(), r.down_out)
+        errs = dict(gated=rel_err(ob.shexp_gated.cpu().numpy(), r.shexp_gated), out=rel_err(out.cpu().numpy(), r.out))
+        assert errs["gated"] <= bar and errs["out"] <= bar, (path, errs)
+    # bf16 activations take the same road
+    xb = W.make_tokens(cfg, T, bf16=True)
+    rb = checker.moe_layer(x=xb, n_threads=os.cpu_count() or 1, **layer.checker_kwargs())
+    gpu_ctx.set_expert_path(1)
+    try:
+        out = layer.to_device(gpu_ctx).forward(torch.from_numpy(xb).cuda().to(torch.bfloat16))
+        gpu_ctx.synchronize()
+    finally:
+        gpu_ctx.set_expert_path(0)
+    assert rel_err(out.cpu().numpy(), rb.out) <= 1e-6
+
+
+def test_shared_expert_arguments(gpu_ctx):
+    cfg = W.small_config(TYPE_NVFP4, n_embd=512, n_expert=16, top_k=4, n_ff=256, n_ff_shexp=512, seed=5)
+    layer = W.make_layer(cfg)
+    dl = layer.to_device(gpu_ctx)
+    dl.desc.up_shexp = None                      # incomplete shared expert: refused, nothing launched
+    before = gpu_ctx.launches()
+    with pytest.raises(B200MoeError, match="shared expert"):
+        dl.forward(torch.zeros((2, 512), device="cuda"))
+    assert gpu_ctx.launches() == before
 
 
 def test_route_and_ffn_entry_points_compose(gpu_ctx, checker):

@@ -29,11 +29,11 @@ def load_case(name):
     return cfg, layer, x, z
 
 
-@pytest.mark.parametrize("name", ["q3k_small", "nvfp4_small", "nvfp4_small_bias", "nvfp4_small_latent"])
+@pytest.mark.parametrize("name", ["q3k_small", "nvfp4_small", "nvfp4_small_bias", "nvfp4_small_latent", "nvfp4_small_shexp"])
 def test_restatement_matches_golden_bitwise(name, restatement):
     cfg, layer, x, z = load_case(name)
     r = restatement.moe_layer(x=x, **layer.checker_kwargs())
-    for f in FIELDS:
+    for f in FIELDS + (("shexp_gated",) if cfg.n_ff_shexp else ()):
         assert np.array_equal(getattr(r, f), z[f]), f"{name}: {f} differs from the reference's golden output"
 
 
