@@ -557,13 +557,18 @@ bool fp4_supported(int wtype, int n_in, int n_ff) { return wtype == TYPE_NVFP4 &
 // digit planes + scale tiles of the expert-sorted routed rows (input of the FP4 kernels)
 // act: rows already on the int8 grid; or src != null: fp32 rows (src_stride floats apart) that are quantised (Q8_0) on the way.
 // ids: expert of every routed row; n_as experts; the token-tile prefix lies behind the three work prefixes of the group tables.
+// emit (with src): also receives the quantised rows (for the exact re-quantisation fix-up, which recomputes with them)
 int launch_act_planes(b200moe_ctx * ctx, ActQuant act, const float * src, const int32_t * ids, int rows, int k, int n_ids, int ne11, int n_as,
-                      cudaStream_t st) {
+                      cudaStream_t st, ActQuant emit = ActQuant{}, int64_t src_stride = 0) {
     Plan & p = ctx->plan;
     PlaneOut po{ reinterpret_cast<uint8_t *>(p.afp16), p.asf, p.arow_scale, p.groups.pos /* free once the rows are grouped */ };
     const int * tiles = p.groups.cost + 3 * (n_as + 1);
-    if (src) act_planes_kernel<true><<<rows, 256, 0, st>>>(act, src, k, p.groups.perm, ids, p.groups.offsets, tiles, p.groups.meta, rows, k, n_ids, ne11, n_as, po);
-    else act_planes_kernel<false><<<rows, 256, 0, st>>>(act, nullptr, 0, p.groups.perm, ids, p.groups.offsets, tiles, p.groups.meta, rows, k, n_ids, ne11, n_as, po);
+    if (src_stride == 0) src_stride = k;
+    if (src && (((uintptr_t) src & 15) || src_stride % 4)) return fail(ctx, B200MOE_ERR_INVALID_ARG, "fp32 activation rows must be 16-byte aligned");
+    const int rows_per_block = 256 / std::min(256, k / 8);
+    const unsigned blocks = (unsigned) ((rows + rows_per_block - 1) / rows_per_block);
+    if (src) act_planes_kernel<true><<<blocks, 256, 0, st>>>(act, src, src_stride, p.groups.perm, ids, p.groups.offsets, tiles, p.groups.meta, rows, k, n_ids, ne11, n_as, po, emit);
+    else act_planes_kernel<false><<<blocks, 256, 0, st>>>(act, nullptr, 0, p.groups.perm, ids, p.groups.offsets, tiles, p.groups.meta, rows, k, n_ids, ne11, n_as, po, ActQuant{});
     return check_launch(ctx, "act_planes");
 }
 
@@ -600,22 +605,44 @@ int launch_quantize(b200moe_ctx * ctx, const XT * src, int64_t stride, ActQuant 
     return check_launch(ctx, "quantize_act");
 }
 
+template <int WE, int WT, typename XT>
+int launch_logits_smem(b200moe_ctx * ctx, const float * w, const float * bias, const XT * x, float * logits, int H, int E, int T, int * zero_buf,
+                       int zero_n, cudaStream_t st) {
+    auto kern = router_logits_smem_kernel<WE, WT, XT>;
+    constexpr size_t smem = router_smem_bytes<WE, WT, XT>();
+    static bool configured[MAX_DEVICE_ORDINALS] = {};
+    if (int rc = raise_smem_limit(ctx, kern, smem, configured)) return rc;
+    const int blocks = ((E + 8 * WE - 1) / (8 * WE)) * ((T + 8 * WT - 1) / (8 * WT));
+    kern<<<blocks, WE * WT * 32, smem, st>>>(w, bias, x, logits, H, E, T, zero_buf, zero_n);
+    return check_launch(ctx, "router_logits");
+}
+
+// F32 matrix times a batch in the reference's summation order: logits [T][E] = W [E][H] . x [T][H] (+ bias)
 template <typename XT>
-int launch_logits(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, cudaStream_t st) {
-    Plan & p = ctx->plan;
+int launch_logits_any(b200moe_ctx * ctx, const float * w, const float * bias, const XT * x, float * logits, int H, int E, int T, int * zero_buf,
+                      int zero_n, cudaStream_t st) {
+    const bool staged = T >= 16 && H % ROUTER_KC == 0 && (((uintptr_t) w | (uintptr_t) x) & 15) == 0;
+    if (staged) {   // shared-memory tiles: 32 experts x 16 tokens when that fills the GPU, else 16 x 8
+        const int big = ((E + 31) / 32) * ((T + 15) / 16);
+        if (big >= ctx->sm_count) return launch_logits_smem<4, 2, XT>(ctx, w, bias, x, logits, H, E, T, zero_buf, zero_n, st);
+        return launch_logits_smem<2, 1, XT>(ctx, w, bias, x, logits, H, E, T, zero_buf, zero_n, st);
+    }
     if (T >= 16) {   // batches: 4 experts x 8 tokens per warp
         constexpr int TE = 4, TT = 8;
-        const int64_t warps = (int64_t) ((l->n_expert + TE - 1) / TE) * ((T + TT - 1) / TT);
-        router_logits_tiled_kernel<TE, TT, XT><<<(unsigned) ((warps * 32 + 255) / 256), 256, 0, st>>>(l->router_w, l->router_bias, x, p.logits, l->n_embd,
-                                                                                                   l->n_expert, T, p.groups.counts, l->n_expert);
+        const int64_t warps = (int64_t) ((E + TE - 1) / TE) * ((T + TT - 1) / TT);
+        router_logits_tiled_kernel<TE, TT, XT><<<(unsigned) ((warps * 32 + 255) / 256), 256, 0, st>>>(w, bias, x, logits, H, E, T, zero_buf, zero_n);
         return check_launch(ctx, "router_logits");
     }
     constexpr int TT = 4;
-    const int64_t warps = (int64_t) l->n_expert * ((T + TT - 1) / TT);
-    const int blocks = (int) ((warps * 32 + 255) / 256);
-    router_logits_kernel<TT, XT><<<blocks, 256, 0, st>>>(l->router_w, l->router_bias, x, p.logits, l->n_embd, l->n_expert, T,
-                                                          p.groups.counts, l->n_expert);
+    const int64_t warps = (int64_t) E * ((T + TT - 1) / TT);
+    router_logits_kernel<TT, XT><<<(unsigned) ((warps * 32 + 255) / 256), 256, 0, st>>>(w, bias, x, logits, H, E, T, zero_buf, zero_n);
     return check_launch(ctx, "router_logits");
+}
+
+template <typename XT>
+int launch_logits(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, cudaStream_t st) {
+    Plan & p = ctx->plan;
+    return launch_logits_any<XT>(ctx, l->router_w, l->router_bias, x, p.logits, l->n_embd, l->n_expert, T, p.groups.counts, l->n_expert, st);
 }
 
 template <int TT, typename XT>
@@ -640,7 +667,7 @@ int launch_front(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T
 int launch_select_group(b200moe_ctx * ctx, const b200moe_layer * l, int T, float * probs, cudaStream_t st) {
     Plan & p = ctx->plan;
     const int E = l->n_expert, K = l->n_expert_used;
-    const size_t sh = (size_t) (2 * E + 1) * sizeof(int);
+    const size_t sh = (size_t) (3 * E + 1) * sizeof(int);
 #define SELG(EPL) launch_k(ctx, route_select_group_kernel<EPL>, dim3(1), dim3(1024), sh, st, p.logits, E, K, T, p.ids, p.wts, probs, p.groups, ctx->d_err)
     if (E <= 32) SELG(1);
     else if (E <= 64) SELG(2);
@@ -670,7 +697,7 @@ int launch_select(b200moe_ctx * ctx, const b200moe_layer * l, int T, int32_t * i
 
 int launch_group(b200moe_ctx * ctx, const int32_t * ids, int E, int rows, cudaStream_t st, bool allow_empty = false) {
     Plan & p = ctx->plan;
-    const size_t sh = (size_t) (2 * E + 1) * sizeof(int);
+    const size_t sh = (size_t) (3 * E + 1) * sizeof(int);
     launch_k(ctx, group_scan_kernel, dim3(1), dim3(1024), sh, st, p.groups, ids, E, rows, ctx->d_err, allow_empty ? 1 : 0);
     return check_launch(ctx, "group_scan");
 }
@@ -773,7 +800,7 @@ int dense_matvec(b200moe_ctx * ctx, int wtype, const void * w, const float * sca
                  float * y, cudaStream_t st, bool exact_requant = false, const void * w1 = nullptr, float * y1_tmp = nullptr) {
     Plan & p = ctx->plan;
     struct DenseMark { b200moe_ctx * c; DenseMark(b200moe_ctx * c_) : c(c_) { c->dense_now = true; } ~DenseMark() { c->dense_now = false; } } mark(ctx);
-    if (dense_on_fp4(ctx, wtype, k, n_out, T) && (!exact_requant || n_out % 32 == 0))
+    if (dense_on_fp4(ctx, wtype, k, n_out, T) && (!exact_requant || n_out % 128 == 0))
         return dense_matmul_fp4(ctx, w, scale, x, k, n_out, T, y, st, exact_requant, xq, p.hid, (size_t) p.max_tokens * p.k * p.n_ff * sizeof(float), w1);
     int rc;
     if (w1 && k > 2048) {   // the fused pair is not built for this width: two products, then silu(a) * b
@@ -822,18 +849,10 @@ int dense_matmul_fp4(b200moe_ctx * ctx, const void * w, const float * scale, con
                      bool exact_requant, ActQuant xq, void * list_room, size_t list_room_bytes, const void * w1) {
     Plan & p = ctx->plan;
     int rc;
-    fill_group_ids_kernel<<<(T + 255) / 256, 256, 0, st>>>(p.one_group_ids, T, T);
-    if ((rc = check_launch(ctx, "fill_group_ids"))) return rc;
-    CUDA_TRY(ctx, cudaMemsetAsync(p.groups.counts, 0, sizeof(int) * 8, st));
-    count_ids_kernel<<<(T + 255) / 256, 256, 0, st>>>(p.one_group_ids, 1, 1, T, 1, p.groups.perm /*scratch: compact ids*/, p.groups.counts, p.groups.pos, ctx->d_err);
-    if ((rc = check_launch(ctx, "count_ids"))) return rc;
-    if ((rc = launch_group(ctx, p.one_group_ids, 1, T, st))) return rc;
-    if (exact_requant) {
-        if ((rc = launch_quantize<float>(ctx, x, k, xq, T, k, TYPE_NVFP4, st))) return rc;
-        if ((rc = launch_act_planes(ctx, xq, nullptr, p.one_group_ids, T, k, 1, 1, 1, st))) return rc;
-    } else {
-        if ((rc = launch_act_planes(ctx, ActQuant{}, x, p.one_group_ids, T, k, 1, 1, 1, st))) return rc;
-    }
+    one_group_kernel<<<(T + 255) / 256, 256, 0, st>>>(p.groups, p.one_group_ids, T);
+    if ((rc = check_launch(ctx, "one_group"))) return rc;
+    // the fix-up recomputes with the quantised activations: have the plane kernel leave them in xq
+    if ((rc = launch_act_planes(ctx, ActQuant{}, x, p.one_group_ids, T, k, 1, 1, 1, st, exact_requant ? xq : ActQuant{}))) return rc;
     if (w1) return launch_gemm_fp4<true>(ctx, k, fp4_params(ctx, nullptr, nullptr, y, n_out, 1), w, w1, reinterpret_cast<const uint8_t *>(p.afp16), T, st);
     if ((rc = launch_gemm_fp4<false>(ctx, k, fp4_params(ctx, scale, nullptr, y, n_out, 1), w, nullptr, reinterpret_cast<const uint8_t *>(p.afp16), T, st))) return rc;
     if (!exact_requant) return B200MOE_OK;
@@ -843,7 +862,7 @@ int dense_matmul_fp4(b200moe_ctx * ctx, const void * w, const float * scale, con
     list.capacity = (int) std::min<size_t>(list_room_bytes / sizeof(int2), (size_t) T * n_out / 4);
     list.overflow = reinterpret_cast<unsigned long long *>(ctx->d_err + 2);
     CUDA_TRY(ctx, cudaMemsetAsync(list.count, 0, sizeof(int), st));
-    const int64_t warps = (int64_t) T * (n_out / 32);
+    const int64_t warps = (int64_t) T * (n_out / 128);
     requant_mark_kernel<<<(unsigned) ((warps * 32 + 255) / 256), 256, 0, st>>>(y, p.groups.perm, p.groups.meta, T, n_out, FIX_STEP_MARGIN_FP4, FIX_REL_MARGIN_FP4, list);
     if ((rc = check_launch(ctx, "requant_mark"))) return rc;
     FixSingleParams fs{ static_cast<const uint8_t *>(w), scale, xq, n_out, y, list };
@@ -911,7 +930,7 @@ int launch_requant_fixup(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq
     list.capacity = (int) std::min<size_t>(room, (size_t) rows * l->n_ff / 4);
     list.overflow = reinterpret_cast<unsigned long long *>(ctx->d_err + 2);
     CUDA_TRY(ctx, cudaMemsetAsync(list.count, 0, sizeof(int), st));
-    const int64_t warps = (int64_t) rows * (l->n_ff / 32);
+    const int64_t warps = (int64_t) rows * (l->n_ff / 128);
     launch_k(ctx, requant_mark_kernel, dim3((unsigned) ((warps * 32 + 255) / 256)), dim3(256), 0, st, (const float *) p.hid,
              (const int *) p.groups.perm, (const int *) p.groups.meta, rows, l->n_ff, after_fp4 ? FIX_STEP_MARGIN_FP4 : FIX_STEP_MARGIN, after_fp4 ? FIX_REL_MARGIN_FP4 : FIX_REL_MARGIN, list);
     int rc = check_launch(ctx, "requant_mark");
@@ -932,8 +951,10 @@ int launch_requant_fixup(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq
 
 // experts on activations xe [T][n_in] (fp32), routing already grouped in the plan
 // y_direct != null: the per-row results of `down` go there ([rows][n_in]) and the weighted combine is left to the caller
+// x_src != null: the activations are still fp32 (rows x_src_stride floats apart, indexed like xq's rows) and xq is only room for
+// their quantised form: the engine that runs gate/up quantises them on its way in
 int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const int32_t * ids, const float * wts, int T, float * out,
-                 const b200moe_observe * ob, cudaStream_t st, float * y_direct = nullptr) {
+                 const b200moe_observe * ob, cudaStream_t st, float * y_direct = nullptr, const float * x_src = nullptr, int64_t x_src_stride = 0) {
     Plan & p = ctx->plan;
     float * const y = y_direct ? y_direct : p.y;
     const int n_in = l->n_latent ? l->n_latent : l->n_embd;
@@ -987,8 +1008,11 @@ int experts_impl(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, const 
     // measured faster (167 us against 182 us at 64 tokens of configuration 2: there the tokens-on-M form is bound by
     // shared-memory traffic, twice the operand tile per stage).
     const bool tm_gu = false, tm_down = small_tiles && n_in % 256 == 0;
+    if (x_src && !fp4_gu && (rc = launch_quantize<float>(ctx, x_src, x_src_stride, xq, T, n_in, l->wtype, st))) return rc;
     if (fp4_gu) {
-        if ((rc = launch_act_planes(ctx, xq, nullptr, p.ids, rows, n_in, k, 1, l->n_expert, st))) return rc;
+        if (x_src) rc = launch_act_planes(ctx, ActQuant{}, x_src, p.ids, rows, n_in, k, 1, l->n_expert, st, fixup ? xq : ActQuant{}, x_src_stride);
+        else rc = launch_act_planes(ctx, xq, nullptr, p.ids, rows, n_in, k, 1, l->n_expert, st);
+        if (rc) return rc;
         if ((rc = launch_gemm_fp4<true>(ctx, n_in, fp4_params(ctx, l->gate_scale, l->up_scale, p.hid, l->n_ff, l->n_expert), l->gate, l->up, reinterpret_cast<const uint8_t *>(p.afp16), rows, st))) return rc;
     } else if (mma_gu) {
         if ((rc = launch_sorted_act(ctx, xq, rows, n_in, k, 1, tm_gu, st))) return rc;
@@ -1110,8 +1134,7 @@ int layer_impl(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, 
     count_ids_kernel<<<(T * k + 255) / 256, 256, 0, st>>>(p.ids, k, k, T, l->n_expert, p.groups.perm, p.groups.counts, p.groups.pos, ctx->d_err);
     if ((rc = check_launch(ctx, "count_ids"))) return rc;
     if ((rc = launch_group(ctx, p.ids, l->n_expert, T * k, st))) return rc;
-    if ((rc = launch_quantize<float>(ctx, p.xl, l->n_latent, p.xlq, T, l->n_latent, l->wtype, st))) return rc;
-    if ((rc = experts_impl(ctx, l, p.xlq, p.ids, p.wts, T, p.moe, ob, st))) return rc;
+    if ((rc = experts_impl(ctx, l, p.xlq, p.ids, p.wts, T, p.moe, ob, st, nullptr, p.xl, l->n_latent))) return rc;
     rc = dense_matvec(ctx, l->wtype, l->lat_up, l->lat_up_scale, p.moe, p.moq, l->n_latent, l->n_embd, T, out, st);
     account(ctx, l, T);
     return rc;
@@ -1591,8 +1614,8 @@ int b200moe_ep_expert_rows(b200moe_ctx * ctx, const b200moe_layer * l, const voi
     count_ids_kernel<<<(R + 255) / 256, 256, 0, st>>>(ids, slot_words, 1, R, l->n_expert, p.ids, p.groups.counts, p.groups.pos, ctx->d_err, 1);
     if ((rc = check_launch(ctx, "count_ids"))) return rc;
     if ((rc = launch_group(ctx, p.ids, l->n_expert, R, st, true))) return rc;
-    if ((rc = launch_quantize<float>(ctx, rows, slot_words, p.xq, R, n_in, l->wtype, st))) return rc;   // empty slots hold garbage nobody reads
-    rc = experts_impl(ctx, l, p.xq, p.ids, nullptr, R, nullptr, nullptr, st, y);
+    // the slots' rows are quantised by whichever engine runs gate/up (empty slots hold garbage nobody reads)
+    rc = experts_impl(ctx, l, p.xq, p.ids, nullptr, R, nullptr, nullptr, st, y, rows, slot_words);
     account(ctx, l, 0);
     return rc;
 }
@@ -1728,18 +1751,7 @@ int b200moe_op_mul_mat_f32(b200moe_ctx * ctx, const float * w, int64_t ne00, int
     if (ne00 % 32) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "F32 matmul rows must be multiples of 32 long");
     if (ne01 * T > ((int64_t) 1 << 30)) return fail(ctx, B200MOE_ERR_UNSUPPORTED, "result too large");
     CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-    if (T >= 16 && ne01 >= 4) {
-        constexpr int TE = 4, TT = 8;
-        const int64_t warps = ((ne01 + TE - 1) / TE) * ((T + TT - 1) / TT);
-        router_logits_tiled_kernel<TE, TT, float><<<(unsigned) ((warps * 32 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(w, nullptr, x, dst, (int) ne00,
-                                                                                                                                   (int) ne01, (int) T, nullptr, 0);
-    } else {
-        constexpr int TT = 4;
-        const int64_t warps = ne01 * ((T + TT - 1) / TT);
-        router_logits_kernel<TT, float><<<(unsigned) ((warps * 32 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(w, nullptr, x, dst, (int) ne00,
-                                                                                                                        (int) ne01, (int) T, nullptr, 0);
-    }
-    return check_launch(ctx, "op_mul_mat_f32");
+    return launch_logits_any<float>(ctx, w, nullptr, x, dst, (int) ne00, (int) ne01, (int) T, nullptr, 0, static_cast<cudaStream_t>(stream));
 }
 
 // ---- probe of the block-scaled FP4 instruction (fp4_probe.cuh) -----------------------------------------------------------

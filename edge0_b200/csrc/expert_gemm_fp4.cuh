@@ -98,27 +98,35 @@ struct PlaneOut {
     int *     tile_expert;  // [tiles] expert of every token tile
 };
 
-// digits, codes and scale bytes of one item: 16-block g, byte j (elements 16g + j and 16g + j + 8) with int8 values q0, q1 and
-// the fp32 bits of the block scale d (an fp16 number: d = M * 2^(exp8 - 137) with M the top 11 bits of the significand)
-__device__ __forceinline__ void plane_item(int q0, int q1, uint32_t dbits, int E_row, int it, int K, int in_tile, uint8_t * __restrict__ prow,
-                                           uint8_t * __restrict__ sft) {
-    const int g = it >> 3, j = it & 7;
+// digits, codes and scale bytes of one quad: 16-block g, bytes j0 .. j0+3 (elements 16g + j and 16g + j + 8) with int8 values lo[], hi[]
+// and the fp32 bits of the block scale d (an fp16 number: d = M * 2^(exp8 - 137) with M the top 11 bits of the significand).
+// The four code bytes of every plane leave as one 32-bit store.
+__device__ __forceinline__ void plane_quad(const int (&lo)[4], const int (&hi)[4], uint32_t dbits, int E_row, int g, int j0, int K, int in_tile,
+                                           uint8_t * __restrict__ prow, uint8_t * __restrict__ sft) {
     const bool nz = (dbits & 0x7fffffffu) != 0;
     const int M = nz ? (int) (((dbits & 0x7fffffu) | 0x800000u) >> 13) : 0;
     const int s = nz ? (int) ((dbits >> 23) & 0xff) - 137 - E_row + 8 : -100;           // scale exponent, at most 8
     const int Ms = s >= -9 ? M : 0;                                                     // flushed blocks contribute nothing
-    int p0 = q0 * Ms, p1 = q1 * Ms;
+    int p0[4], p1[4];
+#pragma unroll
+    for (int m = 0; m < 4; ++m) { p0[m] = lo[m] * Ms; p1[m] = hi[m] * Ms; }
+    uint32_t * pw = reinterpret_cast<uint32_t *>(prow + 8 * g + j0);
 #pragma unroll
     for (int p = 0; p < FP4_PLANES; ++p) {
-        const int d0 = p < FP4_PLANES - 1 ? ((p0 + 4) & 7) - 4 : p0, d1 = p < FP4_PLANES - 1 ? ((p1 + 4) & 7) - 4 : p1;
-        p0 = (p0 - d0) >> 3;
-        p1 = (p1 - d1) >> 3;
-        // E2M1 codes of 0,1,2,3,4: 0,2,4,5,6; sign in bit 3
-        const uint32_t c0 = ((0x65420u >> (4 * abs(d0))) & 0xfu) | (d0 < 0 ? 8u : 0u);
-        const uint32_t c1 = ((0x65420u >> (4 * abs(d1))) & 0xfu) | (d1 < 0 ? 8u : 0u);
-        prow[(size_t) p * (K / 2) + it] = (uint8_t) (c0 | (c1 << 4));
+        uint32_t word = 0;
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const int d0 = p < FP4_PLANES - 1 ? ((p0[m] + 4) & 7) - 4 : p0[m], d1 = p < FP4_PLANES - 1 ? ((p1[m] + 4) & 7) - 4 : p1[m];
+            p0[m] = (p0[m] - d0) >> 3;
+            p1[m] = (p1[m] - d1) >> 3;
+            // E2M1 codes of 0,1,2,3,4: 0,2,4,5,6; sign in bit 3
+            const uint32_t c0 = ((0x65420u >> (4 * abs(d0))) & 0xfu) | (d0 < 0 ? 8u : 0u);
+            const uint32_t c1 = ((0x65420u >> (4 * abs(d1))) & 0xfu) | (d1 < 0 ? 8u : 0u);
+            word |= (c0 | (c1 << 4)) << (8 * m);
+        }
+        pw[(size_t) p * (K / 8)] = word;
     }
-    if (j == 0) {
+    if (j0 == 0) {
         // UE4M3 byte of 2^s: normal for s >= -6, the three power-of-two subnormals below, zero when flushed
         const uint32_t sb = s >= -6 ? (uint32_t) (s + 7) << 3 : s == -7 ? 4u : s == -8 ? 2u : s == -9 ? 1u : 0u;
         uint8_t * dst = sft + (size_t) (g >> 4) * FP4_SF_TILE + ((g >> 2) & 3) * 512 + (g & 3);
@@ -127,84 +135,104 @@ __device__ __forceinline__ void plane_item(int q0, int q1, uint32_t dbits, int E
     }
 }
 
-// One CTA per expert-sorted routed row.  SRC_F32 = false: the row's activations are already quantised (ActQuant planes, Q8_0).
+// K / 8 threads per expert-sorted routed row (at most 256: a block holds 256 * 8 / K rows, and a thread two quads when K = 4096).
+// SRC_F32 = false: the row's activations are already quantised (ActQuant planes, Q8_0).
 // SRC_F32 = true: they are fp32 (`src`, rows `src_stride` floats apart) and are quantised here exactly as quantize_q8_0_block
-// does it (d = half(amax / 127), q = rint(v * (127 / amax))), which saves the separate quantisation pass over `hidden`.
+// does it (d = half(amax / 127), q = rint(v * (127 / amax))), which saves the separate quantisation pass; `emit`, when it has
+// planes, receives that quantised form as well (row index as in `src`).
 template <bool SRC_F32>
 __global__ void __launch_bounds__(256) act_planes_kernel(ActQuant act, const float * __restrict__ src, int64_t src_stride,
                                                         const int * __restrict__ perm, const int32_t * __restrict__ ids,
                                                         const int * __restrict__ offsets, const int * __restrict__ tile_of_expert,
                                                         const int * __restrict__ meta, int rows, int K, int n_ids, int ne11, int n_as,
-                                                        PlaneOut out) {
-    constexpr int MAX_ITEMS = 8;                   // K / 2 items over 256 threads, K <= 4096
-    __shared__ int s_emax[8];
-    __shared__ int s_E;
-    const int i = blockIdx.x;                      // sorted position
-    if (i >= rows || i >= meta[1]) return;         // meta[1]: rows that are in a group (fewer than `rows` when slots are empty)
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int r = perm[i];
-    const int arow = (r / n_ids) * ne11 + (r % n_ids) % ne11;
-    int e = ids[r];
-    e = e < 0 ? 0 : (e >= n_as ? n_as - 1 : e);    // bad ids were reported by the grouping kernels; stay inside the tables
-    const int row_beg = offsets[e];
-    const int in_tile = (i - row_beg) % FP4_RPT;
-    const int tile = tile_of_expert[e] + (i - row_beg) / FP4_RPT;
-    if (in_tile == 0 && tid == 0) out.tile_expert[tile] = e;
+                                                        PlaneOut out, ActQuant emit) {
+    constexpr int MAX_QUADS = 2;
+    __shared__ int s_E[8];
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int tpr = min(256, K / 8), rpb = 256 / tpr, qpt = (K / 8) / tpr;
+    const int lrow = tid / tpr, t_in = tid % tpr;
+    const int i = blockIdx.x * rpb + lrow;          // sorted position
+    if (tid < 8) s_E[tid] = -1000;
+    __syncthreads();
+    // meta[1]: rows that are in a group (fewer than `rows` when slots are empty); threads beyond the block's last whole row idle (K = 768)
+    const bool live = lrow < rpb && i < rows && i < meta[1];
+    int arow = 0, in_tile = 0, tile = 0;
+    if (live) {
+        const int r = perm[i];
+        arow = (r / n_ids) * ne11 + (r % n_ids) % ne11;
+        int e = ids[r];
+        e = e < 0 ? 0 : (e >= n_as ? n_as - 1 : e);    // bad ids were reported by the grouping kernels; stay inside the tables
+        const int row_beg = offsets[e];
+        in_tile = (i - row_beg) % FP4_RPT;
+        tile = tile_of_expert[e] + (i - row_beg) / FP4_RPT;
+        if (in_tile == 0 && t_in == 0) out.tile_expert[tile] = e;
+    }
     const int nb32 = K / 32;
-    uint8_t * prow = out.planes + (size_t) i * FP4_PLANES * (K / 2);
-    uint8_t * sft = out.sf + (size_t) tile * (K / 256) * FP4_SF_TILE;
-    int q0[MAX_ITEMS], q1[MAX_ITEMS];
-    uint32_t db[MAX_ITEMS];
+    int lo[MAX_QUADS][4], hi[MAX_QUADS][4];
+    uint32_t db[MAX_QUADS];
     int emax = -1000;
-    if (SRC_F32) {
-        const float * xrow = src + (size_t) arow * src_stride;
 #pragma unroll
-        for (int u = 0; u < MAX_ITEMS; ++u) {
-            const int it = tid + 256 * u;            // the 16 items of a 32-block sit in 16 consecutive lanes
-            const bool in = it < K / 2;
-            const int g = it >> 3, j = it & 7;
-            const float v0 = in ? xrow[16 * g + j] : 0.0f, v1 = in ? xrow[16 * g + j + 8] : 0.0f;
-            float amax = fmaxf(fabsf(v0), fabsf(v1));
+    for (int u = 0; u < MAX_QUADS; ++u) {
+        db[u] = 0u;
+        if (u < qpt && live) {
+            const int qd = t_in + tpr * u, g = qd >> 1, j0 = (qd & 1) * 4;
+            if (SRC_F32) {
+                const float * xrow = src + (size_t) arow * src_stride + 16 * g + j0;
+                const float4 a = *reinterpret_cast<const float4 *>(xrow), b = *reinterpret_cast<const float4 *>(xrow + 8);
+                const float va[4] = { a.x, a.y, a.z, a.w }, vb[4] = { b.x, b.y, b.z, b.w };
+                float amax = 0.0f;
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            const float d = __half2float(__float2half_rn(__fdiv_rn(amax, 127.0f)));
-            const float id = amax != 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
-            q0[u] = __float2int_rn(__fmul_rn(v0, id));
-            q1[u] = __float2int_rn(__fmul_rn(v1, id));
-            db[u] = in ? __float_as_uint(d) : 0u;
+                for (int m = 0; m < 4; ++m) amax = fmaxf(amax, fmaxf(fabsf(va[m]), fabsf(vb[m])));
+                // the four quads of a 32-block sit in four consecutive lanes (all live or none: a row never splits a warp)
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                const float d = __half2float(__float2half_rn(__fdiv_rn(amax, 127.0f)));
+                const float id = amax != 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    lo[u][m] = __float2int_rn(__fmul_rn(va[m], id));
+                    hi[u][m] = __float2int_rn(__fmul_rn(vb[m], id));
+                }
+                db[u] = __float_as_uint(d);
+                if (emit.q) {
+                    int8_t * qo = emit.q + (size_t) arow * K + 16 * g + j0;
+                    *reinterpret_cast<uint32_t *>(qo) = (uint32_t) (lo[u][0] & 0xff) | ((uint32_t) (lo[u][1] & 0xff) << 8) |
+                                                        ((uint32_t) (lo[u][2] & 0xff) << 16) | ((uint32_t) (lo[u][3] & 0xff) << 24);
+                    *reinterpret_cast<uint32_t *>(qo + 8) = (uint32_t) (hi[u][0] & 0xff) | ((uint32_t) (hi[u][1] & 0xff) << 8) |
+                                                            ((uint32_t) (hi[u][2] & 0xff) << 16) | ((uint32_t) (hi[u][3] & 0xff) << 24);
+                    if ((qd & 3) == 0) emit.d[(size_t) arow * nb32 + (g >> 1)] = d;
+                }
+            } else {
+                const int8_t * qrow = act.q + (size_t) arow * K + 16 * g + j0;
+                const uint32_t wa = *reinterpret_cast<const uint32_t *>(qrow), wb = *reinterpret_cast<const uint32_t *>(qrow + 8);
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    lo[u][m] = (int) (int8_t) (wa >> (8 * m));
+                    hi[u][m] = (int) (int8_t) (wb >> (8 * m));
+                }
+                db[u] = __float_as_uint(act.d[(size_t) arow * nb32 + (g >> 1)]);
+            }
             if (db[u] & 0x7fffffffu) emax = max(emax, (int) ((db[u] >> 23) & 0xff) - 137);
-        }
-    } else {
-        const float * drow = act.d + (size_t) arow * nb32;
-        const int8_t * qrow = act.q + (size_t) arow * K;
-#pragma unroll
-        for (int u = 0; u < MAX_ITEMS; ++u) {
-            const int it = tid + 256 * u;
-            const bool in = it < K / 2;
-            const int g = it >> 3, j = it & 7;
-            q0[u] = in ? (int) qrow[16 * g + j] : 0;
-            q1[u] = in ? (int) qrow[16 * g + j + 8] : 0;
-            db[u] = in ? __float_as_uint(drow[g >> 1]) : 0u;
-            if (db[u] & 0x7fffffffu) emax = max(emax, (int) ((db[u] >> 23) & 0xff) - 137);
+        } else if (SRC_F32 && u < qpt) {   // keep the warp's shuffles uniform
+            __shfl_xor_sync(0xffffffffu, 0.0f, 1);
+            __shfl_xor_sync(0xffffffffu, 0.0f, 2);
         }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) emax = max(emax, __shfl_xor_sync(0xffffffffu, emax, o));
-    if (lane == 0) s_emax[warp] = emax;
+    if (lane == 0 && live) atomicMax(&s_E[lrow], emax);
     __syncthreads();
-    if (tid == 0) {
-        int m = s_emax[0];
-        for (int w = 1; w < 8; ++w) m = max(m, s_emax[w]);
-        s_E = m;
-        out.row_scale[i] = m > -1000 ? __uint_as_float((uint32_t) (m - 8 + 127) << 23) : 0.0f;   // 2^(E_row - 8): far from the fp32 limits
-    }
-    __syncthreads();
-    const int E_row = s_E;
+    if (!live) return;
+    const int E_row = s_E[lrow];
+    if (t_in == 0) out.row_scale[i] = E_row > -1000 ? __uint_as_float((uint32_t) (E_row - 8 + 127) << 23) : 0.0f;   // 2^(E_row - 8): far from the fp32 limits
+    uint8_t * prow = out.planes + (size_t) i * FP4_PLANES * (K / 2);
+    uint8_t * sft = out.sf + (size_t) tile * (K / 256) * FP4_SF_TILE;
 #pragma unroll
-    for (int u = 0; u < MAX_ITEMS; ++u) {
-        const int it = tid + 256 * u;
-        if (it < K / 2) plane_item(q0[u], q1[u], db[u], E_row, it, K, in_tile, prow, sft);
-    }
+    for (int u = 0; u < MAX_QUADS; ++u)
+        if (u < qpt) {
+            const int qd = t_in + tpr * u;
+            plane_quad(lo[u], hi[u], db[u], E_row, qd >> 1, (qd & 1) * 4, K, in_tile, prow, sft);
+        }
 }
 
 // Development builds (-DB200MOE_FP4_PROF) record, per CTA, the cycles each role spends waiting on each of its barriers.

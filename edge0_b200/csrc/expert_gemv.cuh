@@ -215,6 +215,57 @@ __device__ __forceinline__ void lane_chain_split(const uint8_t * __restrict__ ro
     acc[0] = a;
 }
 
+// The same chain run by a whole warp for ONE row: the four 8-lane groups split the half-blocks between them (group rg takes
+// units rg, rg + 4, ...), every lane fetches and decodes its share with all loads in flight at once, and the fp32 chain - which
+// must stay sequential to keep the reference's bits - then collects scale and dot product of every unit in order through
+// shuffles.  All four groups end with the same eight partial sums; the result is valid in every lane.
+template <int K>
+__device__ __forceinline__ float lane_chain_warp(const uint8_t * __restrict__ row, int lane, const uint8_t * __restrict__ q,
+                                                 const float * __restrict__ d, const float * __restrict__ ue_tab) {
+    constexpr int UNITS = K / 32, UPL = UNITS / 4;
+    static_assert(UNITS % 4 == 0, "half-blocks must split over four lane groups");
+    const int L = lane & 7, rg = lane >> 3;
+    const int sub_in_half = L >> 2, mp = L & 3;
+    const int word_off = 4 + 8 * sub_in_half + 4 * (mp & 1);
+    const int nib_shift = 4 * (mp >> 1);
+    uint32_t w[UPL], aw[UPL], dw[UPL];
+    float dy[UPL];
+#pragma unroll
+    for (int i = 0; i < UPL; ++i) {
+        const int u = 4 * i + rg, b = u >> 1, hf = u & 1;
+        const uint8_t * blk = row + b * NVFP4_BLOCK_BYTES;
+        dw[i] = *reinterpret_cast<const uint32_t *>(blk);
+        w[i] = *reinterpret_cast<const uint32_t *>(blk + 16 * hf + word_off);
+        aw[i] = reinterpret_cast<const uint32_t *>(q)[u * 8 + L];
+        dy[i] = d[u];
+    }
+    float sd[UPL], pf[UPL];
+#pragma unroll
+    for (int i = 0; i < UPL; ++i) {
+        const int hf = (4 * i + rg) & 1;
+        const uint32_t t4 = (w[i] >> nib_shift) & 0x0f0f0f0fu;
+        const uint32_t u8 = t4 | (t4 >> 4);
+        const uint32_t sel = (u8 & 0xffff00ffu) | ((u8 >> 8) & 0x0000ff00u);
+        const uint32_t pos = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel);
+        const uint32_t neg = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel ^ 0x8888u);
+        const uint32_t code = pos | ((0x80808080u - neg) ^ 0x80808080u);
+        const float sw = ue_tab[(dw[i] >> (8 * (2 * hf + sub_in_half))) & 0xff];
+        sd[i] = __fmul_rn(sw, dy[i]);
+        pf[i] = small_int_to_float(dot4((int) code, (int) aw[i], 0));
+    }
+    float a = 0.0f;
+#pragma unroll
+    for (int u = 0; u < UNITS; ++u) {
+        const int src = (u & 3) * 8 + L;
+        const float s = __shfl_sync(0xffffffffu, sd[u >> 2], src), pv = __shfl_sync(0xffffffffu, pf[u >> 2], src);
+        a = __fmaf_rn(s, pv, a);
+    }
+    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 4));
+    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 2));
+    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 1));
+    return a;
+}
+
 // chunk walker shared by the producer thread and the consumers
 struct Chunk {
     int a;      // index into active[]

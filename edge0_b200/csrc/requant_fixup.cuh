@@ -39,52 +39,72 @@ __device__ __forceinline__ bool near_half_rounding_boundary(float x, float rel) 
     return fabsf(x - 0.5f * (lo + hi)) <= rel * x;
 }
 
-// One warp per (routed row, block of 32 features).
+// One warp per (routed row, 128 features): a lane holds four neighbouring values, eight lanes one block of 32.
 //   step_margin : distance from a rounding boundary, in quantisation steps, below which a value is recomputed
 //   rel_margin  : relative distance from the block maximum below which a value counts as a candidate for it; the same
 //                 relative uncertainty of the scale widens the step margin of large values
-//   perm        : routed rows sorted by expert.  Warps walk (feature block, sorted row) with the row fastest, so values that need
-//                 the same weight rows (same expert, same 32 features) are listed next to each other and the recomputation
+//   perm        : routed rows sorted by expert.  Warps walk (feature chunk, sorted row) with the row fastest, so values that need
+//                 the same weight rows (same expert, same features) are listed next to each other and the recomputation
 //                 finds those rows in cache instead of fetching 2 x row_bytes from HBM per value.
 //   meta[1]     : number of routed rows that are in a group (fewer than `rows` when an exchange left slots empty)
+// n_ff must be a multiple of 128 and the rows 16-byte aligned.
 __global__ void __launch_bounds__(256) requant_mark_kernel(const float * __restrict__ hid, const int * __restrict__ perm, const int * __restrict__ meta,
                                                           int rows, int n_ff, float step_margin, float rel_margin, FixList list) {
     pdl_wait();
     pdl_launch_dependents();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    const int nb = n_ff / 32;
-    if (warp >= rows * nb || warp % rows >= meta[1]) return;
-    const int b = warp / rows, r = perm[warp % rows];
-    const float v = hid[(size_t) r * n_ff + b * 32 + lane];
-    const float a = fabsf(v);
-    float amax = a;
+    const int chunks = n_ff / 128;
+    if (warp >= rows * chunks || warp % rows >= meta[1]) return;
+    const int c = warp / rows, r = perm[warp % rows];
+    const int f0 = c * 128 + lane * 4;
+    const float4 v4 = *reinterpret_cast<const float4 *>(hid + (size_t) r * n_ff + f0);
+    const float a[4] = { fabsf(v4.x), fabsf(v4.y), fabsf(v4.z), fabsf(v4.w) };
+    float amax = fmaxf(fmaxf(a[0], a[1]), fmaxf(a[2], a[3]));
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    bool risky = false;
+    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // the block's eight lanes
+    bool risky[4] = { false, false, false, false };
     if (amax > 0.0f) {
         const float id = 127.0f / amax;
-        const float t = a * id;                                   // 0 .. 127
-        const float dist = fabsf((t - floorf(t)) - 0.5f);         // distance from the rounding boundary, in steps
-        // the block scale half(amax / 127) is in doubt only near an fp16 rounding boundary: then every candidate for the maximum counts
-        risky = dist < step_margin + t * rel_margin;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float t = a[j] * id;                                // 0 .. 127
+            const float dist = fabsf((t - floorf(t)) - 0.5f);         // distance from the rounding boundary, in steps
+            risky[j] = dist < step_margin + t * rel_margin;
+        }
     }
-    // the maximum's candidates: when the block scale is in doubt, or when a value of the block is recomputed (its rounding is only
-    // decided against the exact maximum)
-    const bool need_max = __any_sync(0xffffffffu, risky) || (amax > 0.0f && near_half_rounding_boundary(amax / 127.0f, 2.0f * rel_margin));
-    risky = risky || (need_max && amax > 0.0f && a >= amax * (1.0f - rel_margin));
-    const uint32_t m = __ballot_sync(0xffffffffu, risky);
-    if (m == 0) return;
+    // the maximum's candidates: when the block scale half(amax / 127) is in doubt (near an fp16 rounding boundary), or when a value of
+    // the block is recomputed (its rounding is only decided against the exact maximum)
+    const uint32_t any = __ballot_sync(0xffffffffu, risky[0] || risky[1] || risky[2] || risky[3]);
+    const bool block_any = ((any >> (lane & 24)) & 0xffu) != 0;
+    const bool need_max = block_any || (amax > 0.0f && near_half_rounding_boundary(amax / 127.0f, 2.0f * rel_margin));
+    int n_mine = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        risky[j] = risky[j] || (need_max && amax > 0.0f && a[j] >= amax * (1.0f - rel_margin));
+        n_mine += risky[j] ? 1 : 0;
+    }
+    int incl = n_mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    const int total = __shfl_sync(0xffffffffu, incl, 31);
+    if (total == 0) return;
     int base = 0;
     if (lane == 0) {
-        base = atomicAdd(list.count, __popc(m));
-        const int over = base + __popc(m) - max(base, list.capacity);
+        base = atomicAdd(list.count, total);
+        const int over = base + total - max(base, list.capacity);
         if (over > 0 && list.overflow) atomicAdd(list.overflow, (unsigned long long) over);
     }
     base = __shfl_sync(0xffffffffu, base, 0);
-    if (risky) {
-        const int slot = base + __popc(m & ((1u << lane) - 1));
-        if (slot < list.capacity) list.items[slot] = make_int2(r, b * 32 + lane);
-    }
+    int slot = base + incl - n_mine;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (risky[j]) {
+            if (slot < list.capacity) list.items[slot] = make_int2(r, f0 + j);
+            ++slot;
+        }
 }
 
 struct FixParams {
@@ -102,10 +122,11 @@ struct FixParams {
     int * err;
 };
 
-// 8 lanes per listed value (the reference's 8 SIMD lanes), 4 values per warp at a time.  Each group runs the same chains as
-// the integer GEMV, so the patched value is the reference's, bit for bit; weight rows and activations are read straight from
-// global memory (the activations and most weight rows are L2-resident right after the GEMM), and latency is hidden by
-// occupancy instead of a staging ring - the listed values are scattered, there is nothing to stream.
+// One warp per listed value (lane_chain_warp): the reference's 8 SIMD lanes run the fp32 chain, all 32 lanes fetch and decode, so
+// every load of a value is in flight at once and the kernel's time is a few memory round trips, not one per group of blocks.
+// The patched value is the reference's, bit for bit; weight rows and activations are read straight from global memory (the
+// activations and most weight rows are L2-resident right after the GEMM) - the listed values are scattered, there is nothing to
+// stream.
 template <int K>
 __global__ void __launch_bounds__(256) requant_fix_kernel(const FixParams p) {
     constexpr int ROW_BYTES = K / 64 * NVFP4_BLOCK_BYTES;
@@ -113,29 +134,23 @@ __global__ void __launch_bounds__(256) requant_fix_kernel(const FixParams p) {
     pdl_wait();
     pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int L = lane & 7, rgrp = lane >> 3;
     ue_tab[tid] = ue4m3_half_to_f32(tid);
     __syncthreads();
     const int n = min(*p.list.count, p.list.capacity);
-    const int groups_per_grid = gridDim.x * 32;
-    // warp-uniform trip count: every lane runs the chains (their shuffles use the full mask); idle groups redo item 0
-    for (int base = (blockIdx.x * 8 + warp) * 4; base < n; base += groups_per_grid) {
-        const int i = base + rgrp;
-        const bool valid = i < n;
-        const int2 it = p.list.items[valid ? i : 0];
+    for (int i = blockIdx.x * 8 + warp; i < n; i += gridDim.x * 8) {
+        const int2 it = p.list.items[i];
         const int r = it.x, f = it.y;
         int e = p.ids[r];
         if (e < 0 || e >= p.n_as) { report_error(p.err, DEV_ERR_BAD_EXPERT_ID); e = 0; }
         const int tok = r / p.n_ids;
-        const uint8_t * g_row = p.w0 + ((size_t) e * p.n_ff + f) * ROW_BYTES;
-        const uint8_t * u_row = p.w1 + ((size_t) e * p.n_ff + f) * ROW_BYTES;
-        float g[1], u[1];
-        lane_chain_split<K>(g_row, L, reinterpret_cast<const uint8_t *>(p.act.q + (size_t) tok * K), p.act.d + (size_t) tok * (K / 32), ue_tab, g);
-        lane_chain_split<K>(u_row, L, reinterpret_cast<const uint8_t *>(p.act.q + (size_t) tok * K), p.act.d + (size_t) tok * (K / 32), ue_tab, u);
-        if (valid && L == 0) {
+        const uint8_t * q = reinterpret_cast<const uint8_t *>(p.act.q + (size_t) tok * K);
+        const float * d = p.act.d + (size_t) tok * (K / 32);
+        const float g = lane_chain_warp<K>(p.w0 + ((size_t) e * p.n_ff + f) * ROW_BYTES, lane, q, d, ue_tab);
+        const float u = lane_chain_warp<K>(p.w1 + ((size_t) e * p.n_ff + f) * ROW_BYTES, lane, q, d, ue_tab);
+        if (lane == 0) {
             const float sc0 = p.scale0 ? p.scale0[e] : 1.0f, sc1 = p.scale1 ? p.scale1[e] : 1.0f;
-            const float v = __fmul_rn(g[0], sc0);
-            p.hid[(size_t) r * p.n_ff + f] = __fmul_rn(ggml_silu(v), __fmul_rn(u[0], sc1));
+            const float v = __fmul_rn(g, sc0);
+            p.hid[(size_t) r * p.n_ff + f] = __fmul_rn(ggml_silu(v), __fmul_rn(u, sc1));
         }
     }
 }
@@ -156,20 +171,15 @@ __global__ void __launch_bounds__(256) requant_fix_single_kernel(const FixSingle
     constexpr int ROW_BYTES = K / 64 * NVFP4_BLOCK_BYTES;
     __shared__ float ue_tab[256];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int L = lane & 7, rgrp = lane >> 3;
     ue_tab[tid] = ue4m3_half_to_f32(tid);
     __syncthreads();
     const int n = min(*p.list.count, p.list.capacity);
-    const int groups_per_grid = gridDim.x * 32;
-    for (int base = (blockIdx.x * 8 + warp) * 4; base < n; base += groups_per_grid) {
-        const int i = base + rgrp;
-        const bool valid = i < n;
-        const int2 it = p.list.items[valid ? i : 0];
+    for (int i = blockIdx.x * 8 + warp; i < n; i += gridDim.x * 8) {
+        const int2 it = p.list.items[i];
         const int tok = it.x, f = it.y;
-        float g[1];
-        lane_chain_split<K>(p.w + (size_t) f * ROW_BYTES, L, reinterpret_cast<const uint8_t *>(p.act.q + (size_t) tok * K), p.act.d + (size_t) tok * (K / 32),
-                            ue_tab, g);
-        if (valid && L == 0) p.y[(size_t) tok * p.n_out + f] = p.scale ? __fmul_rn(g[0], p.scale[0]) : g[0];
+        const float g = lane_chain_warp<K>(p.w + (size_t) f * ROW_BYTES, lane, reinterpret_cast<const uint8_t *>(p.act.q + (size_t) tok * K),
+                                           p.act.d + (size_t) tok * (K / 32), ue_tab);
+        if (lane == 0) p.y[(size_t) tok * p.n_out + f] = p.scale ? __fmul_rn(g, p.scale[0]) : g;
     }
 }
 

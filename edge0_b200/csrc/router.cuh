@@ -126,6 +126,99 @@ __global__ void __launch_bounds__(256) router_logits_tiled_kernel(const float * 
         }
 }
 
+// Shared-memory form for larger batches: a block owns (8 WE experts) x (8 WT tokens); weight and activation rows arrive in
+// 128-element pieces through a three-deep cp.async ring, and every warp runs an 8 x 8 register tile out of shared memory.  The
+// chains are the reference's (lane l owns elements l, l + 32, ... in increasing order), so the logits keep its bits; what changes is
+// that global loads are 16 bytes wide, issued two pieces ahead, and shared by the whole tile.
+// Needs H to be a multiple of 128 and 16-byte aligned rows.
+constexpr int ROUTER_KC = 128, ROUTER_ST = 3;
+template <int WE, int WT, typename XT>
+constexpr size_t router_smem_bytes() { return (size_t) ROUTER_ST * ROUTER_KC * (8 * WE * sizeof(float) + 8 * WT * sizeof(XT)); }
+
+__device__ __forceinline__ void cp_async16(void * smem, const void * gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t) __cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int WE, int WT, typename XT>
+__global__ void __launch_bounds__(WE * WT * 32) router_logits_smem_kernel(const float * __restrict__ W, const float * __restrict__ bias,
+                                                                         const XT * __restrict__ x, float * __restrict__ logits, int H, int E, int T,
+                                                                         int * __restrict__ zero_buf, int zero_n) {
+    constexpr int EB = 8 * WE, TB = 8 * WT, KC = ROUTER_KC, ST = ROUTER_ST, NTHR = WE * WT * 32;
+    constexpr int XP = 16 / sizeof(XT);   // activation elements per 16-byte piece
+    extern __shared__ __align__(16) uint8_t router_smem[];
+    float (*ws)[EB][KC] = reinterpret_cast<float (*)[EB][KC]>(router_smem);
+    XT (*xs)[TB][KC] = reinterpret_cast<XT (*)[TB][KC]>(router_smem + (size_t) ST * EB * KC * sizeof(float));
+    pdl_wait();
+    pdl_launch_dependents();
+    if (blockIdx.x == 0)
+        for (int i = threadIdx.x; i < zero_n; i += NTHR) zero_buf[i] = 0;
+    const int n_eb = (E + EB - 1) / EB;
+    const int e0 = (blockIdx.x % n_eb) * EB, t0 = (blockIdx.x / n_eb) * TB;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int we = (warp % WE) * 8, wt = (warp / WE) * 8;
+    const int n_chunks = H / KC;
+
+    auto load_chunk = [&](int c) {
+        const int s = c % ST;
+        for (int i = threadIdx.x; i < EB * (KC / 4); i += NTHR) {
+            const int r = i / (KC / 4), q = i % (KC / 4);
+            cp_async16(&ws[s][r][q * 4], W + (size_t) min(e0 + r, E - 1) * H + (size_t) c * KC + q * 4);
+        }
+        for (int i = threadIdx.x; i < TB * (KC / XP); i += NTHR) {
+            const int r = i / (KC / XP), q = i % (KC / XP);
+            cp_async16(&xs[s][r][q * XP], x + (size_t) min(t0 + r, T - 1) * H + (size_t) c * KC + q * XP);
+        }
+    };
+    float acc[8][8];
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) acc[a][b] = 0.0f;
+#pragma unroll
+    for (int c = 0; c < ST - 1; ++c) {
+        if (c < n_chunks) load_chunk(c);
+        cp_async_commit();
+    }
+    for (int c = 0; c < n_chunks; ++c) {
+        cp_async_wait<ST - 2>();   // piece c has landed (one younger group may still be in flight)
+        __syncthreads();           // ... for every thread, and everybody is done with the stage the next load overwrites
+        if (c + ST - 1 < n_chunks) load_chunk(c + ST - 1);
+        cp_async_commit();
+        const int s = c % ST;
+#pragma unroll
+        for (int kk = 0; kk < KC / 32; ++kk) {
+            float wv[8], xv[8];
+#pragma unroll
+            for (int a = 0; a < 8; ++a) wv[a] = ws[s][we + a][kk * 32 + lane];
+#pragma unroll
+            for (int b = 0; b < 8; ++b) xv[b] = (float) xs[s][wt + b][kk * 32 + lane];
+#pragma unroll
+            for (int a = 0; a < 8; ++a)
+#pragma unroll
+                for (int b = 0; b < 8; ++b) acc[a][b] = __fmaf_rn(wv[a], xv[b], acc[a][b]);
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            float v = acc[a][b];
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 16));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 8));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+            const int e = e0 + we + a, t = t0 + wt + b;
+            if (lane == 0 && e < E && t < T) {
+                if (bias) v = __fadd_rn(v, bias[e]);
+                logits[(size_t) t * E + e] = v;
+            }
+        }
+}
+
 // ---- activation quantisers -------------------------------------------------------------------------
 // Q8_0 as the reference's AVX2 quantize_row_q8_0 (ggml-cpu/arch/x86/quants.c:302-367): d = amax/127 kept
 // as half, multiplier 127/amax in fp32, round to nearest even.  One warp per 32-element block... here one
@@ -411,13 +504,16 @@ struct Groups {
 __device__ __forceinline__ void group_scan_body(Groups g, const int32_t * __restrict__ ids, int E, int rows, int * err, int * sh, bool allow_empty = false) {
     int * off = sh;
     int * act = sh + (E + 1);  // act[a] = a-th active expert (also written to g.active)
+    int * cnt = sh + (2 * E + 1);  // counts, fetched by the whole block at once (the scan below would wait for memory 32 at a time)
     const int tid = threadIdx.x;
+    for (int e = tid; e < E; e += blockDim.x) cnt[e] = g.counts[e];
+    __syncthreads();
     if (tid < 32) {
         // warp 0: exclusive scan of counts, compaction of active experts and the three work prefixes, 32 experts a step
         int run = 0, na = 0, c1 = 0, c2 = 0, c4 = 0, tl = 0;
         for (int base = 0; base < E; base += 32) {
             const int e = base + tid;
-            const int n = e < E ? g.counts[e] : 0;
+            const int n = e < E ? cnt[e] : 0;
             // work per weight row: nt=1 kernels: one pass per routed row; nt=4 kernels: 3 per pass (decode) + 2 per routed row
             int incl = n, w2 = (n + 1) / 2, w4 = 3 * ((n + 3) / 4) + 2 * n;
             int i2 = w2, i4 = w4, it = (n + TOKEN_TILE_ROWS - 1) / TOKEN_TILE_ROWS;
@@ -463,12 +559,31 @@ __device__ __forceinline__ void group_scan_body(Groups g, const int32_t * __rest
     }
 }
 
+// The grouping of a dense product: every one of the T rows belongs to the single group 0 (one launch instead of the
+// count / scan pair; same tables as group_scan_body leaves for E = 1).
+__global__ void __launch_bounds__(256) one_group_kernel(Groups g, int32_t * __restrict__ ids, int T) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < T) { ids[t] = 0; g.perm[t] = t; }
+    if (t == 0) {
+        g.counts[0] = T;
+        g.offsets[0] = 0; g.offsets[1] = T;
+        g.active[0] = 0;
+        g.meta[0] = 1; g.meta[1] = T;
+        g.cost[0] = 0; g.cost[1] = T;
+        g.cost[2] = 0; g.cost[3] = (T + 1) / 2;
+        g.cost[4] = 0; g.cost[5] = 3 * ((T + 3) / 4) + 2 * T;
+        g.cost[6] = 0; g.cost[7] = (T + TOKEN_TILE_ROWS - 1) / TOKEN_TILE_ROWS;
+    }
+}
+
 // Single block.  counts must be final (selection kernel finished).
 __global__ void __launch_bounds__(1024) group_scan_kernel(Groups g, const int32_t * __restrict__ ids, int E, int rows, int * err, int allow_empty) {
     pdl_wait();
     pdl_launch_dependents();
 
-    extern __shared__ int sh[];  // [E+1] offsets, [E] active flags
+    extern __shared__ int sh[];  // [E+1] offsets, [E] active experts, [E] counts
     group_scan_body(g, ids, E, rows, err, sh, allow_empty != 0);
 }
 
