@@ -399,10 +399,11 @@ def run_c5_arm(args):
     ctx.synchronize()
     clocks = sampler.stop()
     step_ms = ms_total / args.steps
-    c0 = ctx.launches()
+    all_ctx = [ctx] + [e.b.ctx_router for e in eps]          # the router runs in a context (and on a stream) of its own
+    c0 = sum(c.launches() for c in all_ctx)
     eager(0)
-    ctx.synchronize()
-    launches = (ctx.launches() - c0) * args.steps
+    torch.cuda.synchronize()
+    launches = (sum(c.launches() for c in all_ctx) - c0) * args.steps
 
     # end to end: this rank's tokens start in pinned host memory and the result returns to the host every step
     xh = [x.cpu().pin_memory() for x in xs]

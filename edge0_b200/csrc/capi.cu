@@ -865,7 +865,7 @@ int dense_matmul_fp4(b200moe_ctx * ctx, const void * w, const float * scale, con
     const int64_t warps = (int64_t) T * (n_out / 128);
     requant_mark_kernel<<<(unsigned) ((warps * 32 + 255) / 256), 256, 0, st>>>(y, p.groups.perm, p.groups.meta, T, n_out, FIX_STEP_MARGIN_FP4, FIX_REL_MARGIN_FP4, list);
     if ((rc = check_launch(ctx, "requant_mark"))) return rc;
-    FixSingleParams fs{ static_cast<const uint8_t *>(w), scale, xq, n_out, y, list };
+    FixSingleParams fs{ static_cast<const uint8_t *>(w), scale, xq, n_out, y, list, FIX_REL_MARGIN_FP4 };
     switch (k) {
         case 256: return launch_fix_single_t<256>(ctx, fs, st);
         case 512: return launch_fix_single_t<512>(ctx, fs, st);
@@ -917,19 +917,27 @@ int route_impl(b200moe_ctx * ctx, const b200moe_layer * l, const XT * x, int T, 
 
 template <int K>
 int launch_fix_t(b200moe_ctx * ctx, const FixParams & fp, cudaStream_t st) {
-    launch_k(ctx, requant_fix_kernel<K>, dim3(ctx->sm_count * 8), dim3(256), 0, st, fp);
+    constexpr size_t smem = requant_fix_smem_bytes<K>();
+    static bool configured[MAX_DEVICE_ORDINALS] = {};
+    if (int rc = raise_smem_limit(ctx, requant_fix_kernel<K>, smem, configured)) return rc;
+    launch_k(ctx, requant_fix_kernel<K>, dim3(ctx->sm_count * 8), dim3(256), smem, st, fp);
     return check_launch(ctx, "requant_fix");
 }
 
 int launch_requant_fixup(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq, int rows, int n_in, int n_ids, bool after_fp4, cudaStream_t st) {
     Plan & p = ctx->plan;
-    FixList list;
+    // two lists in the `down` output buffer (not in use yet): marked values, then the block-maximum candidates the first pass finds
+    const size_t room = (size_t) rows * n_in * sizeof(float) / sizeof(int2);
+    FixList list, more;
     list.items = reinterpret_cast<int2 *>(p.y);
     list.count = p.groups.meta + 2;
-    const size_t room = (size_t) rows * n_in * sizeof(float) / sizeof(int2);
-    list.capacity = (int) std::min<size_t>(room, (size_t) rows * l->n_ff / 4);
+    list.capacity = (int) std::min<size_t>(room * 3 / 4, (size_t) rows * l->n_ff / 4);
     list.overflow = reinterpret_cast<unsigned long long *>(ctx->d_err + 2);
-    CUDA_TRY(ctx, cudaMemsetAsync(list.count, 0, sizeof(int), st));
+    more.items = list.items + room * 3 / 4;
+    more.count = p.groups.meta + 3;
+    more.capacity = (int) (room - room * 3 / 4);
+    more.overflow = list.overflow;
+    CUDA_TRY(ctx, cudaMemsetAsync(list.count, 0, 2 * sizeof(int), st));
     const int64_t warps = (int64_t) rows * (l->n_ff / 128);
     launch_k(ctx, requant_mark_kernel, dim3((unsigned) ((warps * 32 + 255) / 256)), dim3(256), 0, st, (const float *) p.hid,
              (const int *) p.groups.perm, (const int *) p.groups.meta, rows, l->n_ff, after_fp4 ? FIX_STEP_MARGIN_FP4 : FIX_STEP_MARGIN, after_fp4 ? FIX_REL_MARGIN_FP4 : FIX_REL_MARGIN, list);
@@ -938,15 +946,22 @@ int launch_requant_fixup(b200moe_ctx * ctx, const b200moe_layer * l, ActQuant xq
     FixParams fp{};
     fp.w0 = static_cast<const uint8_t *>(l->gate); fp.w1 = static_cast<const uint8_t *>(l->up);
     fp.scale0 = l->gate_scale; fp.scale1 = l->up_scale; fp.act = xq; fp.ids = p.ids; fp.n_ids = n_ids; fp.n_ff = l->n_ff;
-    fp.n_as = l->n_expert; fp.hid = p.hid; fp.list = list; fp.err = ctx->d_err;
-    switch (n_in) {
-        case 256: return launch_fix_t<256>(ctx, fp, st);
-        case 512: return launch_fix_t<512>(ctx, fp, st);
-        case 768: return launch_fix_t<768>(ctx, fp, st);
-        case 1024: return launch_fix_t<1024>(ctx, fp, st);
-        case 2048: return launch_fix_t<2048>(ctx, fp, st);
+    fp.n_as = l->n_expert; fp.hid = p.hid; fp.list = list; fp.more = more; fp.err = ctx->d_err; fp.rel_margin = after_fp4 ? FIX_REL_MARGIN_FP4 : FIX_REL_MARGIN;
+    FixParams second = fp;      // the second pass recomputes what the first one found and looks no further
+    second.list = more;
+    second.more = FixList{};
+    for (const FixParams * pass : { &fp, &second }) {
+        switch (n_in) {
+            case 256: rc = launch_fix_t<256>(ctx, *pass, st); break;
+            case 512: rc = launch_fix_t<512>(ctx, *pass, st); break;
+            case 768: rc = launch_fix_t<768>(ctx, *pass, st); break;
+            case 1024: rc = launch_fix_t<1024>(ctx, *pass, st); break;
+            case 2048: rc = launch_fix_t<2048>(ctx, *pass, st); break;
+            default: return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no re-quantisation fix-up for width %d", n_in);
+        }
+        if (rc) return rc;
     }
-    return fail(ctx, B200MOE_ERR_UNSUPPORTED, "no re-quantisation fix-up for width %d", n_in);
+    return B200MOE_OK;
 }
 
 // experts on activations xe [T][n_in] (fp32), routing already grouped in the plan

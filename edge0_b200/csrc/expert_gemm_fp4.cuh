@@ -111,17 +111,24 @@ __device__ __forceinline__ void plane_quad(const int (&lo)[4], const int (&hi)[4
 #pragma unroll
     for (int m = 0; m < 4; ++m) { p0[m] = lo[m] * Ms; p1[m] = hi[m] * Ms; }
     uint32_t * pw = reinterpret_cast<uint32_t *>(prow + 8 * g + j0);
+    // Balanced radix-8 digits, lowest first: digit = ((p + 4) & 7) - 4 and carry (p + 4) >> 3.  The digit's E2M1 code comes from
+    // a table indexed by p & 7 (residues 0..3 are the digits 0..3, residues 4..7 the digits -4..-1): codes 0,2,4,5 and, with the
+    // sign bit, E,D,C,A.  The top plane takes what is left (|p| <= 4) through the magnitude table 0,2,4,5,6.
 #pragma unroll
     for (int p = 0; p < FP4_PLANES; ++p) {
         uint32_t word = 0;
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
-            const int d0 = p < FP4_PLANES - 1 ? ((p0[m] + 4) & 7) - 4 : p0[m], d1 = p < FP4_PLANES - 1 ? ((p1[m] + 4) & 7) - 4 : p1[m];
-            p0[m] = (p0[m] - d0) >> 3;
-            p1[m] = (p1[m] - d1) >> 3;
-            // E2M1 codes of 0,1,2,3,4: 0,2,4,5,6; sign in bit 3
-            const uint32_t c0 = ((0x65420u >> (4 * abs(d0))) & 0xfu) | (d0 < 0 ? 8u : 0u);
-            const uint32_t c1 = ((0x65420u >> (4 * abs(d1))) & 0xfu) | (d1 < 0 ? 8u : 0u);
+            uint32_t c0, c1;
+            if (p < FP4_PLANES - 1) {
+                c0 = (0xACDE5420u >> (4 * (p0[m] & 7))) & 0xfu;
+                c1 = (0xACDE5420u >> (4 * (p1[m] & 7))) & 0xfu;
+                p0[m] = (p0[m] + 4) >> 3;
+                p1[m] = (p1[m] + 4) >> 3;
+            } else {
+                c0 = ((0x65420u >> (4 * abs(p0[m]))) & 0xfu) | (p0[m] < 0 ? 8u : 0u);
+                c1 = ((0x65420u >> (4 * abs(p1[m]))) & 0xfu) | (p1[m] < 0 ? 8u : 0u);
+            }
             word |= (c0 | (c1 << 4)) << (8 * m);
         }
         pw[(size_t) p * (K / 8)] = word;

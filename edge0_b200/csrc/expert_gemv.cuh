@@ -110,7 +110,7 @@ __device__ __forceinline__ void lane_chain(const uint8_t * __restrict__ row, int
                 const uint32_t w = *reinterpret_cast<const uint32_t *>(blk + 16 * hf + word_off);
                 const uint32_t t4 = (w >> nib_shift) & 0x0f0f0f0fu;          // four codes, one per byte
                 const uint32_t u = t4 | (t4 >> 4);
-                const uint32_t sel = (u & 0xffff00ffu) | ((u >> 8) & 0x0000ff00u);   // the four codes packed into 16 bits
+                const uint32_t sel = byte_perm(u, 0u, 0x4420u);              // the four codes packed into 16 bits (bytes 0 and 2 of u)
                 const uint32_t pos = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel);
                 const uint32_t neg = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel ^ 0x8888u);
                 // signed bytes: a byte of `neg` is a magnitude 0..12, 0x80 - it never borrows, the xor drops the guard bit
@@ -179,6 +179,100 @@ __device__ __forceinline__ void lane_chain(const uint8_t * __restrict__ row, int
     }
 }
 
+// decode of four NVFP4 codes (one per byte of t4's nibbles) to signed int8 (twice the E2M1 value)
+__device__ __forceinline__ uint32_t nvfp4_codes_to_s8(uint32_t w, int nib_shift) {
+    const uint32_t t4 = (w >> nib_shift) & 0x0f0f0f0fu;          // four codes, one per byte
+    const uint32_t u = t4 | (t4 >> 4);
+    const uint32_t sel = byte_perm(u, 0u, 0x4420u);              // the four codes packed into 16 bits (bytes 0 and 2 of u)
+    const uint32_t pos = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel);
+    const uint32_t neg = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel ^ 0x8888u);
+    // signed bytes: a byte of `neg` is a magnitude 0..12, 0x80 - it never borrows, the xor drops the guard bit
+    return pos | ((0x80808080u - neg) ^ 0x80808080u);
+}
+
+// lane_chain<TYPE_NVFP4> for TWO weight rows against the same activations (the gate row and the up row of a feature): the two
+// chains are independent, so running them in one loop doubles the work in flight per lane - and each activation word and block
+// scale is fetched once for both.  Every chain keeps its own order of operations: the results are those of two lane_chain calls.
+template <int K, int NT, int NTS>
+__device__ __forceinline__ void lane_chain_pair(const uint8_t * __restrict__ row0, const uint8_t * __restrict__ row1, int L,
+                                                const uint8_t * __restrict__ acts, const float * __restrict__ ue_tab, float (&acc0)[NT],
+                                                float (&acc1)[NT]) {
+#pragma unroll
+    for (int t = 0; t < NT; ++t) acc0[t] = acc1[t] = 0.0f;
+    const int sub_in_half = L >> 2, mp = L & 3;
+    const int word_off = 4 + 8 * sub_in_half + 4 * (mp & 1);
+    const int nib_shift = 4 * (mp >> 1);
+#pragma unroll 2
+    for (int b = 0; b < K / 64; ++b) {
+        const uint8_t * blk0 = row0 + b * NVFP4_BLOCK_BYTES, * blk1 = row1 + b * NVFP4_BLOCK_BYTES;
+        const uint32_t dw0 = *reinterpret_cast<const uint32_t *>(blk0), dw1 = *reinterpret_cast<const uint32_t *>(blk1);
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            const uint32_t code0 = nvfp4_codes_to_s8(*reinterpret_cast<const uint32_t *>(blk0 + 16 * hf + word_off), nib_shift);
+            const uint32_t code1 = nvfp4_codes_to_s8(*reinterpret_cast<const uint32_t *>(blk1 + 16 * hf + word_off), nib_shift);
+            const float sw0 = ue_tab[(dw0 >> (8 * (2 * hf + sub_in_half))) & 0xff], sw1 = ue_tab[(dw1 >> (8 * (2 * hf + sub_in_half))) & 0xff];
+            const int unit = 2 * b + hf;
+            uint32_t aw[NT];
+            float dy[NT];
+            load_vec<NT>(aw, reinterpret_cast<const uint32_t *>(acts) + (size_t) (unit * 8 + L) * NTS);
+            load_vec<NT>(dy, reinterpret_cast<const float *>(acts + (size_t) K * NTS) + (size_t) unit * NTS);
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                acc0[t] = __fmaf_rn(__fmul_rn(sw0, dy[t]), small_int_to_float(dot4((int) code0, (int) aw[t], 0)), acc0[t]);
+                acc1[t] = __fmaf_rn(__fmul_rn(sw1, dy[t]), small_int_to_float(dot4((int) code1, (int) aw[t], 0)), acc1[t]);
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        float v = acc0[t], w = acc1[t];
+        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
+        w = __fadd_rn(w, __shfl_xor_sync(0xffffffffu, w, 4));
+        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+        w = __fadd_rn(w, __shfl_xor_sync(0xffffffffu, w, 2));
+        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+        w = __fadd_rn(w, __shfl_xor_sync(0xffffffffu, w, 1));
+        acc0[t] = v;
+        acc1[t] = w;
+    }
+}
+
+// The same pair for ONE activation row whose int8 values (q, K bytes) and block scales (d, K/32 floats) lie in separate arrays,
+// in any address space (the layout lane_chain_split reads).
+template <int K>
+__device__ __forceinline__ void lane_chain_split_pair(const uint8_t * __restrict__ row0, const uint8_t * __restrict__ row1, int L,
+                                                      const uint8_t * __restrict__ q, const float * __restrict__ d,
+                                                      const float * __restrict__ ue_tab, float & out0, float & out1) {
+    const int sub_in_half = L >> 2, mp = L & 3;
+    const int word_off = 4 + 8 * sub_in_half + 4 * (mp & 1);
+    const int nib_shift = 4 * (mp >> 1);
+    float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll 4
+    for (int b = 0; b < K / 64; ++b) {
+        const uint8_t * blk0 = row0 + b * NVFP4_BLOCK_BYTES, * blk1 = row1 + b * NVFP4_BLOCK_BYTES;
+        const uint32_t dw0 = *reinterpret_cast<const uint32_t *>(blk0), dw1 = *reinterpret_cast<const uint32_t *>(blk1);
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            const uint32_t code0 = nvfp4_codes_to_s8(*reinterpret_cast<const uint32_t *>(blk0 + 16 * hf + word_off), nib_shift);
+            const uint32_t code1 = nvfp4_codes_to_s8(*reinterpret_cast<const uint32_t *>(blk1 + 16 * hf + word_off), nib_shift);
+            const float sw0 = ue_tab[(dw0 >> (8 * (2 * hf + sub_in_half))) & 0xff], sw1 = ue_tab[(dw1 >> (8 * (2 * hf + sub_in_half))) & 0xff];
+            const int unit = 2 * b + hf;
+            const uint32_t aw = reinterpret_cast<const uint32_t *>(q)[unit * 8 + L];
+            const float dy = d[unit];
+            a0 = __fmaf_rn(__fmul_rn(sw0, dy), small_int_to_float(dot4((int) code0, (int) aw, 0)), a0);
+            a1 = __fmaf_rn(__fmul_rn(sw1, dy), small_int_to_float(dot4((int) code1, (int) aw, 0)), a1);
+        }
+    }
+    a0 = __fadd_rn(a0, __shfl_xor_sync(0xffffffffu, a0, 4));
+    a1 = __fadd_rn(a1, __shfl_xor_sync(0xffffffffu, a1, 4));
+    a0 = __fadd_rn(a0, __shfl_xor_sync(0xffffffffu, a0, 2));
+    a1 = __fadd_rn(a1, __shfl_xor_sync(0xffffffffu, a1, 2));
+    a0 = __fadd_rn(a0, __shfl_xor_sync(0xffffffffu, a0, 1));
+    a1 = __fadd_rn(a1, __shfl_xor_sync(0xffffffffu, a1, 1));
+    out0 = a0;
+    out1 = a1;
+}
+
 // The NVFP4 chain of lane_chain for ONE activation row whose int8 values (q, K bytes) and block scales (d, K/32 floats)
 // lie in separate arrays, in any address space.  Same operations in the same order as lane_chain<TYPE_NVFP4, K, 1, 1>.
 template <int K>
@@ -197,7 +291,7 @@ __device__ __forceinline__ void lane_chain_split(const uint8_t * __restrict__ ro
             const uint32_t w = *reinterpret_cast<const uint32_t *>(blk + 16 * hf + word_off);
             const uint32_t t4 = (w >> nib_shift) & 0x0f0f0f0fu;
             const uint32_t u = t4 | (t4 >> 4);
-            const uint32_t sel = (u & 0xffff00ffu) | ((u >> 8) & 0x0000ff00u);
+            const uint32_t sel = byte_perm(u, 0u, 0x4420u);
             const uint32_t pos = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel);
             const uint32_t neg = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel ^ 0x8888u);
             const uint32_t code = pos | ((0x80808080u - neg) ^ 0x80808080u);
@@ -222,43 +316,47 @@ __device__ __forceinline__ void lane_chain_split(const uint8_t * __restrict__ ro
 template <int K>
 __device__ __forceinline__ float lane_chain_warp(const uint8_t * __restrict__ row, int lane, const uint8_t * __restrict__ q,
                                                  const float * __restrict__ d, const float * __restrict__ ue_tab) {
-    constexpr int UNITS = K / 32, UPL = UNITS / 4;
-    static_assert(UNITS % 4 == 0, "half-blocks must split over four lane groups");
+    constexpr int UNITS = K / 32, UPL = UNITS / 4;       // half-blocks in the row, and per lane
+    constexpr int BATCH = UPL < 8 ? UPL : 8;             // fetched and decoded at a time (bounds the registers)
+    static_assert(UNITS % 4 == 0 && UPL % BATCH == 0, "half-blocks must split over four lane groups in whole batches");
     const int L = lane & 7, rg = lane >> 3;
     const int sub_in_half = L >> 2, mp = L & 3;
     const int word_off = 4 + 8 * sub_in_half + 4 * (mp & 1);
     const int nib_shift = 4 * (mp >> 1);
-    uint32_t w[UPL], aw[UPL], dw[UPL];
-    float dy[UPL];
-#pragma unroll
-    for (int i = 0; i < UPL; ++i) {
-        const int u = 4 * i + rg, b = u >> 1, hf = u & 1;
-        const uint8_t * blk = row + b * NVFP4_BLOCK_BYTES;
-        dw[i] = *reinterpret_cast<const uint32_t *>(blk);
-        w[i] = *reinterpret_cast<const uint32_t *>(blk + 16 * hf + word_off);
-        aw[i] = reinterpret_cast<const uint32_t *>(q)[u * 8 + L];
-        dy[i] = d[u];
-    }
-    float sd[UPL], pf[UPL];
-#pragma unroll
-    for (int i = 0; i < UPL; ++i) {
-        const int hf = (4 * i + rg) & 1;
-        const uint32_t t4 = (w[i] >> nib_shift) & 0x0f0f0f0fu;
-        const uint32_t u8 = t4 | (t4 >> 4);
-        const uint32_t sel = (u8 & 0xffff00ffu) | ((u8 >> 8) & 0x0000ff00u);
-        const uint32_t pos = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel);
-        const uint32_t neg = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel ^ 0x8888u);
-        const uint32_t code = pos | ((0x80808080u - neg) ^ 0x80808080u);
-        const float sw = ue_tab[(dw[i] >> (8 * (2 * hf + sub_in_half))) & 0xff];
-        sd[i] = __fmul_rn(sw, dy[i]);
-        pf[i] = small_int_to_float(dot4((int) code, (int) aw[i], 0));
-    }
     float a = 0.0f;
+#pragma unroll 1
+    for (int i0 = 0; i0 < UPL; i0 += BATCH) {
+        uint32_t w[BATCH], aw[BATCH], dw[BATCH];
+        float dy[BATCH];
 #pragma unroll
-    for (int u = 0; u < UNITS; ++u) {
-        const int src = (u & 3) * 8 + L;
-        const float s = __shfl_sync(0xffffffffu, sd[u >> 2], src), pv = __shfl_sync(0xffffffffu, pf[u >> 2], src);
-        a = __fmaf_rn(s, pv, a);
+        for (int i = 0; i < BATCH; ++i) {
+            const int u = 4 * (i0 + i) + rg, b = u >> 1, hf = u & 1;
+            const uint8_t * blk = row + b * NVFP4_BLOCK_BYTES;
+            dw[i] = *reinterpret_cast<const uint32_t *>(blk);
+            w[i] = *reinterpret_cast<const uint32_t *>(blk + 16 * hf + word_off);
+            aw[i] = reinterpret_cast<const uint32_t *>(q)[u * 8 + L];
+            dy[i] = d[u];
+        }
+        float sd[BATCH], pf[BATCH];
+#pragma unroll
+        for (int i = 0; i < BATCH; ++i) {
+            const int hf = rg & 1;                       // u = 4 (i0 + i) + rg
+            const uint32_t t4 = (w[i] >> nib_shift) & 0x0f0f0f0fu;
+            const uint32_t u8 = t4 | (t4 >> 4);
+            const uint32_t sel = byte_perm(u8, 0u, 0x4420u);
+            const uint32_t pos = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel);
+            const uint32_t neg = byte_perm(FP4_MAG_LO, FP4_MAG_HI, sel ^ 0x8888u);
+            const uint32_t code = pos | ((0x80808080u - neg) ^ 0x80808080u);
+            const float sw = ue_tab[(dw[i] >> (8 * (2 * hf + sub_in_half))) & 0xff];
+            sd[i] = __fmul_rn(sw, dy[i]);
+            pf[i] = small_int_to_float(dot4((int) code, (int) aw[i], 0));
+        }
+#pragma unroll
+        for (int u = 0; u < 4 * BATCH; ++u) {            // units 4 i0 .. 4 (i0 + BATCH) - 1, in order
+            const int src = (u & 3) * 8 + L;
+            const float sv = __shfl_sync(0xffffffffu, sd[u >> 2], src), pv = __shfl_sync(0xffffffffu, pf[u >> 2], src);
+            a = __fmaf_rn(sv, pv, a);
+        }
     }
     a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 4));
     a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 2));
@@ -454,8 +552,12 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 1 : 4) expert_gemv_kernel(c
                 auto run = [&](auto ntag) {
                     constexpr int NTC = decltype(ntag)::value;
                     float gg[NTC], uu[NTC];
-                    lane_chain<WT, K, NTC, NT>(wrow, L, acts, ue_tab, gg);
-                    if (DUAL) lane_chain<WT, K, NTC, NT>(wrow + C::TENSOR_STAGE_BYTES, L, acts, ue_tab, uu);
+                    if constexpr (DUAL && WT == TYPE_NVFP4) {
+                        lane_chain_pair<K, NTC, NT>(wrow, wrow + C::TENSOR_STAGE_BYTES, L, acts, ue_tab, gg, uu);
+                    } else {
+                        lane_chain<WT, K, NTC, NT>(wrow, L, acts, ue_tab, gg);
+                        if (DUAL) lane_chain<WT, K, NTC, NT>(wrow + C::TENSOR_STAGE_BYTES, L, acts, ue_tab, uu);
+                    }
 #pragma unroll
                     for (int t = 0; t < NTC; ++t) { g[t] = gg[t]; uacc[t] = DUAL ? uu[t] : 0.0f; }
                 };

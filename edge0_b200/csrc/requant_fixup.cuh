@@ -13,10 +13,12 @@
 //      the integer down kernel the whole layer - is the reference's, bit for bit, as long as the GEMM's error stays
 //      inside the margin (a few per cent of the values are recomputed; the margin is ~10x the largest error measured).
 // What has to be exact is the QUANTISED block, not the fp32 values: q = round(h * 127 / amax) and d = half(amax / 127).  The
-// block maximum (one value in 32) therefore needs recomputing only when something hangs on its last bits: when amax / 127 lies
-// within the error of a rounding boundary of fp16 (d in doubt), or when some value of the block sits close to an int8 rounding
-// boundary (a recomputed value that close is only decided once amax is exact too).  Blocks with neither keep the GEMM's maximum.
-// With the FP4 engine's margin about 1.3 % of the values are listed, with the f16 engine's about 6 %.
+// block maximum (one value in 32) therefore needs recomputing only when something hangs on its last bits:
+//   * amax / 127 lies within the error of a rounding boundary of fp16 (d in doubt): the mark kernel lists the candidates;
+//   * a RECOMPUTED value still sits so close to an int8 rounding boundary that the maximum's own error decides it (a fifth of
+//     the recomputed values - they were listed for being close): the fix kernel notices that itself and puts the block's
+//     candidates on a second list, which a second pass of the same kernel recomputes.
+// Blocks with neither keep the GEMM's maximum.  With the FP4 engine's margin under 1 % of the values are listed.
 // The list holds a quarter of all values; when more are marked (degenerate inputs such as blocks of equal values), the surplus
 // stays as the GEMM produced it and the overflow is counted (FixList::overflow, reported through b200moe_get_counters).
 #pragma once
@@ -72,11 +74,9 @@ __global__ void __launch_bounds__(256) requant_mark_kernel(const float * __restr
             risky[j] = dist < step_margin + t * rel_margin;
         }
     }
-    // the maximum's candidates: when the block scale half(amax / 127) is in doubt (near an fp16 rounding boundary), or when a value of
-    // the block is recomputed (its rounding is only decided against the exact maximum)
-    const uint32_t any = __ballot_sync(0xffffffffu, risky[0] || risky[1] || risky[2] || risky[3]);
-    const bool block_any = ((any >> (lane & 24)) & 0xffu) != 0;
-    const bool need_max = block_any || (amax > 0.0f && near_half_rounding_boundary(amax / 127.0f, 2.0f * rel_margin));
+    // the maximum's candidates: when the block scale half(amax / 127) is in doubt (near an fp16 rounding boundary).  (A recomputed
+    // value whose rounding hangs on the maximum's last bits is dealt with by the fix kernel.)
+    const bool need_max = amax > 0.0f && near_half_rounding_boundary(amax / 127.0f, 2.0f * rel_margin);
     int n_mine = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -119,39 +119,94 @@ struct FixParams {
     int n_as;
     float * hid;               // [rows][n_ff], patched in place
     FixList list;
+    FixList more;              // candidates for block maxima found while fixing (items null: this is the second pass, find none)
     int * err;
+    float rel_margin;          // the mark kernel's: relative uncertainty of a block maximum the GEMM left
 };
 
-// One warp per listed value (lane_chain_warp): the reference's 8 SIMD lanes run the fp32 chain, all 32 lanes fetch and decode, so
-// every load of a value is in flight at once and the kernel's time is a few memory round trips, not one per group of blocks.
-// The patched value is the reference's, bit for bit; weight rows and activations are read straight from global memory (the
-// activations and most weight rows are L2-resident right after the GEMM) - the listed values are scattered, there is nothing to
-// stream.
+// 8 lanes per listed value (the reference's 8 SIMD lanes), 4 values per warp at a time.  Each group runs the same chains as
+// the integer GEMV, so the patched value is the reference's, bit for bit.  The listed values are scattered - nothing streams - so
+// every warp fetches the two weight rows of its four values with bulk copies into its own piece of shared memory (whole rows in
+// one request each instead of a few words per dependent load) and waits once; the activations are L2-resident and read directly.
+// Latency is hidden by the other warps of the SM.
+template <int K>
+constexpr size_t requant_fix_smem_bytes() { return (size_t) 8 * 4 * 2 * (K / 64 * NVFP4_BLOCK_BYTES); }
+
 template <int K>
 __global__ void __launch_bounds__(256) requant_fix_kernel(const FixParams p) {
     constexpr int ROW_BYTES = K / 64 * NVFP4_BLOCK_BYTES;
+    static_assert(ROW_BYTES % 16 == 0, "bulk copies move multiples of 16 bytes");
+    extern __shared__ __align__(128) uint8_t fix_rows[];   // [8 warps][4 values][gate row, up row]
     __shared__ float ue_tab[256];
+    __shared__ uint64_t bars[8];
     pdl_wait();
     pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int L = lane & 7, rgrp = lane >> 3;
     ue_tab[tid] = ue4m3_half_to_f32(tid);
+    if (tid < 8) mbar_init(&bars[tid], 1);
+    mbar_fence_init();
     __syncthreads();
+    uint8_t * const rows_smem = fix_rows + (size_t) (warp * 4 + rgrp) * 2 * ROW_BYTES;
     const int n = min(*p.list.count, p.list.capacity);
-    for (int i = blockIdx.x * 8 + warp; i < n; i += gridDim.x * 8) {
-        const int2 it = p.list.items[i];
+    const int groups_per_grid = gridDim.x * 32;
+    uint32_t parity = 0;
+    // warp-uniform trip count: every lane runs the chains (their shuffles use the full mask); idle groups redo item 0
+    for (int base = (blockIdx.x * 8 + warp) * 4; base < n; base += groups_per_grid) {
+        const int i = base + rgrp;
+        const bool valid = i < n;
+        const int2 it = p.list.items[valid ? i : 0];
         const int r = it.x, f = it.y;
         int e = p.ids[r];
         if (e < 0 || e >= p.n_as) { report_error(p.err, DEV_ERR_BAD_EXPERT_ID); e = 0; }
         const int tok = r / p.n_ids;
-        const uint8_t * q = reinterpret_cast<const uint8_t *>(p.act.q + (size_t) tok * K);
-        const float * d = p.act.d + (size_t) tok * (K / 32);
-        const float g = lane_chain_warp<K>(p.w0 + ((size_t) e * p.n_ff + f) * ROW_BYTES, lane, q, d, ue_tab);
-        const float u = lane_chain_warp<K>(p.w1 + ((size_t) e * p.n_ff + f) * ROW_BYTES, lane, q, d, ue_tab);
-        if (lane == 0) {
-            const float sc0 = p.scale0 ? p.scale0[e] : 1.0f, sc1 = p.scale1 ? p.scale1[e] : 1.0f;
-            const float v = __fmul_rn(g, sc0);
-            p.hid[(size_t) r * p.n_ff + f] = __fmul_rn(ggml_silu(v), __fmul_rn(u, sc1));
+        if (lane == 0) mbar_arrive_expect_tx(&bars[warp], 4 * 2 * ROW_BYTES);
+        if (L == 0) {
+            bulk_g2s(rows_smem, p.w0 + ((size_t) e * p.n_ff + f) * ROW_BYTES, ROW_BYTES, &bars[warp]);
+            bulk_g2s(rows_smem + ROW_BYTES, p.w1 + ((size_t) e * p.n_ff + f) * ROW_BYTES, ROW_BYTES, &bars[warp]);
         }
+        const bool landed = mbar_wait_bounded(&bars[warp], parity);
+        if (!__all_sync(0xffffffffu, landed)) {                     // warp-uniform: the chains below shuffle with the full mask
+            report_error(p.err, DEV_ERR_BARRIER_TIMEOUT);
+            mbar_wait_bounded(&bars[warp], parity, 200000000ull);   // bounded drain before the shared memory goes away
+            break;
+        }
+        parity ^= 1u;
+        const uint8_t * g_row = rows_smem;
+        const uint8_t * u_row = rows_smem + ROW_BYTES;
+        float g[1], u[1];
+        lane_chain_split_pair<K>(g_row, u_row, L, reinterpret_cast<const uint8_t *>(p.act.q + (size_t) tok * K), p.act.d + (size_t) tok * (K / 32), ue_tab,
+                                 g[0], u[0]);
+        const float sc0 = p.scale0 ? p.scale0[e] : 1.0f, sc1 = p.scale1 ? p.scale1[e] : 1.0f;
+        const float hv = __fmul_rn(ggml_silu(__fmul_rn(g[0], sc0)), __fmul_rn(u[0], sc1));   // the same in all 8 lanes of the group
+        float * hrow = p.hid + (size_t) r * p.n_ff;
+        if (valid && L == 0) hrow[f] = hv;
+        // Is the rounding of the exact value decided whatever the last bits of the block maximum are?  The group's 8 lanes read
+        // the block (4 values each; values another group patches meanwhile are within the margin either way).  If not, the
+        // candidates for the maximum go on the second list.
+        if (p.more.items) {
+            const int fb = f & ~31;
+            const float4 nb = *reinterpret_cast<const float4 *>(hrow + fb + 4 * L);
+            const float av[4] = { fabsf(nb.x), fabsf(nb.y), fabsf(nb.z), fabsf(nb.w) };
+            float am = fmaxf(fmaxf(av[0], av[1]), fmaxf(av[2], av[3]));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 4));
+            am = fmaxf(am, fabsf(hv));
+            if (valid && am > 0.0f) {
+                const float t = fabsf(hv) * (127.0f / am);
+                if (fabsf((t - floorf(t)) - 0.5f) < t * p.rel_margin + 2e-5f) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (av[j] >= am * (1.0f - p.rel_margin) && fb + 4 * L + j != f) {
+                            const int slot = atomicAdd(p.more.count, 1);
+                            if (slot < p.more.capacity) p.more.items[slot] = make_int2(r, fb + 4 * L + j);
+                            else if (p.more.overflow) atomicAdd(p.more.overflow, 1ull);
+                        }
+                }
+            }
+        }
+        __syncwarp();   // all lanes are done with the staged rows before the next round's copies land on them
     }
 }
 
@@ -164,8 +219,11 @@ struct FixSingleParams {
     int n_out;
     float * y;                 // [tokens][n_out], patched in place
     FixList list;
+    float rel_margin;          // as in FixParams
 };
 
+// One warp per listed value here (lane_chain_warp): the list of a dense product is short and its rows long (K up to 4096), so the
+// kernel's time is one value's latency; with every load of the row in flight at once that is a few memory round trips.
 template <int K>
 __global__ void __launch_bounds__(256) requant_fix_single_kernel(const FixSingleParams p) {
     constexpr int ROW_BYTES = K / 64 * NVFP4_BLOCK_BYTES;
@@ -177,9 +235,32 @@ __global__ void __launch_bounds__(256) requant_fix_single_kernel(const FixSingle
     for (int i = blockIdx.x * 8 + warp; i < n; i += gridDim.x * 8) {
         const int2 it = p.list.items[i];
         const int tok = it.x, f = it.y;
-        const float g = lane_chain_warp<K>(p.w + (size_t) f * ROW_BYTES, lane, reinterpret_cast<const uint8_t *>(p.act.q + (size_t) tok * K),
-                                           p.act.d + (size_t) tok * (K / 32), ue_tab);
-        if (lane == 0) p.y[(size_t) tok * p.n_out + f] = p.scale ? __fmul_rn(g, p.scale[0]) : g;
+        const uint8_t * q = reinterpret_cast<const uint8_t *>(p.act.q + (size_t) tok * K);
+        const float * d = p.act.d + (size_t) tok * (K / 32);
+        const float g = lane_chain_warp<K>(p.w + (size_t) f * ROW_BYTES, lane, q, d, ue_tab);
+        const float yv = p.scale ? __fmul_rn(g, p.scale[0]) : g;
+        float * yrow = p.y + (size_t) tok * p.n_out;
+        if (lane == 0) yrow[f] = yv;
+        // the block of 32 this value is quantised with: is its rounding decided whatever the last bits of the block maximum are?
+        const int fb = f & ~31;
+        const float mine = yrow[fb + lane];
+        float am = fabsf(mine);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+        am = fmaxf(am, fabsf(yv));
+        if (am > 0.0f) {
+            const float t = fabsf(yv) * (127.0f / am);
+            if (fabsf((t - floorf(t)) - 0.5f) < t * p.rel_margin + 2e-5f) {
+                // rare: recompute every candidate for the block maximum (warp-uniform: all lanes hold the same yv and am)
+                uint32_t cands = __ballot_sync(0xffffffffu, fabsf(mine) >= am * (1.0f - p.rel_margin) && fb + lane != f);
+                while (cands) {
+                    const int c = __ffs(cands) - 1;
+                    cands &= cands - 1;
+                    const float gc = lane_chain_warp<K>(p.w + (size_t) (fb + c) * ROW_BYTES, lane, q, d, ue_tab);
+                    if (lane == 0) yrow[fb + c] = p.scale ? __fmul_rn(gc, p.scale[0]) : gc;
+                }
+            }
+        }
     }
 }
 

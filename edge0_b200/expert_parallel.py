@@ -109,8 +109,11 @@ class ExpertParallelLayer:
             raise ValueError(f"{T} tokens x top-{k} exceed the slot capacity {cap} this layer was built for")
         mark = self._mark
         mark("start")
-        ids, w = b.route(x_local)                                    # [T,k]
-        xl = b.project_down(x_local)                                 # [T,L] float32
+        if hasattr(b, "route_and_project"):                          # independent of each other: the backend may run them side by side
+            ids, w, xl = b.route_and_project(x_local)
+        else:
+            ids, w = b.route(x_local)                                # [T,k]
+            xl = b.project_down(x_local)                             # [T,L] float32
         mark("route+D")
         slots, slot_of = b.pack(xl, ids, N, self.E // N, cap)         # [N, cap, slot]
         recv = self._exchange(slots)
@@ -189,6 +192,12 @@ class CudaBackend:
                                   up_scale=sl(host_layer.up_scale), down_scale=sl(host_layer.down_scale))
         self.dev = dev
         self._buf = {}
+        # The router and the latent down-projection read the same tokens and nothing of each other: the router gets a context
+        # (scratch memory) and a stream of its own, so the two run side by side (both are small grids that leave SMs idle).
+        self.ctx_router = moe.Context(ctx.device)
+        self.router = moe.MoeLayer(self.ctx_router, wtype=cfg.wtype, top_k=cfg.top_k, router_w=host_layer.router_w, router_bias=host_layer.router_bias,
+                                   gate=host_layer.gate[:1], up=host_layer.up[:1], down=host_layer.down[:1], check_shapes=False)
+        self._side = torch.cuda.Stream(device=dev)
 
     def _get(self, name, shape, dtype, zero=False):
         t = self._buf.get(name)
@@ -202,6 +211,20 @@ class CudaBackend:
 
     def project_down(self, x):
         return self.route_layer.latent_down(x)
+
+    def route_and_project(self, x):
+        """(ids, weights, latent rows): routing on the side stream while the down-projection runs on the caller's."""
+        T = x.shape[0]
+        ids = self._get("ids", (T, self.cfg.top_k), torch.int32)
+        w = self._get("w", (T, self.cfg.top_k), torch.float32)
+        xl = self._get("xl", (T, self.cfg.n_latent), torch.float32)
+        cur = torch.cuda.current_stream(self.dev)
+        self._side.wait_stream(cur)
+        with torch.cuda.stream(self._side):
+            self.router.route(x, out=(ids, w))
+        self.route_layer.latent_down(x, out=xl)
+        cur.wait_stream(self._side)
+        return ids, w, xl
 
     def project_up(self, m):
         return self.route_layer.latent_up(m)

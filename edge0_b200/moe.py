@@ -244,11 +244,14 @@ class MoeLayer:
             s.ffn_shexp_gated = o.shexp_gated.data_ptr()
         return s, o
 
-    def route(self, x: torch.Tensor):
-        """x [T, n_embd] -> (ids int32 [T, k], weights float32 [T, k])."""
+    def route(self, x: torch.Tensor, out=None):
+        """x [T, n_embd] -> (ids int32 [T, k], weights float32 [T, k]); out: that pair, allocated by the caller."""
         T = x.shape[0]
-        ids = torch.empty((T, self.top_k), dtype=torch.int32, device=x.device)
-        w = torch.empty((T, self.top_k), dtype=torch.float32, device=x.device)
+        if out is not None:
+            ids, w = out
+        else:
+            ids = torch.empty((T, self.top_k), dtype=torch.int32, device=x.device)
+            w = torch.empty((T, self.top_k), dtype=torch.float32, device=x.device)
         c = self.ctx
         c.check(c.lib.b200moe_route(c.handle, C.byref(self.desc), _ptr(x), _x_type(x), T, _ptr(ids), _ptr(w), None, c._stream()))
         return ids, w
@@ -262,10 +265,10 @@ class MoeLayer:
                                   _ptr(out), None, c._stream()))
         return out
 
-    def latent_down(self, x: torch.Tensor) -> torch.Tensor:
+    def latent_down(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x [T, n_embd] -> latent rows float32 [T, n_latent] (edge0-strata latent_moe.cpp: xl = D x)."""
         T = x.shape[0]
-        xl = torch.empty((T, self.n_latent), dtype=torch.float32, device=x.device)
+        xl = out if out is not None else torch.empty((T, self.n_latent), dtype=torch.float32, device=x.device)
         c = self.ctx
         c.check(c.lib.b200moe_latent_down(c.handle, C.byref(self.desc), _ptr(x), _x_type(x), T, _ptr(xl), c._stream()))
         return xl
