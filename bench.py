@@ -91,17 +91,21 @@ def physical_cores() -> int:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (reads only)."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (reads only).  One sampler per job
+    (rank 0, its own GPU): eight nvidia-smi pollers on one box were measured to slow every rank's kernel launches threefold
+    (the queries serialise in the driver), so the other ranks start none."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index: int, enabled: bool = True):
+        self.index, self.rows, self.proc, self.enabled = index, [], None, enabled
 
     def start(self):
+        if not self.enabled:
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "25"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -111,6 +115,8 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self) -> dict:
+        if not self.enabled:
+            return {}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -389,7 +395,7 @@ def run_c5_arm(args):
         outs[i % n_sets] = eps[i % n_sets].forward(xs[i % n_sets])
 
     step, how = make_graph_stepper(eager, n_sets, ctx, not args.no_graph)
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(local, enabled=(rank == 0))
     for i in range(args.warmup):
         step(i)
     ctx.synchronize()
@@ -555,7 +561,7 @@ def run_c2_arm(args):
 
     eager = lambda i: layers[i % n_sets].forward(xs[i % n_sets], out=out)
     step, how = make_graph_stepper(eager, n_sets, ctx, not args.no_graph)
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(local, enabled=(rank == 0))
     for i in range(args.warmup):
         step(i)
     barrier()

@@ -181,7 +181,8 @@ bool gemv_supported(int wtype, int64_t k) {
 // +7 % end to end through the host entry point, nothing under CUDA-graph replay (and slower at 8 tokens), which is why it is
 // off by default.  With prefill-sized grids it gains nothing, and the gate/up grouped GEMM with 128-token tiles was measured
 // to return wrong values when a large dependent grid was resident beside it (cause not found by reading; serial launches are
-// correct), so large calls always launch serially.
+// correct), so large calls always launch serially, and the tensor-core kernels are never launched with the attribute nor
+// release their dependents early: nothing becomes resident beside a kernel that holds tensor memory.
 void layer_overlap(b200moe_ctx * ctx, int64_t rows, int n_expert) { ctx->overlap_now = rows < (int64_t) 24 * n_expert; }
 
 // Launch with programmatic stream serialisation: the kernel may start while its predecessor in the stream is still running;
@@ -428,7 +429,7 @@ int launch_gemm_t(b200moe_ctx * ctx, const MmaParams & p, int rows, cudaStream_t
         tm.kind = DUAL ? 0 : ctx->dense_now ? 2 : 1;
         CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
     }
-    launch_k(ctx, kern, dim3(ctx->sm_count), dim3(GEMM_THREADS), C::SMEM, st, p, mw0, mw1, mhi, mlo);
+    kern<<<dim3(ctx->sm_count), dim3(GEMM_THREADS), C::SMEM, st>>>(p, mw0, mw1, mhi, mlo);   // never as a programmatic dependent (layer_overlap)
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventRecord(tm.end, st));
         ctx->timed.push_back(tm);
@@ -461,7 +462,7 @@ int launch_gemm_tm_t(b200moe_ctx * ctx, const MmaParams & p, int rows, cudaStrea
         tm.kind = DUAL ? 0 : ctx->dense_now ? 2 : 1;
         CUDA_TRY(ctx, cudaEventRecord(tm.beg, st));
     }
-    launch_k(ctx, kern, dim3(ctx->sm_count), dim3(GEMM_TM_THREADS), C::SMEM, st, p, mw0, mw1, mact);
+    kern<<<dim3(ctx->sm_count), dim3(GEMM_TM_THREADS), C::SMEM, st>>>(p, mw0, mw1, mact);   // never as a programmatic dependent (layer_overlap)
     if (ctx->timing) {
         CUDA_TRY(ctx, cudaEventRecord(tm.end, st));
         ctx->timed.push_back(tm);

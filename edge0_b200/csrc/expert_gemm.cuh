@@ -160,8 +160,9 @@ expert_gemm_nvfp4_kernel(const MmaParams p, const __grid_constant__ CUtensorMap 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
-    pdl_wait();                 // programmatic dependent launch: everything before this ran alongside the previous kernel's tail
-    pdl_launch_dependents();
+    pdl_wait();                 // a no-op unless the launch carried the programmatic attribute (the library never gives it to this kernel)
+    // No early griddepcontrol.launch_dependents here: a dependent grid must not become resident beside a kernel that holds tensor
+    // memory (wrong values were measured in that situation; dependents of this kernel start when it has finished).
 
     const int n_active = p.meta[0];
     const int m_tiles = p.n_out / 128;
