@@ -524,10 +524,11 @@ int launch_gemm_fp4_t(b200moe_ctx * ctx, const Fp4Params & fp, const void * w0, 
         std::vector<long long> h(24 * 256);
         cudaStreamSynchronize(st);
         cudaMemcpy(h.data(), d_prof, sizeof(long long) * 24 * 256, cudaMemcpyDeviceToHost);
-        const char * names[13] = {"raw: wait raw_empty", "raw: total", "act: wait act_empty", "act: total", "mma: wait acc_empty", "mma: wait act_full", "mma: wait tile_full", "mma: total",
-                                  "epi: wait acc_full", "epi: total", "repack: wait raw_full", "repack: wait tile_empty", "repack: total"};
+        const char * names[16] = {"raw: wait raw_empty", "raw: total", "act: wait act_empty", "act: total", "mma: wait acc_empty", "mma: wait act_full", "mma: wait tile+sf_full", "mma: total",
+                                  "epi: wait acc_full", "epi: total", "repack: wait raw_full", "repack: wait tile_empty", "repack: total",
+                                  "sfcopy: wait act_full", "sfcopy: wait tile_full", "sfcopy: total"};
         printf("fp4 kernel K=%d DUAL=%d role cycles (mean over CTAs / max):\n", K, (int) DUAL);
-        for (int k = 0; k < 13; ++k) {
+        for (int k = 0; k < 16; ++k) {
             double sum = 0; long long mx = 0;
             for (int b = 0; b < ctx->sm_count; ++b) { sum += h[b * 24 + k]; mx = std::max(mx, h[b * 24 + k]); }
             printf("  %-26s %10.0f %10lld\n", names[k], sum / ctx->sm_count, mx);

@@ -307,14 +307,14 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
     uint8_t * tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
     uint8_t * acts = tiles + (size_t) TS * C::STAGE;
     uint8_t * raws = acts + (size_t) AS * C::ACT_STAGE;
-    __shared__ uint64_t raw_full[RS], raw_empty[RS], tile_full[TS], tile_empty[TS], act_full[AS], act_empty[AS], acc_full[2], acc_empty[2];
+    __shared__ uint64_t raw_full[RS], raw_empty[RS], tile_full[TS], tile_empty[TS], act_full[AS], act_empty[AS], acc_full[2], acc_empty[2], sf_full[TS];
     __shared__ uint32_t s_tmem;
     __shared__ volatile int s_abort;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 8); }
-        for (int i = 0; i < TS; ++i) { mbar_init(&tile_full[i], 256); mbar_init(&tile_empty[i], 1); }
+        for (int i = 0; i < TS; ++i) { mbar_init(&tile_full[i], 256); mbar_init(&tile_empty[i], 1); mbar_init(&sf_full[i], 1); }
         for (int i = 0; i < AS; ++i) { mbar_init(&act_full[i], 1); mbar_init(&act_empty[i], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
         mbar_fence_init();
@@ -427,18 +427,18 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
                         const uint32_t sbase = smem_u32(tiles + (size_t) tile.stage * C::STAGE);
                         const uint32_t abase = smem_u32(acts + (size_t) act.stage * C::ACT_STAGE);
                         const uint32_t da = DESC_LO | (sbase >> 4), db = DESC_LO | (abase >> 4);
-                        // Scale factors go to the set of tensor-memory columns that belongs to this operand stage.  The set was last
-                        // read by the MMAs of the stage two back, and those have completed: their commit released the operand stage,
-                        // the repack threads waited for that before refilling it, and only then could tile_full be seen above.  (Two
-                        // accumulators are in flight, and a scale copy is not ordered behind an earlier MMA on another accumulator:
-                        // with one set of columns a copy was measured to overtake MMAs of the previous stage.)
+                        // The scale factors of this stage were copied into their set of tensor-memory columns by the scale-copy thread
+                        // (warp 3); its commit on sf_full says the copies are complete.
+                        {
+                            FP4_PROF_T0();
+                            if (!wait_or_abort<20>(&sf_full[tile.stage], tile.phase, &s_abort, p.err)) break;
+                            FP4_PROF_ADD(2);
+                        }
+                        tc_fence_after();
                         const uint32_t sf_set = tmem + C::SF_COL + 48 * (uint32_t) tile.stage;
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {   // 4 x K64 = 256; 32 bytes (2 units) further along the 128-byte row each
                             const uint32_t t_sfa0 = sf_set + 12 * kk, t_sfa1 = t_sfa0 + 4, t_sfb = t_sfa0 + 8;
-                            tmem_cp_sf(t_sfa0, sbase + OFF_SFA + kk * 512);
-                            tmem_cp_sf(t_sfa1, sbase + OFF_SFA + FP4_SF_TILE + kk * 512);
-                            tmem_cp_sf(t_sfb, abase + OFF_SFB + kk * 512);
                             const bool accum = kc != 0 || kk != 0;
                             umma_fp4(d0, da + 2 * kk, db + 2 * kk, DESC_HI, idesc, t_sfa0, t_sfb, accum);
                             umma_fp4(d1, da + (OFF_A1 >> 4) + 2 * kk, db + 2 * kk, DESC_HI, idesc, t_sfa1, t_sfb, accum);
@@ -453,6 +453,48 @@ expert_gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap ma
                 }
             }
             FP4_PROF_STORE(4, 3);
+        }
+    } else if (warp == 3) {
+        // ---------------------------------------------------------------- scale-factor copies (shared memory -> tensor memory)
+        // A thread of its own (splitting the copies over two threads was tried: no faster, and one parity case failed): a tcgen05.cp holds its issuing thread for ~80 cycles, and twelve of them per stage in front of the
+        // MMAs were more than half of the MMA thread's time.  The set of columns that belongs to an operand stage was last read by
+        // the MMAs of the stage two back, and those have completed: their commit released the operand stage, the repack threads
+        // waited for that before refilling it, and only then can tile_full be seen here.  (A scale copy is not ordered behind an
+        // earlier MMA on another accumulator: with one set of columns a copy was measured to overtake MMAs of the previous stage.)
+        if (lane == 0) {
+            Ring tile, act;
+            FP4_PROF_DECL();
+            for (int u = blockIdx.x; u < n_units && !s_abort; u += gridDim.x) {
+                bool ok = true;
+                for (int kc = 0; kc < KC; ++kc) {
+                    {
+                        FP4_PROF_T0();
+                        if (!wait_or_abort<20>(&act_full[act.stage], act.phase, &s_abort, p.err)) { ok = false; break; }
+                        FP4_PROF_ADD(0);
+                    }
+                    {
+                        FP4_PROF_T0();
+                        if (!wait_or_abort<20>(&tile_full[tile.stage], tile.phase, &s_abort, p.err)) { ok = false; break; }
+                        FP4_PROF_ADD(1);
+                    }
+                    tc_fence_after();
+                    const uint32_t sbase = smem_u32(tiles + (size_t) tile.stage * C::STAGE);
+                    const uint32_t abase = smem_u32(acts + (size_t) act.stage * C::ACT_STAGE);
+                    const uint32_t sf_set = tmem + C::SF_COL + 48 * (uint32_t) tile.stage;
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint32_t t_sfa0 = sf_set + 12 * kk;
+                        tmem_cp_sf(t_sfa0, sbase + OFF_SFA + kk * 512);
+                        tmem_cp_sf(t_sfa0 + 4, sbase + OFF_SFA + FP4_SF_TILE + kk * 512);
+                        tmem_cp_sf(t_sfa0 + 8, abase + OFF_SFB + kk * 512);
+                    }
+                    umma_commit(&sf_full[tile.stage]);
+                    tile.template advance<TS>();
+                    act.template advance<AS>();
+                }
+                if (!ok) break;
+            }
+            FP4_PROF_STORE(13, 2);
         }
     } else if (warp >= 4 && warp < 8) {
         // ---------------------------------------------------------------- epilogue
