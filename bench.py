@@ -90,6 +90,10 @@ def physical_cores() -> int:
     return os.cpu_count() or 1
 
 
+# DRAM bytes per algorithmic byte of the gate/up expert kernel, from the ncu capture summarised in profiles/ (627.26 MB / 598.08 MB)
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0488
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (reads only).  One sampler per job
     (rank 0, its own GPU): eight nvidia-smi pollers on one box were measured to slow every rank's kernel launches threefold
@@ -502,8 +506,10 @@ def run_c5_arm(args):
                 "gpu_launches": launches, "clocks": clocks,
                 "roofline": {"bound": "hbm", "kernel": "expert_gemm_fp4_kernel<1024, DUAL> (gate+up+SwiGLU of this rank's experts, tcgen05 kind::mxf4nvf4)",
                              "achieved": gu_b / (gu_us * 1e-6) / 1e9 if gu_us else 0.0, "peak": peak, "unit": "GB/s",
-                             "frac": gu_b / (gu_us * 1e-6) / 1e9 / peak if gu_us else 0.0, "traffic": None,
-                             "traffic_source": "see profiles/ for the ncu capture of this kernel", "peak_source": peak_kind,
+                             "frac": gu_b / (gu_us * 1e-6) / 1e9 / peak if gu_us else 0.0, "traffic": gu_b * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE,
+                             "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of this kernel in the ncu capture of the one-GPU step "
+                                               "(profiles/expert_gemm_fp4_c5_latent_T256.md: 627.26 MB for 598.08 MB algorithmic), scaled by the "
+                                               "experts this rank holds", "peak_source": peak_kind,
                              "algorithmic_bytes_per_launch": gu_b, "avg_launch_us": gu_us, "experts_touched_on_rank0": U_local,
                              "down_kernel": {"achieved": dn_b / (dn_us * 1e-6) / 1e9 if dn_us else 0.0, "avg_launch_us": dn_us,
                                              "algorithmic_bytes_per_launch": dn_b, "frac": dn_b / (dn_us * 1e-6) / 1e9 / peak if dn_us else 0.0},
