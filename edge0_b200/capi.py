@@ -57,6 +57,9 @@ SIGNATURES = {
     "b200moe_mul_mat_id_width_ok": (C.c_int, [C.c_int, C.c_int64]),
     "b200moe_quantize_nvfp4_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]),
     "b200moe_dequantize_host": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]),
+    "b200moe_expert_blob_bytes_nvfp4": (C.c_int64, [C.c_int32, C.c_int32]),
+    "b200moe_unpack_expert_blobs_nvfp4": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                    C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "b200moe_route": (C.c_int, [C.c_void_p, C.POINTER(Layer), C.c_void_p, C.c_int, C.c_int32, C.c_void_p, C.c_void_p,
                                 C.POINTER(Observe), C.c_void_p]),
     "b200moe_mul_mat_id": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int64,

@@ -1348,6 +1348,50 @@ int b200moe_quantize_nvfp4_host(const float * src, void * dst, int64_t nrows, in
     return B200MOE_OK;
 }
 
+int64_t b200moe_expert_blob_bytes_nvfp4(int32_t n_embd, int32_t n_ff) {
+    if (n_embd <= 0 || n_ff <= 0 || n_embd % 64 || n_ff % 64) return -1;
+    const int64_t gu_row = (int64_t) n_embd / 64 * NVFP4_BLOCK_BYTES, d_row = (int64_t) n_ff / 64 * NVFP4_BLOCK_BYTES;
+    return 2 * n_ff * gu_row + n_embd * d_row + 16;
+}
+
+int b200moe_unpack_expert_blobs_nvfp4(const void * blobs, int64_t blob_stride, int32_t n_expert, int32_t n_embd, int32_t n_ff, void * gate, void * up,
+                                      void * down, float * gate_scale, float * up_scale, float * down_scale, int to_device, void * stream) {
+    const int64_t bytes = b200moe_expert_blob_bytes_nvfp4(n_embd, n_ff);
+    if (bytes < 0 || n_expert <= 0 || !blobs || !gate || !up || !down || !gate_scale || !up_scale || !down_scale || blob_stride < bytes)
+        return B200MOE_ERR_INVALID_ARG;
+    const size_t gu = (size_t) n_ff * ((size_t) n_embd / 64 * NVFP4_BLOCK_BYTES), dn = (size_t) n_embd * ((size_t) n_ff / 64 * NVFP4_BLOCK_BYTES);
+    std::vector<float> sg(n_expert), su(n_expert), sd(n_expert);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    for (int e = 0; e < n_expert; ++e) {
+        const uint8_t * b = static_cast<const uint8_t *>(blobs) + (size_t) e * blob_stride;
+        float tail[4];
+        memcpy(tail, b + 2 * gu + dn, sizeof tail);
+        sg[e] = tail[0]; su[e] = tail[1]; sd[e] = tail[2];
+        uint8_t * dg = static_cast<uint8_t *>(gate) + (size_t) e * gu, * du = static_cast<uint8_t *>(up) + (size_t) e * gu,
+                * dd = static_cast<uint8_t *>(down) + (size_t) e * dn;
+        if (!to_device) {
+            memcpy(dg, b, gu); memcpy(du, b + gu, gu); memcpy(dd, b + 2 * gu, dn);
+        } else if (cudaMemcpyAsync(dg, b, gu, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+                   cudaMemcpyAsync(du, b + gu, gu, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+                   cudaMemcpyAsync(dd, b + 2 * gu, dn, cudaMemcpyHostToDevice, st) != cudaSuccess) {
+            cudaGetLastError();
+            return B200MOE_ERR_CUDA;
+        }
+    }
+    const size_t sb = sizeof(float) * (size_t) n_expert;
+    if (!to_device) {
+        memcpy(gate_scale, sg.data(), sb); memcpy(up_scale, su.data(), sb); memcpy(down_scale, sd.data(), sb);
+        return B200MOE_OK;
+    }
+    if (cudaMemcpyAsync(gate_scale, sg.data(), sb, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+        cudaMemcpyAsync(up_scale, su.data(), sb, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+        cudaMemcpyAsync(down_scale, sd.data(), sb, cudaMemcpyHostToDevice, st) != cudaSuccess || cudaStreamSynchronize(st) != cudaSuccess) {
+        cudaGetLastError();
+        return B200MOE_ERR_CUDA;
+    }
+    return B200MOE_OK;
+}
+
 int b200moe_dequantize_host(int type, const void * src, float * dst, int64_t nrows, int64_t n_per_row) {
     if (!src || !dst || nrows < 0 || n_per_row <= 0) return B200MOE_ERR_INVALID_ARG;
     const uint8_t * s = static_cast<const uint8_t *>(src);

@@ -61,6 +61,35 @@ def _x_type(x: torch.Tensor) -> int:
     raise TypeError("activations must be float32 or bfloat16")
 
 
+def unpack_expert_blobs_nvfp4(blobs: np.ndarray, n_embd: int, n_ff: int, device=None):
+    """edge0-strata expert blobs (uint8 [n_expert][>= blob bytes]) -> (gate, up, down, gate_scale, up_scale, down_scale) in the layout of
+    b200moe_layer: numpy arrays, or torch tensors on `device` when one is given (copied straight from the blobs, no repacking)."""
+    lib = capi.load()
+    blobs = np.ascontiguousarray(blobs, dtype=np.uint8)
+    E, stride = blobs.shape
+    need = lib.b200moe_expert_blob_bytes_nvfp4(n_embd, n_ff)
+    if need < 0 or stride < need:
+        raise ValueError(f"blobs of {stride} bytes cannot hold experts of {n_embd} x {n_ff} ({need} bytes)")
+    gu_row, d_row = n_embd // 64 * 36, n_ff // 64 * 36
+    if device is None:
+        g, u = np.empty((E, n_ff, gu_row), np.uint8), np.empty((E, n_ff, gu_row), np.uint8)
+        d = np.empty((E, n_embd, d_row), np.uint8)
+        sc = [np.empty(E, np.float32) for _ in range(3)]
+        ptr = lambda a: a.ctypes.data
+        stream = None
+    else:
+        g, u = (torch.empty((E, n_ff, gu_row), dtype=torch.uint8, device=device) for _ in range(2))
+        d = torch.empty((E, n_embd, d_row), dtype=torch.uint8, device=device)
+        sc = [torch.empty(E, dtype=torch.float32, device=device) for _ in range(3)]
+        ptr = lambda a: a.data_ptr()
+        stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    rc = lib.b200moe_unpack_expert_blobs_nvfp4(blobs.ctypes.data, stride, E, n_embd, n_ff, ptr(g), ptr(u), ptr(d), ptr(sc[0]), ptr(sc[1]), ptr(sc[2]),
+                                               0 if device is None else 1, stream)
+    if rc:
+        raise B200MoeError(rc, "b200moe_unpack_expert_blobs_nvfp4")
+    return g, u, d, sc[0], sc[1], sc[2]
+
+
 class Context:
     """One per GPU and stream of work (reference: one ggml backend instance, one graph in flight)."""
 

@@ -215,3 +215,15 @@ def algorithmic_bytes(cfg: LayerConfig, n_tokens: int, experts_touched: int, x_b
         b += cfg.n_latent * moe.row_size(cfg.wtype, cfg.n_embd) + cfg.n_embd * moe.row_size(cfg.wtype, cfg.n_latent)
     b += n_tokens * cfg.n_embd * (x_bytes_per_elt + 4)
     return int(b)
+
+
+def pack_expert_blobs_nvfp4(layer: "HostLayer") -> np.ndarray:
+    """The layer's NVFP4 experts as edge0-strata writes them to experts.bin (tools/iq_pack.py; docs/NVFP4.md:44-47): one blob per
+    expert, [gate rows | up rows | down rows] + the 16-byte tail {s_gate, s_up, s_down, 0}.  uint8 [n_expert][blob bytes]."""
+    E = layer.gate.shape[0]
+    one = np.ones(E, np.float32)
+    sg = layer.gate_scale if layer.gate_scale is not None else one
+    su = layer.up_scale if layer.up_scale is not None else one
+    sd = layer.down_scale if layer.down_scale is not None else one
+    tail = np.stack([sg, su, sd, np.zeros(E, np.float32)], axis=1).astype(np.float32).view(np.uint8).reshape(E, 16)
+    return np.concatenate([layer.gate.reshape(E, -1), layer.up.reshape(E, -1), layer.down.reshape(E, -1), tail], axis=1)

@@ -171,6 +171,20 @@ B200MOE_API int  b200moe_mul_mat_id_width_ok(int type, int64_t ne00);
 B200MOE_API int  b200moe_quantize_nvfp4_host(const float * src, void * dst, int64_t nrows, int64_t n_per_row);
 B200MOE_API int  b200moe_dequantize_host(int type, const void * src, float * dst, int64_t nrows, int64_t n_per_row);
 
+/* ---- expert packs of edge0-strata (tools/iq_pack.py, docs/NVFP4.md:44-47; layout: NativeExpertLayout,
+ *      include/strata/kernels/iq_kernels.hpp:53-60): experts.bin holds one blob per expert,
+ *          [gate rows (n_ff x n_embd) | up rows (n_ff x n_embd) | down rows (n_embd x n_ff)] as raw block_nvfp4 rows
+ *          + a 16-byte tail {s_gate, s_up, s_down, 0} (fp32),
+ *      because the GGUF has no room for the per-tensor scales.  The rows are the bytes the kernels read: loading is three
+ *      copies per expert into the [n_expert][rows][row_bytes] tensors of b200moe_layer plus the tails into its three scale
+ *      arrays - no repacking.  `blobs` is host memory, expert e at blobs + e * blob_stride (blob_stride >= blob bytes).
+ *      to_device = 0: the destinations are host memory too; 1: device memory, copied on `stream`, which the call synchronises
+ *      before it returns (the blobs may be freed afterwards). */
+B200MOE_API int64_t b200moe_expert_blob_bytes_nvfp4(int32_t n_embd, int32_t n_ff);
+B200MOE_API int  b200moe_unpack_expert_blobs_nvfp4(const void * blobs, int64_t blob_stride, int32_t n_expert, int32_t n_embd, int32_t n_ff,
+                                                   void * gate, void * up, void * down, float * gate_scale, float * up_scale,
+                                                   float * down_scale, int to_device, void * stream);
+
 /* ---- compute.  `stream` is a cudaStream_t (NULL = default stream); calls are asynchronous on it. */
 
 /* Builder::route (forward.cpp:262-271) = mul_mat(F32) -> soft_max -> argsort_top_k -> get_rows ->

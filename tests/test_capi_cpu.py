@@ -43,6 +43,25 @@ def test_nvfp4_quantiser_and_dequantisers_match_checker(restatement):
     assert np.array_equal(moe.quantize_nvfp4(z["nvfp4_w"]), z["nvfp4_wq"])
 
 
+def test_strata_expert_blobs_unpack_into_the_layer_layout():
+    """edge0-strata's experts.bin blobs ([gate | up | down] + {s_gate, s_up, s_down, 0}, docs/NVFP4.md:44-47) unpack into the tensors and
+    scale arrays of b200moe_layer byte for byte (host destinations here; the device path is the same copies with cudaMemcpyAsync)."""
+    from edge0_b200 import workloads as W
+    cfg = W.small_config(TYPE_NVFP4, n_embd=256, n_expert=8, top_k=2, n_ff=128, seed=31)
+    layer = W.make_layer(cfg)
+    blobs = W.pack_expert_blobs_nvfp4(layer)
+    lib = capi.load()
+    assert blobs.shape[1] == lib.b200moe_expert_blob_bytes_nvfp4(256, 128) == 2 * 128 * 144 + 256 * 72 + 16
+    padded = np.concatenate([blobs, np.full((8, 48), 0xEE, np.uint8)], axis=1)          # a pack may align its blobs
+    for b in (blobs, padded):
+        g, u, d, sg, su, sd = moe.unpack_expert_blobs_nvfp4(b, 256, 128)
+        assert np.array_equal(g, layer.gate) and np.array_equal(u, layer.up) and np.array_equal(d, layer.down)
+        assert np.array_equal(sg, layer.gate_scale) and np.array_equal(su, layer.up_scale) and np.array_equal(sd, layer.down_scale)
+    assert lib.b200moe_expert_blob_bytes_nvfp4(250, 128) == -1
+    with pytest.raises(ValueError):
+        moe.unpack_expert_blobs_nvfp4(blobs[:, :-1], 256, 128)
+
+
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU behaviour")
 def test_no_device_means_no_compute():
     lib = capi.load()

@@ -358,6 +358,21 @@ def test_shared_expert_arguments(gpu_ctx):
     assert gpu_ctx.launches() == before
 
 
+def test_layer_loaded_from_strata_expert_blobs(gpu_ctx):
+    """Experts copied straight from edge0-strata's experts.bin blobs ([gate | up | down] + scale tail, docs/NVFP4.md:44-47) into device
+    tensors give the layer the very same bits as the layer built from the separate arrays."""
+    cfg = W.small_config(TYPE_NVFP4, n_embd=512, n_expert=16, top_k=4, n_ff=256, seed=33)
+    host = W.make_layer(cfg)
+    g, u, d, sg, su, sd = moe.unpack_expert_blobs_nvfp4(W.pack_expert_blobs_nvfp4(host), 512, 256, device=torch.device("cuda", 0))
+    assert np.array_equal(g.cpu().numpy(), host.gate) and np.array_equal(d.cpu().numpy(), host.down) and np.array_equal(su.cpu().numpy(), host.up_scale)
+    loaded = moe.MoeLayer(gpu_ctx, wtype=TYPE_NVFP4, top_k=4, router_w=host.router_w, gate=g, up=u, down=d, gate_scale=sg, up_scale=su, down_scale=sd)
+    x = torch.from_numpy(W.make_tokens(cfg, 9)).cuda()
+    a = loaded.forward(x)
+    b = host.to_device(gpu_ctx).forward(x)
+    gpu_ctx.synchronize()
+    assert torch.equal(a, b)
+
+
 def test_route_and_ffn_entry_points_compose(gpu_ctx, checker):
     cfg = W.small_config(TYPE_NVFP4, seed=5)
     layer = W.make_layer(cfg)
