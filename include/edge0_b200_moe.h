@@ -151,9 +151,11 @@ B200MOE_API int  b200moe_set_expert_path(b200moe_ctx * ctx, int path);
 
 /* Launch overlap (no counterpart in the reference; comparable to a backend's own stream options).  OFF by default.  When on, calls
  * in the batched-decode regime (fewer than 24 routed rows per expert on average; larger calls always launch serially) launch the
- * kernels of one layer as programmatic dependents of one another, so a kernel's launch and set-up (barriers, tables, tensor
- * memory) run alongside the tail of its predecessor; every kernel waits for its predecessor to finish before it reads or writes
- * global memory.  Helps eagerly launched steps (+7 % through b200moe_layer_forward_host), not CUDA-graph replay. */
+ * small kernels and the integer expert kernels of one layer as programmatic dependents of one another, so a kernel's launch and
+ * set-up (barriers, tables) run alongside the tail of its predecessor; every kernel waits for its predecessor to finish before it
+ * reads or writes global memory.  The tensor-core kernels are never launched this way and never release their dependents early:
+ * nothing becomes resident beside a kernel that holds tensor memory.  Helps eagerly launched steps (+7 % through
+ * b200moe_layer_forward_host when measured on the integer path), not CUDA-graph replay. */
 B200MOE_API int  b200moe_set_launch_overlap(b200moe_ctx * ctx, int enable);
 /* Per-kernel device timing (reference: DecodeTiming with an injectable clock, include/edge0/timing.h:4-9).
  * When enabled, every expert-matmul launch is bracketed by CUDA events on its stream; b200moe_kernel_times
