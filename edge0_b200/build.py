@@ -10,7 +10,7 @@ import subprocess
 import sys
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-SRC = [os.path.join(ROOT, "csrc", "capi.cu")]
+SRC = [os.path.join(ROOT, "csrc", "capi.cu"), os.path.join(ROOT, "csrc", "gguf_reader.cpp")]
 DEPS = [os.path.join(ROOT, "csrc", f) for f in os.listdir(os.path.join(ROOT, "csrc"))] + [
     os.path.join(os.path.dirname(ROOT), "include", "edge0_b200_moe.h")]
 LIB = os.path.join(ROOT, "lib", "libedge0_b200.so")

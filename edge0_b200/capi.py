@@ -57,6 +57,12 @@ SIGNATURES = {
     "b200moe_mul_mat_id_width_ok": (C.c_int, [C.c_int, C.c_int64]),
     "b200moe_quantize_nvfp4_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]),
     "b200moe_dequantize_host": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]),
+    "b200moe_gguf_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p), C.c_char_p, C.c_size_t]),
+    "b200moe_gguf_close": (None, [C.c_void_p]),
+    "b200moe_gguf_n_tensors": (C.c_int64, [C.c_void_p]),
+    "b200moe_gguf_tensor": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_int32), C.POINTER(C.c_int64 * 4), C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
+    "b200moe_gguf_metadata_u64": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "b200moe_gguf_moe_layer": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(Layer), C.c_char_p, C.c_size_t]),
     "b200moe_expert_blob_bytes_nvfp4": (C.c_int64, [C.c_int32, C.c_int32]),
     "b200moe_unpack_expert_blobs_nvfp4": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
                                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),

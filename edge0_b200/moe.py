@@ -90,6 +90,72 @@ def unpack_expert_blobs_nvfp4(blobs: np.ndarray, n_embd: int, n_ff: int, device=
     return g, u, d, sc[0], sc[1], sc[2]
 
 
+class GgufFile:
+    """A GGUF model file mapped read-only (b200moe_gguf_*): tensors come out as numpy views of the mapping in ggml's block layout.
+    Keep the object alive while such views (or layers built from them before their copy to the device) are in use."""
+
+    def __init__(self, path: str):
+        self.lib = capi.load()
+        h, err = C.c_void_p(), C.create_string_buffer(256)
+        rc = self.lib.b200moe_gguf_open(str(path).encode(), C.byref(h), err, 256)
+        if rc:
+            raise B200MoeError(rc, err.value.decode())
+        self.handle = h
+
+    def close(self):
+        if self.handle:
+            self.lib.b200moe_gguf_close(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def n_tensors(self) -> int:
+        return int(self.lib.b200moe_gguf_n_tensors(self.handle))
+
+    def tensor(self, name: str):
+        """(ggml type, ne[4], uint8 view of the tensor's bytes)."""
+        t, ne, data, nb = C.c_int32(), (C.c_int64 * 4)(), C.c_void_p(), C.c_uint64()
+        rc = self.lib.b200moe_gguf_tensor(self.handle, name.encode(), C.byref(t), C.byref(ne), C.byref(data), C.byref(nb))
+        if rc:
+            raise B200MoeError(rc, f"tensor {name}")
+        buf = (C.c_uint8 * nb.value).from_address(data.value)
+        return t.value, tuple(ne), np.frombuffer(buf, dtype=np.uint8)
+
+    def metadata_u64(self, key: str) -> int:
+        v = C.c_uint64()
+        rc = self.lib.b200moe_gguf_metadata_u64(self.handle, key.encode(), C.byref(v))
+        if rc:
+            raise KeyError(key)
+        return int(v.value)
+
+    def moe_layer_tensors(self, layer: int, top_k: int = 0) -> dict:
+        """The MoE FFN tensors of block `layer` as keyword arguments of MoeLayer (numpy views of the mapping; MoeLayer copies them to
+        the device as they are)."""
+        d, err = Layer(), C.create_string_buffer(256)
+        rc = self.lib.b200moe_gguf_moe_layer(self.handle, layer, top_k, C.byref(d), err, 256)
+        if rc:
+            raise B200MoeError(rc, err.value.decode())
+        H, E, I, Is = d.n_embd, d.n_expert, d.n_ff, d.n_ff_shexp
+        row = lambda n: int(self.lib.b200moe_row_size(d.wtype, n))
+
+        def view(ptr, shape, dtype):
+            if not ptr:
+                return None
+            n = int(np.prod(shape)) * np.dtype(dtype).itemsize
+            return np.frombuffer((C.c_uint8 * n).from_address(ptr), dtype=dtype).reshape(shape)
+
+        out = dict(wtype=d.wtype, top_k=d.n_expert_used, router_w=view(d.router_w, (E, H), np.float32), router_bias=view(d.router_bias, (E,), np.float32),
+                   gate=view(d.gate, (E, I, row(H)), np.uint8), up=view(d.up, (E, I, row(H)), np.uint8), down=view(d.down, (E, H, row(I)), np.uint8))
+        if Is:
+            out.update(gate_shexp=view(d.gate_shexp, (Is, row(H)), np.uint8), up_shexp=view(d.up_shexp, (Is, row(H)), np.uint8),
+                       down_shexp=view(d.down_shexp, (H, row(Is)), np.uint8), gate_inp_shexp=view(d.gate_inp_shexp, (H,), np.float32))
+        return out
+
+
 class Context:
     """One per GPU and stream of work (reference: one ggml backend instance, one graph in flight)."""
 

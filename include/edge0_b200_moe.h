@@ -187,6 +187,23 @@ B200MOE_API int  b200moe_unpack_expert_blobs_nvfp4(const void * blobs, int64_t b
                                                    void * gate, void * up, void * down, float * gate_scale, float * up_scale,
                                                    float * down_scale, int to_device, void * stream);
 
+/* ---- GGUF model files (reference: edge0-infer reads its weights through ggml's gguf API, src/model/asset_index.cpp; format:
+ *      third_party/ggml/docs/gguf.md).  Host code.  The file is mapped read-only and tensors are handed out as pointers into the
+ *      mapping, in ggml's block layout - the layout the kernels read, so a layer loads with one copy per tensor and no repacking.
+ *      b200moe_gguf_moe_layer fills a b200moe_layer with HOST pointers to the MoE FFN tensors of block `layer` as edge0-infer names
+ *      them (forward.cpp:262-314: blk.N.ffn_gate_inp.weight, ffn_gate_exps / ffn_up_exps / ffn_down_exps .weight, optionally
+ *      exp_probs_b.bias and the four shared-expert tensors); n_expert_used <= 0 reads <general.architecture>.expert_used_count
+ *      (models/edge0_35b/assets.cpp:63-66).  The caller copies the tensors to the device (their sizes: b200moe_gguf_tensor) and
+ *      passes device pointers to the compute entry points; the mapping must stay open until those copies are done. */
+typedef struct b200moe_gguf b200moe_gguf;
+B200MOE_API int  b200moe_gguf_open(const char * path, b200moe_gguf ** out, char * err, size_t err_len);
+B200MOE_API void b200moe_gguf_close(b200moe_gguf * g);
+B200MOE_API int64_t b200moe_gguf_n_tensors(const b200moe_gguf * g);
+/* B200MOE_ERR_INVALID_ARG: no such tensor; B200MOE_ERR_UNSUPPORTED: a ggml type this library does not read (type and ne are still set) */
+B200MOE_API int  b200moe_gguf_tensor(const b200moe_gguf * g, const char * name, int32_t * type, int64_t ne[4], const void ** data, uint64_t * nbytes);
+B200MOE_API int  b200moe_gguf_metadata_u64(const b200moe_gguf * g, const char * key, uint64_t * value);
+B200MOE_API int  b200moe_gguf_moe_layer(const b200moe_gguf * g, int32_t layer, int32_t n_expert_used, b200moe_layer * out, char * err, size_t err_len);
+
 /* ---- compute.  `stream` is a cudaStream_t (NULL = default stream); calls are asynchronous on it. */
 
 /* Builder::route (forward.cpp:262-271) = mul_mat(F32) -> soft_max -> argsort_top_k -> get_rows ->

@@ -209,6 +209,8 @@ class Reference(_Checker):
         self.lib.ref_mul_mat_id_backend.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
                                                     C.c_int64, C.c_int64, C.c_void_p, C.c_int]
         self.lib.ref_mul_mat_id_backend.restype = C.c_int
+        self.lib.ref_write_moe_gguf.argtypes = [C.c_char_p, C.POINTER(MoeArgs), C.c_int]
+        self.lib.ref_write_moe_gguf.restype = C.c_int
         self.lib.ref_backend_confirm.argtypes = [C.c_void_p]
         self.lib.ref_backend_confirm.restype = C.c_int
         self.lib.ref_backend_free.argtypes = [C.c_void_p]
@@ -229,6 +231,22 @@ class Reference(_Checker):
         rc = self.lib.ref_mul_mat_id_backend(backend, int(wtype), experts.ctypes.data, ne00, ne01, n_as, x.ctypes.data, ids.ctypes.data,
                                              n_ids, T, dst.ctypes.data, n_threads)
         return rc, dst
+
+    def write_moe_gguf(self, path, *, layer, wtype, router_w, gate, up, down, top_k, sh_gate=None, sh_up=None, sh_down=None, sh_gate_inp=None):
+        """One MoE block written as a GGUF file by the reference's own gguf writer (test input for the product's GGUF reader)."""
+        f32 = lambda a: None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+        u8 = lambda a: None if a is None else np.ascontiguousarray(a, dtype=np.uint8)
+        keep = dict(router_w=f32(router_w), gate=u8(gate), up=u8(up), down=u8(down), sh_gate=u8(sh_gate), sh_up=u8(sh_up), sh_down=u8(sh_down),
+                    sh_gate_inp=f32(sh_gate_inp))
+        E, H = keep["router_w"].shape
+        a = MoeArgs(H=H, L=H, E=E, K=top_k, I=gate.shape[1], T=0, wtype=wtype, n_threads=1, repeats=0, latent=0)
+        if sh_gate is not None:
+            a.I_sh = keep["sh_gate"].shape[0]
+        for k, v in keep.items():
+            setattr(a, k, _ptr(v))
+        rc = self.lib.ref_write_moe_gguf(str(path).encode(), C.byref(a), int(layer))
+        if rc:
+            raise RuntimeError(f"ref_write_moe_gguf failed with {rc}")
 
     def backend_confirm(self, backend) -> int:
         """Synchronize, then compute an empty graph on `backend`: 0 when everything before it completed, else 4."""

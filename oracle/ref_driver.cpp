@@ -16,11 +16,13 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <string>
 #include <vector>
 
 #include "ggml.h"
 #include "ggml-alloc.h"
 #include "ggml-backend.h"
+#include "gguf.h"
 #include "ggml-cpu.h"
 
 extern "C" {
@@ -314,6 +316,43 @@ int ref_backend_confirm(void * backend) {
     const int rc = ggml_backend_graph_compute((ggml_backend_t) backend, g) == GGML_STATUS_SUCCESS ? 0 : 4;
     ggml_free(c);
     return rc;
+}
+
+// Writes a GGUF file with ONE MoE block through the reference's own gguf writer (third_party/ggml/src/gguf.cpp): metadata
+// general.architecture = "qwen3next", qwen3next.block_count / expert_count / expert_used_count, and the tensors edge0-infer's graph
+// names (forward.cpp:262-314): blk.<layer>.ffn_gate_inp.weight (F32), ffn_gate_exps / ffn_up_exps / ffn_down_exps .weight, and the
+// four shared-expert tensors when the arguments hold them.  Test input for the product's GGUF reader.
+int ref_write_moe_gguf(const char * path, const ref_moe_args * a, int layer) {
+    if (!path || !a || a->latent) return 1;
+    ggml_init_params ip = { ggml_tensor_overhead() * 16, nullptr, true };
+    ggml_context * c = ggml_init(ip);
+    gguf_context * g = gguf_init_empty();
+    if (!c || !g) return 2;
+    gguf_set_val_str(g, "general.architecture", "qwen3next");
+    gguf_set_val_u32(g, "qwen3next.block_count", (uint32_t) layer + 1);
+    gguf_set_val_u32(g, "qwen3next.expert_count", (uint32_t) a->E);
+    gguf_set_val_u32(g, "qwen3next.expert_used_count", (uint32_t) a->K);
+    const ggml_type wt = (ggml_type) a->wtype;
+    const std::string prefix = "blk." + std::to_string(layer) + ".";
+    auto add = [&](ggml_tensor * t, const char * name, const void * data) {
+        ggml_set_name(t, (prefix + name).c_str());
+        t->data = const_cast<void *>(data);
+        gguf_add_tensor(g, t);
+    };
+    add(ggml_new_tensor_2d(c, GGML_TYPE_F32, a->H, a->E), "ffn_gate_inp.weight", a->router_w);
+    add(ggml_new_tensor_3d(c, wt, a->H, a->I, a->E), "ffn_gate_exps.weight", a->gate);
+    add(ggml_new_tensor_3d(c, wt, a->H, a->I, a->E), "ffn_up_exps.weight", a->up);
+    add(ggml_new_tensor_3d(c, wt, a->I, a->H, a->E), "ffn_down_exps.weight", a->down);
+    if (a->sh_gate) {
+        add(ggml_new_tensor_2d(c, wt, a->H, a->I_sh), "ffn_gate_shexp.weight", a->sh_gate);
+        add(ggml_new_tensor_2d(c, wt, a->H, a->I_sh), "ffn_up_shexp.weight", a->sh_up);
+        add(ggml_new_tensor_2d(c, wt, a->I_sh, a->H), "ffn_down_shexp.weight", a->sh_down);
+        add(ggml_new_tensor_1d(c, GGML_TYPE_F32, a->H), "ffn_gate_inp_shexp.weight", a->sh_gate_inp);
+    }
+    const bool ok = gguf_write_to_file(g, path, false);
+    gguf_free(g);
+    ggml_free(c);
+    return ok ? 0 : 3;
 }
 
 void ref_backend_free(void * backend) { if (backend) ggml_backend_free((ggml_backend_t) backend); }

@@ -29,11 +29,28 @@ CASES = {
 }
 
 
+# a GGUF file with one MoE block (and its shared expert), written by the reference's gguf writer: input of the reader's tests
+GGUF_CASE = dict(config=W.small_config(TYPE_NVFP4, n_embd=64, n_expert=8, top_k=2, n_ff=64, n_ff_shexp=128, seed=16, tensor_scales=False), layer=5,
+                 file="moe_block_nvfp4.gguf")
+
+
+def write_gguf_fixture(ref, path=None):
+    cfg = GGUF_CASE["config"]
+    layer = W.make_layer(cfg)
+    path = path or os.path.join(HERE, GGUF_CASE["file"])
+    ref.write_moe_gguf(path, layer=GGUF_CASE["layer"], wtype=cfg.wtype, router_w=layer.router_w, gate=layer.gate, up=layer.up, down=layer.down,
+                       top_k=cfg.top_k, sh_gate=layer.gate_shexp, sh_up=layer.up_shexp, sh_down=layer.down_shexp, sh_gate_inp=layer.gate_inp_shexp)
+    return path
+
+
 def main():
     ref = O.reference()
     print("reference ISA:", ref.isa())
     q3k = lambda w: ref.quantize(TYPE_Q3_K, w)
     only = sys.argv[1:]
+    if not only or "gguf" in only:
+        p = write_gguf_fixture(ref)
+        print(os.path.basename(p), os.path.getsize(p) // 1024, "KiB")
     for name, (cfg, T, bf16) in CASES.items():
         if only and name not in only:
             continue

@@ -373,6 +373,27 @@ def test_layer_loaded_from_strata_expert_blobs(gpu_ctx):
     assert torch.equal(a, b)
 
 
+def test_layer_loaded_from_a_gguf_file(gpu_ctx, tmp_path):
+    """A block written to a GGUF file by the reference's gguf writer, read back by the library's reader and copied to the device as
+    it lies, computes the very same bits as the layer built from the arrays (shared expert included)."""
+    from oracle import oracle as O
+    if not O.have_reference():
+        pytest.skip("needs the compiled reference (its gguf writer)")
+    cfg = W.small_config(TYPE_NVFP4, n_embd=512, n_expert=16, top_k=4, n_ff=256, n_ff_shexp=256, seed=37, tensor_scales=False)
+    host = W.make_layer(cfg)
+    path = tmp_path / "block.gguf"
+    O.reference().write_moe_gguf(path, layer=2, wtype=cfg.wtype, router_w=host.router_w, gate=host.gate, up=host.up, down=host.down, top_k=4,
+                                 sh_gate=host.gate_shexp, sh_up=host.up_shexp, sh_down=host.down_shexp, sh_gate_inp=host.gate_inp_shexp)
+    g = moe.GgufFile(path)
+    loaded = moe.MoeLayer(gpu_ctx, **g.moe_layer_tensors(2))
+    g.close()                                           # the tensors are on the device now
+    x = torch.from_numpy(W.make_tokens(cfg, 7)).cuda()
+    a = loaded.forward(x)
+    b = host.to_device(gpu_ctx).forward(x)
+    gpu_ctx.synchronize()
+    assert torch.equal(a, b)
+
+
 def test_route_and_ffn_entry_points_compose(gpu_ctx, checker):
     cfg = W.small_config(TYPE_NVFP4, seed=5)
     layer = W.make_layer(cfg)
