@@ -147,3 +147,21 @@ def test_expert_parallel_equals_single_process(world, restatement):
         got[lo:hi] = out
         assert np.array_equal(ids, want.ids[lo:hi])
     assert np.array_equal(got, want.out), "expert-parallel result must not depend on the number of ranks"
+
+
+def test_backend_may_fuse_route_and_projection(restatement):
+    """A backend that offers route_and_project (the CUDA backend runs the two side by side on two streams) is used through it, with
+    the same result."""
+    cfg, layer, x = make_case()
+    want = restatement.moe_layer(x=x, **layer.checker_kwargs())
+
+    class Fused(CheckerBackend):
+        calls = 0
+
+        def route_and_project(self, x):
+            Fused.calls += 1
+            ids, w = self.route(x)
+            return ids, w, self.project_down(x)
+
+    out = ExpertParallelLayer(Fused(layer, 0, 1), cfg.n_expert, cfg.top_k).forward(torch.from_numpy(x))
+    assert Fused.calls == 1 and np.array_equal(out.numpy(), want.out)
